@@ -1,0 +1,70 @@
+// Shared device helpers of the janas_b200 kernels (sm_100a).
+//
+// Storage types are float or __nv_bfloat16; all arithmetic is done in float.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace jb {
+
+typedef __nv_bfloat16 bf16;
+
+// Positions a page of the cache holds.  The host side (cache/pages.py) uses the
+// same number.
+constexpr int PAGE = 64;
+
+// Error codes returned by the launchers (0 = launched).
+enum : int {
+    JB_OK = 0,
+    JB_EINVAL = -1,   // an argument the kernel does not take
+    JB_ELAUNCH = -2,  // the launch itself failed (cudaGetLastError)
+};
+
+template <typename T> __device__ __forceinline__ float to_f(T v);
+template <> __device__ __forceinline__ float to_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f<bf16>(bf16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f(float v);
+template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_f<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+        v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float warp_max(float v)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+        v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result.  The
+// order of the additions depends only on the block size.  red: 32 floats of
+// shared memory.
+__device__ __forceinline__ float block_sum(float v, float *red)
+{
+    int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int nwarp = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();  // red may still be read from an earlier call
+    if (lane == 0)
+        red[warp] = v;
+    __syncthreads();
+    float t = lane < nwarp ? red[lane] : 0.0f;
+    return warp_sum(t);
+}
+
+inline int launch_status()
+{
+    return cudaGetLastError() == cudaSuccess ? JB_OK : JB_ELAUNCH;
+}
+
+}  // namespace jb

@@ -1,0 +1,51 @@
+// The C interface of the janas_b200 kernel library.
+//
+// Every function takes device pointers and the stream to launch on, allocates
+// nothing and returns 0 or a negative code (JB_EINVAL: a size or type the
+// kernel does not take; JB_ELAUNCH: the launch failed).  The Python side
+// (janas_b200/csrc/ops.py) checks shapes and types before it calls in here.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+// element types of buffers
+#define JB_F32 0
+#define JB_BF16 1
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+int jb_embed(const void *table, int table_dt, const int32_t *tokens, float *x, int n, int dm,
+             cudaStream_t st);
+int jb_rmsnorm(float *x, const float *delta, int S, long long delta_stride,
+               const int32_t *row_idx, const void *w, int w_dt, void *out, int out_dt, int n_out,
+               int dm, float eps, cudaStream_t st);
+int jb_swiglu(const float *gu, int S, long long stride, void *out, int out_dt, int n, int ff,
+              cudaStream_t st);
+int jb_rope_table(float *cs, float *sn, const float *inv_freq, int n_pos, int half,
+                  cudaStream_t st);
+int jb_qk_norm_rope_append(const float *qkv, int S, long long split_stride, const void *q_w,
+                           const void *k_w, int w_dt, float eps, const float *cs, const float *sn,
+                           int rot_half, const int32_t *row_pos, const int32_t *row_seq,
+                           const int32_t *block_table, int bt_stride, void *q_out, void *k_cache,
+                           void *v_cache, int cache_dt, int n, int nh, int nkv, int hd,
+                           cudaStream_t st);
+int jb_attention_chunk(void);
+long long jb_attention_scratch(int n_rows, int nh, int hd, int max_chunks);
+int jb_attention(const void *q, const void *k_cache, const void *v_cache, int dt,
+                 const int32_t *row_pos, const int32_t *row_seq, const int32_t *block_table,
+                 int bt_stride, float *scratch, void *out, int row0, int n_rows, int nh, int nkv,
+                 int hd, int window, float scale, int max_chunks, cudaStream_t st);
+int jb_gemm_simt(const void *A, int a_dt, const void *W, int w_dt, float *out, int n, int m, int k,
+                 cudaStream_t st);
+int jb_sample_small_cap(void);
+int jb_sample(const float *logits, int rows, int V, const int32_t *row_slot,
+              const float *temperature, const int32_t *top_k, const float *top_p,
+              const float *min_p, unsigned long long *rng, unsigned long long *big_keys,
+              float *big_probs, long long big_cap, int32_t *out, int32_t *forced, cudaStream_t st);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,315 @@
+"""The kernels as Python functions over CUDA tensors.
+
+This module loads the compiled library (building it at the first call) and
+checks every argument before handing raw pointers to it.  There is no CPU
+fallback and no library model code behind these functions: without a GPU, or
+when the library cannot be built or loaded, they raise.
+
+Conventions: the residual stream and every matrix product's output are
+float32.  A product's output is a stack ``[S, n, m]`` of S partial sums whose
+sum over S is the result (S = 1 unless the product was split over k); the
+kernels that consume a product add the partial sums in the order 0 .. S-1.
+"""
+from __future__ import annotations
+
+import ctypes
+import threading
+from typing import Optional, Tuple
+
+import torch
+
+from . import build
+
+PAGE = 64  # positions per cache page; common.cuh has the same number
+
+_DT = {torch.float32: 0, torch.bfloat16: 1}
+_lock = threading.Lock()
+_lib: Optional[ctypes.CDLL] = None
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        with _lock:
+            if _lib is None:
+                path = build.library_path()
+                try:
+                    _lib = ctypes.CDLL(path)
+                except OSError as e:
+                    raise KernelError(f"janas_b200: cannot load {path}: {e}") from None
+                for name in ("jb_attention_scratch",):
+                    getattr(_lib, name).restype = ctypes.c_longlong
+    return _lib
+
+
+def loaded_library_path() -> Optional[str]:
+    return _lib._name if _lib is not None else None
+
+
+def _stream() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _p(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _need(t: torch.Tensor, name: str, dtype=None, shape=None) -> None:
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise KernelError(f"{name}: a CUDA tensor is needed (there is no CPU path)")
+    if not t.is_contiguous():
+        raise KernelError(f"{name}: must be contiguous")
+    if dtype is not None:
+        ok = t.dtype in dtype if isinstance(dtype, (tuple, list)) else t.dtype == dtype
+        if not ok:
+            raise KernelError(f"{name}: dtype {t.dtype}, expected {dtype}")
+    if shape is not None:
+        if len(shape) != t.dim() or any(s is not None and s != d for s, d in zip(shape, t.shape)):
+            raise KernelError(f"{name}: shape {tuple(t.shape)}, expected {tuple(shape)}")
+
+
+def _check(code: int, what: str) -> None:
+    if code == 0:
+        return
+    if code == -1:
+        raise KernelError(f"{what}: the kernel does not take these sizes or types")
+    raise KernelError(f"{what}: the launch failed (code {code})")
+
+
+_FLOATS = (torch.float32, torch.bfloat16)
+
+
+def stack(t: torch.Tensor) -> torch.Tensor:
+    """A product's output as a stack of partial sums: [n, m] -> [1, n, m]."""
+    return t if t.dim() == 3 else t.unsqueeze(0)
+
+
+# ------------------------------------------------------------------ row-wise
+def embed(table: torch.Tensor, tokens: torch.Tensor) -> torch.Tensor:
+    """x[j, :] = table[tokens[j], :] as float32."""
+    _need(table, "embedding table", _FLOATS)
+    _need(tokens, "tokens", torch.int32)
+    n, dm = tokens.numel(), table.shape[1]
+    x = torch.empty((n, dm), dtype=torch.float32, device=table.device)
+    _check(lib().jb_embed(_p(table), _DT[table.dtype], _p(tokens), _p(x), n, dm, _stream()),
+           "embed")
+    return x
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.dtype,
+            delta: Optional[torch.Tensor] = None,
+            rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """RMSNorm of the rows of x (float32 [n, dm]).
+
+    With ``delta`` (a stack [S, n, dm] of float32 partial sums) x is first
+    updated in place, x += delta[0] + ... + delta[S-1].  With ``rows`` (int32
+    indices) only those rows are normalized and returned, in that order."""
+    _need(x, "x", torch.float32, (None, None))
+    n, dm = x.shape
+    _need(weight, "norm weight", _FLOATS, (dm,))
+    S, stride = 0, 0
+    if delta is not None:
+        delta = stack(delta)
+        _need(delta, "delta", torch.float32, (None, n, dm))
+        S, stride = delta.shape[0], n * dm
+        if rows is not None:
+            raise KernelError("rmsnorm: delta and rows cannot be combined")
+    n_out = n
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+        n_out = rows.numel()
+    out = torch.empty((n_out, dm), dtype=out_dtype, device=x.device)
+    _check(lib().jb_rmsnorm(_p(x), _p(delta), S, ctypes.c_longlong(stride), _p(rows),
+                            _p(weight), _DT[weight.dtype], _p(out), _DT[out_dtype], n_out, dm,
+                            ctypes.c_float(eps), _stream()), "rmsnorm")
+    return out
+
+
+def add_(x: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
+    """x += delta[0] + ... + delta[S-1] in place (float32)."""
+    _need(x, "x", torch.float32, (None, None))
+    n, dm = x.shape
+    delta = stack(delta)
+    _need(delta, "delta", torch.float32, (None, n, dm))
+    _check(lib().jb_rmsnorm(_p(x), _p(delta), delta.shape[0], ctypes.c_longlong(n * dm),
+                            _p(None), _p(None), 0, _p(None), 0, n, dm, ctypes.c_float(0.0),
+                            _stream()), "add")
+    return x
+
+
+def swiglu(gate_up: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """SiLU(gate) * up for a stack [S, n, 2 ff] whose columns are [gate | up]."""
+    gate_up = stack(gate_up)
+    _need(gate_up, "gate_up", torch.float32, (None, None, None))
+    S, n, two_ff = gate_up.shape
+    if two_ff % 2:
+        raise KernelError("swiglu: the gate_up width must be even")
+    ff = two_ff // 2
+    out = torch.empty((n, ff), dtype=out_dtype, device=gate_up.device)
+    _check(lib().jb_swiglu(_p(gate_up), S, ctypes.c_longlong(n * two_ff), _p(out),
+                           _DT[out_dtype], n, ff, _stream()), "swiglu")
+    return out
+
+
+# ------------------------------------------------------------------ position
+def rope_table(inv_freq: torch.Tensor, n_pos: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """cos and sin of (float)p * inv_freq[i] for p < n_pos: two [n_pos, half]."""
+    _need(inv_freq, "inv_freq", torch.float32)
+    half = inv_freq.numel()
+    cs = torch.empty((n_pos, half), dtype=torch.float32, device=inv_freq.device)
+    sn = torch.empty_like(cs)
+    _check(lib().jb_rope_table(_p(cs), _p(sn), _p(inv_freq), n_pos, half, _stream()),
+           "rope_table")
+    return cs, sn
+
+
+def qk_norm_rope_append(qkv: torch.Tensor, q_weight: Optional[torch.Tensor],
+                        k_weight: Optional[torch.Tensor], eps: float,
+                        cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
+                        row_pos: torch.Tensor, row_seq: torch.Tensor,
+                        block_table: torch.Tensor, k_cache: Optional[torch.Tensor],
+                        v_cache: Optional[torch.Tensor], num_heads: int, num_kv_heads: int,
+                        head_dim: int, out_dtype: torch.dtype) -> torch.Tensor:
+    """Per-head RMSNorm of q and k (when weights are given), NeoX rotation by
+    the rows' positions (when tables are given), K and V appended to the cache
+    pages (when caches are given).  Returns q [n, heads, head_dim].
+
+    qkv: stack [S, n, (heads + 2 kv_heads) head_dim] float32, columns
+    [q | k | v].  k_cache, v_cache: [pages, kv_heads, PAGE, head_dim]."""
+    qkv = stack(qkv)
+    width = (num_heads + 2 * num_kv_heads) * head_dim
+    _need(qkv, "qkv", torch.float32, (None, None, width))
+    S, n, _ = qkv.shape
+    _need(row_pos, "row_pos", torch.int32, (n,))
+    _need(row_seq, "row_seq", torch.int32, (n,))
+    _need(block_table, "block_table", torch.int32, (None, None))
+    w_dt = 0
+    if q_weight is not None:
+        _need(q_weight, "q_norm weight", _FLOATS, (head_dim,))
+        _need(k_weight, "k_norm weight", q_weight.dtype, (head_dim,))
+        w_dt = _DT[q_weight.dtype]
+    rot_half = 0
+    if cos is not None:
+        _need(cos, "cos", torch.float32, (None, head_dim // 2))
+        _need(sin, "sin", torch.float32, tuple(cos.shape))
+        rot_half = head_dim // 2
+    if k_cache is not None:
+        _need(k_cache, "k_cache", out_dtype, (None, num_kv_heads, PAGE, head_dim))
+        _need(v_cache, "v_cache", out_dtype, tuple(k_cache.shape))
+    q = torch.empty((n, num_heads, head_dim), dtype=out_dtype, device=qkv.device)
+    _check(lib().jb_qk_norm_rope_append(
+        _p(qkv), S, ctypes.c_longlong(n * width), _p(q_weight), _p(k_weight), w_dt,
+        ctypes.c_float(eps), _p(cos), _p(sin), rot_half, _p(row_pos), _p(row_seq),
+        _p(block_table), block_table.shape[1], _p(q), _p(k_cache), _p(v_cache), _DT[out_dtype],
+        n, num_heads, num_kv_heads, head_dim, _stream()), "qk_norm_rope_append")
+    return q
+
+
+# ----------------------------------------------------------------- attention
+def attention_chunk() -> int:
+    return int(lib().jb_attention_chunk())
+
+
+_ATT_SCRATCH_BYTES = 256 << 20
+_att_scratch: dict = {}
+
+
+def _scratch(device: torch.device, floats: int) -> torch.Tensor:
+    buf = _att_scratch.get(device)
+    if buf is None or buf.numel() < floats:
+        buf = torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=device)
+        _att_scratch[device] = buf
+    return buf
+
+
+def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+              row_pos: torch.Tensor, row_seq: torch.Tensor, block_table: torch.Tensor,
+              window: int, scale: float, max_chunks: int) -> torch.Tensor:
+    """Causal GQA attention of every row over its sequence's cache pages.
+
+    q: [n, heads, hd]; caches [pages, kv_heads, PAGE, hd] of q's dtype.  Row r
+    is at position row_pos[r] of sequence row_seq[r], whose pages are
+    block_table[row_seq[r]]; it sees positions max(0, pos + 1 - window) .. pos
+    (all of 0 .. pos when window is 0).  max_chunks: the most chunks of
+    ``attention_chunk()`` positions that any row's range touches."""
+    _need(q, "q", _FLOATS, (None, None, None))
+    n, nh, hd = q.shape
+    _need(k_cache, "k_cache", q.dtype, (None, None, PAGE, hd))
+    _need(v_cache, "v_cache", q.dtype, tuple(k_cache.shape))
+    nkv = k_cache.shape[1]
+    _need(row_pos, "row_pos", torch.int32, (n,))
+    _need(row_seq, "row_seq", torch.int32, (n,))
+    _need(block_table, "block_table", torch.int32, (None, None))
+    out = torch.empty_like(q)
+    L = lib()
+    per_row = int(L.jb_attention_scratch(1, nh, hd, max_chunks))
+    rows_per_call = max(1, min(n, (_ATT_SCRATCH_BYTES // 4) // max(per_row, 1)))
+    scratch = _scratch(q.device, per_row * rows_per_call)
+    for row0 in range(0, n, rows_per_call):
+        cnt = min(rows_per_call, n - row0)
+        _check(L.jb_attention(_p(q), _p(k_cache), _p(v_cache), _DT[q.dtype], _p(row_pos),
+                              _p(row_seq), _p(block_table), block_table.shape[1], _p(scratch),
+                              _p(out), row0, cnt, nh, nkv, hd, window, ctypes.c_float(scale),
+                              max_chunks, _stream()), "attention")
+    return out
+
+
+# ------------------------------------------------------------------ products
+def linear(a: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """a [n, k] . weight[m, k]^T as a stack [S, n, m] of float32 partial sums."""
+    _need(a, "activations", _FLOATS, (None, None))
+    _need(weight, "weight", _FLOATS, (None, a.shape[1]))
+    n, k = a.shape
+    m = weight.shape[0]
+    out = torch.empty((1, n, m), dtype=torch.float32, device=a.device)
+    _check(lib().jb_gemm_simt(_p(a), _DT[a.dtype], _p(weight), _DT[weight.dtype], _p(out), n, m,
+                              k, _stream()), "linear")
+    return out
+
+
+# ------------------------------------------------------------------ sampling
+def sample(logits: torch.Tensor, out: Optional[torch.Tensor] = None,
+           row_slot: Optional[torch.Tensor] = None,
+           temperature: Optional[torch.Tensor] = None, top_k: Optional[torch.Tensor] = None,
+           top_p: Optional[torch.Tensor] = None, min_p: Optional[torch.Tensor] = None,
+           rng: Optional[torch.Tensor] = None, big_keys: Optional[torch.Tensor] = None,
+           big_probs: Optional[torch.Tensor] = None,
+           forced: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One token per row of logits [rows, V] (float32).
+
+    Without ``temperature`` every row takes the first index of its maximum.
+    Otherwise the settings (float32 / int32 arrays) and ``rng`` (int64 array,
+    the splitmix64 states) are indexed by row_slot[row]; a row whose
+    temperature is 0 is still greedy and leaves its state alone."""
+    _need(logits, "logits", torch.float32, (None, None))
+    rows, V = logits.shape
+    if out is None:
+        out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    _need(out, "out", torch.int32, (rows,))
+    for t, name, dt in ((row_slot, "row_slot", torch.int32), (temperature, "temperature",
+                        torch.float32), (top_k, "top_k", torch.int32),
+                        (top_p, "top_p", torch.float32), (min_p, "min_p", torch.float32),
+                        (rng, "rng", torch.int64), (forced, "forced", torch.int32)):
+        if t is not None:
+            _need(t, name, dt)
+    big_cap = 0
+    if big_keys is not None:
+        _need(big_keys, "big_keys", torch.int64, (None, None))
+        _need(big_probs, "big_probs", torch.float32, tuple(big_keys.shape))
+        if big_keys.shape[0] < rows:
+            raise KernelError("sample: scratch for fewer rows than logits")
+        big_cap = big_keys.shape[1]
+    if temperature is not None and rng is None:
+        raise KernelError("sample: temperature needs the random states")
+    _check(lib().jb_sample(_p(logits), rows, V, _p(row_slot), _p(temperature), _p(top_k),
+                           _p(top_p), _p(min_p), _p(rng), _p(big_keys), _p(big_probs),
+                           ctypes.c_longlong(big_cap), _p(out), _p(forced), _stream()), "sample")
+    return out
+
+
+def sample_small_cap() -> int:
+    return int(lib().jb_sample_small_cap())

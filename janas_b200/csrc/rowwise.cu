@@ -1,0 +1,151 @@
+// Row-wise kernels: embedding gather, RMSNorm (plain, gathered, fused with the
+// residual add), the activated gate of the feed-forward.
+//
+// The residual stream is float; the sum of squares, the scale and the product
+// with the weight are computed in float.  One block works on one row and adds
+// in an order that depends only on the row's width, so a row's result does not
+// depend on what else is in the batch.
+//
+// Formulas: the reference's rms_norm, out = (x * scale) * w with
+// scale = 1 / sqrtf(mean(x^2) + eps) (src/llm/model_impl.h:635-644), its
+// embedding rows without scaling (src/llm/model.c:78-91), and
+// SiLU(g) * u = g / (1 + e^-g) * u (src/llm/vmath.h:64-68).
+#include "common.cuh"
+#include "kernels.h"
+
+namespace jb {
+
+template <typename TT>
+__global__ void embed_kernel(const TT *__restrict__ table, const int32_t *__restrict__ tokens,
+                             float *__restrict__ x, int dm)
+{
+    size_t row = blockIdx.x;
+    const TT *src = table + (size_t)tokens[row] * dm;
+    float *dst = x + row * dm;
+    for (int i = threadIdx.x; i < dm; i += blockDim.x)
+        dst[i] = to_f(src[i]);
+}
+
+// x: [n, dm] float.  delta: S stacked [n, dm] float partial sums (or null).
+// When delta is given, x[row] += delta[0][row] + delta[1][row] + ... first and
+// is written back.  row_idx (or null) picks the rows that are normalized; with
+// it, out has one row per entry and no delta is allowed.
+template <typename TW, typename TO>
+__global__ void rmsnorm_kernel(float *__restrict__ x, const float *__restrict__ delta, int S,
+                               size_t delta_stride, const int32_t *__restrict__ row_idx,
+                               const TW *__restrict__ w, TO *__restrict__ out, int dm, float eps)
+{
+    __shared__ float red[32];
+    size_t orow = blockIdx.x;
+    size_t row = row_idx ? (size_t)row_idx[orow] : orow;
+    float *xr = x + row * dm;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < dm; i += blockDim.x) {
+        float v = xr[i];
+        if (delta) {
+            for (int s = 0; s < S; s++)
+                v += delta[(size_t)s * delta_stride + row * dm + i];
+            xr[i] = v;
+        }
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, red);
+    if (out == nullptr)
+        return;
+    float scale = 1.0f / sqrtf(ss / (float)dm + eps);
+    TO *o = out + orow * dm;
+    for (int i = threadIdx.x; i < dm; i += blockDim.x)
+        o[i] = from_f<TO>((xr[i] * scale) * to_f(w[i]));
+}
+
+// gu: S stacked [n, 2 ff] float partial sums; columns [0, ff) are the gate,
+// [ff, 2 ff) the up projection.  out[n, ff] = SiLU(gate) * up.
+template <typename TO>
+__global__ void swiglu_kernel(const float *__restrict__ gu, int S, size_t stride,
+                              TO *__restrict__ out, int ff, size_t total)
+{
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total)
+        return;
+    size_t row = i / ff;
+    int c = (int)(i % ff);
+    float g = 0.0f, u = 0.0f;
+    for (int s = 0; s < S; s++) {
+        const float *p = gu + (size_t)s * stride + row * 2 * ff;
+        g += p[c];
+        u += p[ff + c];
+    }
+    float h = g / (1.0f + expf(-g)) * u;
+    out[i] = from_f<TO>(h);
+}
+
+static int norm_threads(int dm)
+{
+    int t = 32;
+    while (t < 1024 && t * 4 < dm)
+        t <<= 1;
+    return t;
+}
+
+}  // namespace jb
+
+using namespace jb;
+
+extern "C" int jb_embed(const void *table, int table_dt, const int32_t *tokens, float *x, int n,
+                        int dm, cudaStream_t st)
+{
+    if (n <= 0)
+        return JB_OK;
+    int threads = norm_threads(dm);
+    if (table_dt == JB_F32)
+        embed_kernel<float><<<n, threads, 0, st>>>((const float *)table, tokens, x, dm);
+    else if (table_dt == JB_BF16)
+        embed_kernel<bf16><<<n, threads, 0, st>>>((const bf16 *)table, tokens, x, dm);
+    else
+        return JB_EINVAL;
+    return launch_status();
+}
+
+extern "C" int jb_rmsnorm(float *x, const float *delta, int S, long long delta_stride,
+                          const int32_t *row_idx, const void *w, int w_dt, void *out, int out_dt,
+                          int n_out, int dm, float eps, cudaStream_t st)
+{
+    if (n_out <= 0)
+        return JB_OK;
+    if (delta && row_idx)
+        return JB_EINVAL;
+    int threads = norm_threads(dm);
+#define JB_NORM(TW, TO)                                                                       \
+    rmsnorm_kernel<TW, TO><<<n_out, threads, 0, st>>>(x, delta, S, (size_t)delta_stride,      \
+                                                      row_idx, (const TW *)w, (TO *)out, dm, eps)
+    if (out == nullptr)
+        JB_NORM(float, float);
+    else if (w_dt == JB_F32 && out_dt == JB_F32)
+        JB_NORM(float, float);
+    else if (w_dt == JB_F32 && out_dt == JB_BF16)
+        JB_NORM(float, bf16);
+    else if (w_dt == JB_BF16 && out_dt == JB_F32)
+        JB_NORM(bf16, float);
+    else if (w_dt == JB_BF16 && out_dt == JB_BF16)
+        JB_NORM(bf16, bf16);
+    else
+        return JB_EINVAL;
+#undef JB_NORM
+    return launch_status();
+}
+
+extern "C" int jb_swiglu(const float *gu, int S, long long stride, void *out, int out_dt, int n,
+                         int ff, cudaStream_t st)
+{
+    size_t total = (size_t)n * ff;
+    if (total == 0)
+        return JB_OK;
+    unsigned blocks = (unsigned)((total + 255) / 256);
+    if (out_dt == JB_F32)
+        swiglu_kernel<float><<<blocks, 256, 0, st>>>(gu, S, (size_t)stride, (float *)out, ff, total);
+    else if (out_dt == JB_BF16)
+        swiglu_kernel<bf16><<<blocks, 256, 0, st>>>(gu, S, (size_t)stride, (bf16 *)out, ff, total);
+    else
+        return JB_EINVAL;
+    return launch_status();
+}

@@ -1,0 +1,308 @@
+// Choosing a token from a row of logits on the device: the first maximum, or
+// a draw after temperature, top-k, top-p and min-p.
+//
+// The draw follows the reference's sampler step by step
+// (src/llm/sample.c:283-342): the candidates are the logits not below
+// max - 30 T; with 0 < top_k < vocab only the top_k largest of them (equal
+// logits: the lower id first); sorted by falling logit, then rising id;
+// p_i = exp((l_i - l_0) / T) summed in double in that order; top_p keeps the
+// shortest prefix whose mass reaches top_p * sum; min_p drops what lies below
+// min_p * p_0; one splitmix64 number (src/llm/sample.c:133-139), scaled by the
+// sum, picks by walking the prefix.  A row with T <= 0 takes the first index
+// of the maximum (src/llm/sample.c:141-148) and uses no random number.
+//
+// One block works on one row.  Up to SMALL_CAP candidates are sorted in shared
+// memory; more than that (top_k off or very large) needs the caller's scratch.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace jb {
+
+constexpr int SAMPLE_THREADS = 1024;
+constexpr int SMALL_CAP = 2048;
+
+__device__ __forceinline__ uint32_t ordered_key(float f)
+{
+    uint32_t u = __float_as_uint(f);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+__device__ __forceinline__ float key_value(uint32_t k)
+{
+    return __uint_as_float((k & 0x80000000u) ? (k ^ 0x80000000u) : ~k);
+}
+
+__device__ __forceinline__ uint64_t splitmix64(uint64_t *state)
+{
+    uint64_t z = (*state += 0x9e3779b97f4a7c15ull);
+    z = (z ^ (z >> 30)) * 0xbf58476d1ce4e5b9ull;
+    z = (z ^ (z >> 27)) * 0x94d049bb133111ebull;
+    return z ^ (z >> 31);
+}
+
+// Ascending bitonic sort of n = a power of two keys, by the whole block.
+__device__ void bitonic_sort(uint64_t *keys, int n)
+{
+    for (int size = 2; size <= n; size <<= 1) {
+        for (int stride = size >> 1; stride > 0; stride >>= 1) {
+            __syncthreads();
+            for (int i = threadIdx.x; i < n / 2; i += blockDim.x) {
+                int lo = 2 * i - (i & (stride - 1));
+                int hi = lo + stride;
+                bool up = (lo & size) == 0;
+                uint64_t a = keys[lo], b = keys[hi];
+                if ((a > b) == up) {
+                    keys[lo] = b;
+                    keys[hi] = a;
+                }
+            }
+        }
+    }
+    __syncthreads();
+}
+
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+sample_kernel(const float *__restrict__ logits, int V, const int32_t *__restrict__ row_slot,
+              const float *__restrict__ temperature, const int32_t *__restrict__ top_k,
+              const float *__restrict__ top_p, const float *__restrict__ min_p,
+              uint64_t *__restrict__ rng, uint64_t *__restrict__ big_keys,
+              float *__restrict__ big_probs, long long big_cap, int32_t *__restrict__ out,
+              int32_t *__restrict__ forced)
+{
+    __shared__ float red_v[32];
+    __shared__ int red_i[32];
+    __shared__ uint32_t hist[256];
+    __shared__ uint64_t small_keys[SMALL_CAP];
+    __shared__ float small_probs[SMALL_CAP];
+    __shared__ unsigned n_fill, n_elig, sh_prefix, sh_remain;
+
+    int row = blockIdx.x, tid = threadIdx.x;
+    int lane = tid & 31, warp = tid >> 5;
+    const float *lg = logits + (size_t)row * V;
+    int slot = row_slot ? row_slot[row] : row;
+
+    // ---- the first maximum
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = tid; i < V; i += SAMPLE_THREADS) {
+        float v = lg[i];
+        if (bi == 0x7fffffff || v > bv) {
+            bv = v;
+            bi = i;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) {
+            bv = ov;
+            bi = oi;
+        }
+    }
+    if (lane == 0) {
+        red_v[warp] = bv;
+        red_i[warp] = bi;
+    }
+    __syncthreads();
+    if (warp == 0) {
+        bv = red_v[lane];
+        bi = red_i[lane];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) {
+                bv = ov;
+                bi = oi;
+            }
+        }
+        if (lane == 0) {
+            red_v[0] = bv;
+            red_i[0] = bi;
+        }
+    }
+    __syncthreads();
+    float mx = red_v[0];
+    int amax = red_i[0];
+    float T = temperature ? temperature[slot] : 0.0f;
+    if (!(T > 0.0f)) {
+        if (tid == 0) {
+            out[row] = amax;
+            if (forced)
+                forced[row] = 0;
+        }
+        return;
+    }
+
+    // ---- the candidates
+    float floor_v = mx - 30.0f * T;
+    int tk = top_k ? top_k[slot] : 0;
+    unsigned K = tk > 0 && tk < V ? (unsigned)tk : (unsigned)V;
+    if (tid == 0) {
+        n_fill = 0;
+        n_elig = 0;
+    }
+    __syncthreads();
+    unsigned mine = 0;
+    for (int i = tid; i < V; i += SAMPLE_THREADS)
+        mine += lg[i] >= floor_v;
+    mine = (unsigned)__reduce_add_sync(0xffffffffu, mine);
+    if (lane == 0)
+        atomicAdd(&n_elig, mine);
+    __syncthreads();
+    unsigned E = n_elig;
+    unsigned n_sel = E < K ? E : K;
+    uint32_t thr = 0;     // with E > K: the key of the K-th largest candidate
+    unsigned need_eq = 0;  // and how many candidates equal to it are taken
+    if (E > K) {
+        uint32_t prefix = 0, mask = 0;
+        unsigned remain = K;
+        for (int shift = 24; shift >= 0; shift -= 8) {
+            if (tid < 256)
+                hist[tid] = 0;
+            __syncthreads();
+            for (int i = tid; i < V; i += SAMPLE_THREADS) {
+                float v = lg[i];
+                uint32_t u = ordered_key(v);
+                if (v >= floor_v && (u & mask) == prefix)
+                    atomicAdd(&hist[(u >> shift) & 255u], 1u);
+            }
+            __syncthreads();
+            if (tid == 0) {
+                unsigned above = 0;
+                int b = 255;
+                for (; b > 0; b--) {
+                    if (above + hist[b] >= remain)
+                        break;
+                    above += hist[b];
+                }
+                sh_prefix = prefix | ((uint32_t)b << shift);
+                sh_remain = remain - above;
+            }
+            __syncthreads();
+            prefix = sh_prefix;
+            remain = sh_remain;
+            mask |= 255u << shift;
+            __syncthreads();
+        }
+        thr = prefix;
+        need_eq = remain;
+    }
+
+    bool small = n_sel <= SMALL_CAP;
+    uint64_t *keys = small ? small_keys : big_keys + (size_t)row * big_cap;
+    float *probs = small ? small_probs : big_probs + (size_t)row * big_cap;
+    int P = 1;
+    while ((unsigned)P < n_sel)
+        P <<= 1;
+    if (!small && (big_keys == nullptr || (long long)P > big_cap)) {
+        if (tid == 0)
+            out[row] = -1;  // no scratch for this many candidates
+        return;
+    }
+    for (int i = tid; i < V; i += SAMPLE_THREADS) {
+        float v = lg[i];
+        if (!(v >= floor_v))
+            continue;
+        uint32_t u = ordered_key(v);
+        if (E > K && u <= thr)
+            continue;
+        unsigned at = atomicAdd(&n_fill, 1u);
+        keys[at] = ((uint64_t)(~u) << 32) | (uint32_t)i;
+    }
+    __syncthreads();
+    if (E > K && tid == 0) {
+        // the candidates equal to the K-th: the lowest ids first
+        unsigned at = n_fill, got = 0;
+        for (int i = 0; i < V && got < need_eq; i++) {
+            float v = lg[i];
+            if (v >= floor_v && ordered_key(v) == thr) {
+                keys[at++] = ((uint64_t)(~thr) << 32) | (uint32_t)i;
+                got++;
+            }
+        }
+    }
+    for (int i = n_sel + tid; i < P; i += SAMPLE_THREADS)
+        keys[i] = ~0ull;
+    __syncthreads();
+    bitonic_sort(keys, P);
+
+    float top = key_value(~(uint32_t)(keys[0] >> 32));
+    for (unsigned i = tid; i < n_sel; i += SAMPLE_THREADS) {
+        float l = key_value(~(uint32_t)(keys[i] >> 32));
+        probs[i] = expf((l - top) / T);
+    }
+    __syncthreads();
+    if (tid != 0)
+        return;
+
+    // ---- the draw, in the candidates' order
+    unsigned nc = n_sel;
+    double sum = 0.0;
+    for (unsigned i = 0; i < nc; i++)
+        sum += (double)probs[i];
+    float tp = top_p ? top_p[slot] : 0.0f;
+    if (tp > 0.0f && tp < 1.0f) {
+        double c = 0.0;
+        double lim = (double)tp * sum;
+        unsigned kk = 0;
+        while (kk < nc && c < lim)
+            c += (double)probs[kk++];
+        nc = kk;
+        sum = c;
+    }
+    float mp = min_p ? min_p[slot] : 0.0f;
+    if (mp > 0.0f) {
+        unsigned kk = 1;
+        float lim = mp * probs[0];
+        while (kk < nc && probs[kk] >= lim)
+            kk++;
+        for (unsigned i = kk; i < nc; i++)
+            sum -= (double)probs[i];
+        nc = kk;
+    }
+    if (forced)
+        forced[row] = nc <= 1;
+    uint64_t state = rng[slot];
+    double u = (double)(splitmix64(&state) >> 11) * 0x1.0p-53 * sum;
+    rng[slot] = state;
+    int32_t pick = (int32_t)(uint32_t)keys[nc - 1];
+    for (unsigned i = 0; i + 1 < nc; i++) {
+        u -= (double)probs[i];
+        if (u < 0) {
+            pick = (int32_t)(uint32_t)keys[i];
+            break;
+        }
+    }
+    out[row] = pick;
+}
+
+}  // namespace jb
+
+using namespace jb;
+
+extern "C" int jb_sample_small_cap() { return SMALL_CAP; }
+
+// logits: [rows, V] float.  The per-sequence settings and the random state
+// are indexed by row_slot[row] (by the row itself when row_slot is null);
+// temperature null means every row takes the first maximum.  big_keys
+// [rows, big_cap] and big_probs [rows, big_cap] are needed only when a row may
+// keep more than jb_sample_small_cap() candidates; big_cap must then be a power
+// of two not below V.  out[row] is the token, or -1 when that scratch was
+// needed and not given.
+extern "C" int jb_sample(const float *logits, int rows, int V, const int32_t *row_slot,
+                         const float *temperature, const int32_t *top_k, const float *top_p,
+                         const float *min_p, unsigned long long *rng,
+                         unsigned long long *big_keys, float *big_probs, long long big_cap,
+                         int32_t *out, int32_t *forced, cudaStream_t st)
+{
+    if (rows <= 0)
+        return JB_OK;
+    if (V <= 0 || (temperature != nullptr && rng == nullptr))
+        return JB_EINVAL;
+    sample_kernel<<<rows, SAMPLE_THREADS, 0, st>>>(logits, V, row_slot, temperature, top_k, top_p,
+                                                   min_p, (uint64_t *)rng, (uint64_t *)big_keys,
+                                                   big_probs, big_cap, out, forced);
+    return launch_status();
+}

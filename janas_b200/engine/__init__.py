@@ -1,0 +1,6 @@
+"""The engine: the generic decoder, the step function, the generation loop."""
+from .model import DecoderModel, expected_tensors
+from .engine import Engine, StepEntry, StepError, parse_dtype
+from .replay import Replayer
+
+__all__ = ["DecoderModel", "expected_tensors", "Engine", "StepEntry", "StepError", "parse_dtype", "Replayer"]

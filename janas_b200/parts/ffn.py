@@ -1,0 +1,46 @@
+"""The SwiGLU feed-forward: down(SiLU(gate(x)) * up(x)), no biases
+(src/llm/model_ffn.c:147-154, src/llm/vmath.h:64-68).  The reference runs a
+dense layer as the single expert of a mixture with router weight exactly 1
+(src/llm/model_load.c:505-514); here it is a part of its own."""
+from __future__ import annotations
+
+from typing import Dict, Mapping, Optional
+
+import torch
+
+from ..csrc import ops
+from ..weights import MATRIX, TensorSpec
+from .base import FeedForward, StepContext
+from .linear import fuse_rows, product
+from .registry import register_feed_forward
+
+
+@register_feed_forward("swiglu")
+class SwiGLU(FeedForward):
+    """params: hidden_size, intermediate_size."""
+
+    def __init__(self, spec, dtype, device):
+        super().__init__(spec, dtype, device)
+        self.hidden = int(spec.params["hidden_size"])
+        self.inter = int(spec.params["intermediate_size"])
+        self.w_gate_up: Optional[torch.Tensor] = None
+        self.w_down: Optional[torch.Tensor] = None
+
+    def tensors(self, prefix: str) -> Dict[str, TensorSpec]:
+        n = self._name
+        return {
+            n(prefix, "gate_proj.weight"): TensorSpec((self.inter, self.hidden), MATRIX),
+            n(prefix, "up_proj.weight"): TensorSpec((self.inter, self.hidden), MATRIX),
+            n(prefix, "down_proj.weight"): TensorSpec((self.hidden, self.inter), MATRIX),
+        }
+
+    def load(self, prefix: str, tensors: Mapping[str, torch.Tensor]) -> None:
+        n = self._name
+        self.w_gate_up = fuse_rows([tensors[n(prefix, "gate_proj.weight")],
+                                    tensors[n(prefix, "up_proj.weight")]])
+        self.w_down = tensors[n(prefix, "down_proj.weight")].contiguous()
+
+    def forward(self, ctx: StepContext, h: torch.Tensor) -> torch.Tensor:
+        gu = product(h, self.w_gate_up)
+        act = ops.swiglu(gu, ctx.dtype)
+        return product(act, self.w_down)
