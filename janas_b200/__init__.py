@@ -7,3 +7,11 @@ generation loop (``engine``), sampling (``sampling``) and the CUDA kernels
 for sm_100a (``csrc``).
 """
 __version__ = "0.1.0"
+
+from .api import (ABI_VERSION, EFAIL, EFULL, EINVAL, EMODEL, ENOMEM, EOPEN, OK, LLM, LLMError,
+                  LLMParams, abi_version, open, params_default)
+from .engine.generate import GenOptions, GenStats
+
+__all__ = ["ABI_VERSION", "EFAIL", "EFULL", "EINVAL", "EMODEL", "ENOMEM", "EOPEN", "OK", "LLM",
+           "LLMError", "LLMParams", "abi_version", "open", "params_default", "GenOptions",
+           "GenStats"]

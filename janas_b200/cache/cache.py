@@ -157,16 +157,22 @@ class Cache:
         self.slots.give_back(slot)
         self.length[slot] = 0
 
-    def set_sampler(self, slot: int, temperature: float, top_k: int, top_p: float, min_p: float,
-                    seed: int) -> None:
-        """The sequence's sampling settings; the random sequence starts at
-        ``seed`` (src/llm/sample.c:118)."""
-        seed &= (1 << 64) - 1
-        self.rng[slot] = seed - (1 << 64) if seed >= (1 << 63) else seed
-        self.temperature[slot] = float(temperature)
-        self.top_k[slot] = int(top_k)
-        self.top_p[slot] = float(top_p)
-        self.min_p[slot] = float(min_p)
+    def set_samplers(self, slots: Sequence[int], options: Sequence) -> None:
+        """The sequences' sampling settings (objects with temperature, top_k,
+        top_p, min_p and seed); each random sequence starts at its seed
+        (src/llm/sample.c:118)."""
+        def signed(seed: int) -> int:
+            seed &= (1 << 64) - 1
+            return seed - (1 << 64) if seed >= (1 << 63) else seed
+
+        idx = torch.tensor(list(slots), dtype=torch.int64, device=self.device)
+        put = lambda dst, vals, dt: dst.index_copy_(
+            0, idx, torch.tensor(vals, dtype=dt).to(self.device))
+        put(self.rng, [signed(int(o.seed)) for o in options], torch.int64)
+        put(self.temperature, [float(o.temperature) for o in options], torch.float32)
+        put(self.top_k, [int(o.top_k) for o in options], torch.int32)
+        put(self.top_p, [float(o.top_p) for o in options], torch.float32)
+        put(self.min_p, [float(o.min_p) for o in options], torch.float32)
 
     # ---------------------------------------------------------------- steps
     def reserve(self, slots: Sequence[int], counts: Sequence[int]) -> None:

@@ -1,0 +1,128 @@
+"""The generation loop's decisions, without a device: which requests form a
+batch, when a sequence ends, and the whole loop over a fake engine."""
+import numpy as np
+import pytest
+
+from janas_b200.engine import generate as G
+from janas_b200.engine.generate import (FINISH_CONTEXT, FINISH_LENGTH, FINISH_STOP, GenOptions,
+                                        Request, finish_reason, plan_batches, tokens_needed)
+
+
+def test_tokens_needed():
+    assert tokens_needed(1, 1, 1000) == 64          # the last new token is never fed back
+    assert tokens_needed(64, 1, 1000) == 64
+    assert tokens_needed(64, 2, 1000) == 128
+    assert tokens_needed(900, 500, 1000) == 1024    # capped by the context, in whole pages
+
+
+def test_plan_batches():
+    assert plan_batches([10] * 5, [5] * 5, 2, 10_000, 1000) == [[0, 1], [2, 3], [4]]
+    # the cache holds 256 tokens: 100+30 -> 192, 10+5 -> 64, then full
+    assert plan_batches([100, 10, 10, 200], [30, 5, 5, 20], 8, 256, 1000) == [[0, 1], [2], [3]]
+    with pytest.raises(ValueError, match="need"):
+        plan_batches([300], [10], 8, 256, 1000)
+
+
+def test_finish_reason():
+    stops = frozenset([7, 9])
+    assert finish_reason(7, 1, 10, 5, 100, stops) == FINISH_STOP
+    assert finish_reason(3, 10, 10, 5, 100, stops) == FINISH_LENGTH
+    assert finish_reason(9, 10, 10, 5, 100, stops) == FINISH_STOP      # stop wins
+    assert finish_reason(3, 2, 10, 100, 100, stops) == FINISH_CONTEXT
+    assert finish_reason(3, 2, 10, 99, 100, stops) is None
+
+
+def test_options():
+    assert GenOptions(eos=5, stop=[1, 2]).stop_set() == frozenset([1, 2, 5])
+    assert GenOptions().stop_set() == frozenset()
+    with pytest.raises(ValueError):
+        GenOptions(stop=[1, 2, 3, 4, 5]).validate(100)
+    with pytest.raises(ValueError):
+        GenOptions(top_p=1.5).validate(100)
+
+
+class FakeEngine:
+    """Stands in for the engine: the "model" answers token t with (t + 1) % 50,
+    and the bookkeeping of slots is checked as the loop goes."""
+
+    class _Spec:
+        vocab_size = 50
+
+    class _Model:
+        pass
+
+    def __init__(self, max_positions=40, max_tokens=64 * 4, max_seqs=3):
+        from janas_b200.cache import SlotPool
+        self.model = self._Model()
+        self.model.spec = self._Spec()
+        self.max_positions = max_positions
+        self.device = "cpu"
+        self.pool = SlotPool(max_seqs)
+        self.len = {}
+        self.steps = []
+        eng = self
+
+        class _Cache:
+            max_seqs = eng.pool.n_slots
+            max_tokens = 64 * 4
+
+            def set_samplers(self, slots, options):
+                pass
+        self.cache = _Cache()
+        self.cache.max_tokens = max_tokens
+
+    def new_sequence(self):
+        s = self.pool.take()
+        self.len[s] = 0
+        return s
+
+    def free_sequence(self, s):
+        self.pool.give_back(s)
+        del self.len[s]
+
+    def length(self, s):
+        return self.len[s]
+
+    def step(self, entries):
+        self.steps.append([(e.slot, len(e.tokens)) for e in entries])
+        out = []
+        for e in entries:
+            assert self.pool.live(e.slot)
+            assert self.len[e.slot] + len(e.tokens) <= self.max_positions
+            self.len[e.slot] += len(e.tokens)
+            out.append((e.tokens[-1] + 1) % 50)
+        return out
+
+
+def run(monkeypatch, eng, reqs, **kw):
+    monkeypatch.setattr(G, "_pick", lambda engine, logits, slots, sampled, big:
+                        (np.asarray(logits), 0))
+    return G.generate(eng, reqs, **kw)
+
+
+def test_loop_unequal_prompts_stops_and_batches(monkeypatch):
+    eng = FakeEngine()
+    reqs = [Request([1, 2, 3], 5), Request([10], 3, GenOptions(eos=12)),
+            Request([20, 21], 0), Request([30] * 38, 10), Request([5], 2, GenOptions(stop=[6]))]
+    st = G.GenStats()
+    res = run(monkeypatch, eng, reqs, max_batch=3, stats=st)
+    assert res[0].tokens == [4, 5, 6, 7, 8] and res[0].finish == FINISH_LENGTH
+    assert res[1].tokens == [11, 12] and res[1].finish == FINISH_STOP      # the stop token counts
+    assert res[2].tokens == [] and res[2].finish == FINISH_LENGTH
+    # 38 prompt tokens, context 40: tokens at 38 and 39 are fed, then the context is full
+    assert res[3].tokens == [31, 32, 33] and res[3].finish == FINISH_CONTEXT
+    assert res[4].tokens == [6] and res[4].finish == FINISH_STOP
+    assert eng.pool.n_free == 3 and not eng.len            # every slot came back
+    assert st.batches == 2 and st.new_tokens == 11 and st.prompt_tokens == 3 + 1 + 38 + 1
+    # first batch: requests 0, 1 (2 has nothing to do); its second request ends first
+    assert [len(s) for s in eng.steps[:5]] == [2, 2, 1, 1, 1]
+    assert eng.steps[0] == [(eng.steps[0][0][0], 3), (eng.steps[0][1][0], 1)]
+
+
+def test_loop_refuses_bad_requests(monkeypatch):
+    eng = FakeEngine()
+    with pytest.raises(ValueError, match="empty"):
+        run(monkeypatch, eng, [Request([], 3)])
+    with pytest.raises(ValueError, match="context"):
+        run(monkeypatch, eng, [Request([1] * 41, 3)])
+    assert eng.pool.n_free == 3
