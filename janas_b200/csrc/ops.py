@@ -72,8 +72,13 @@ def _need(t: torch.Tensor, name: str, dtype=None, shape=None) -> None:
             raise KernelError(f"{name}: shape {tuple(t.shape)}, expected {tuple(shape)}")
 
 
-def _check(code: int, what: str) -> None:
+# how many of the library's kernels have been launched (for measurements)
+COUNTERS = {"launches": 0}
+
+
+def _check(code: int, what: str, kernels: int = 1) -> None:
     if code == 0:
+        COUNTERS["launches"] += kernels
         return
     if code == -1:
         raise KernelError(f"{what}: the kernel does not take these sizes or types")
@@ -254,7 +259,7 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
         _check(L.jb_attention(_p(q), _p(k_cache), _p(v_cache), _DT[q.dtype], _p(row_pos),
                               _p(row_seq), _p(block_table), block_table.shape[1], _p(scratch),
                               _p(out), row0, cnt, nh, nkv, hd, window, ctypes.c_float(scale),
-                              max_chunks, _stream()), "attention")
+                              max_chunks, _stream()), "attention", kernels=2)
     return out
 
 

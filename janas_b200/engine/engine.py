@@ -70,6 +70,7 @@ class Engine:
                            self.dtype, self.device)
         self.max_positions = min(model.spec.max_positions, self.cache.max_tokens)
         model.prepare(self.max_positions)
+        self.h2d_bytes = 0       # bytes of step inputs copied to the device so far
         # run-order entry -> (group, index within the group) of the cache it uses
         self._cache_entry: List[Optional[int]] = []
         for e, entry in enumerate(model.spec.run_order):
@@ -170,6 +171,7 @@ class Engine:
             + [t.reshape(-1) for t in tables]
         sizes = [p.size for p in parts]
         host = torch.from_numpy(np.concatenate(parts)).pin_memory()
+        self.h2d_bytes += host.numel() * host.element_size()
         with torch.cuda.device(self.device):
             dev = host.to(self.device, non_blocking=True)
             offs = np.concatenate([[0], np.cumsum(sizes)])

@@ -74,6 +74,8 @@ class GenStats:
     decode_seconds: float = 0.0
     sample_seconds: float = 0.0
     batches: int = 0
+    h2d_bytes: int = 0          # step inputs copied to the device while decoding
+    d2h_bytes: int = 0          # chosen tokens read back while decoding
 
 
 @dataclass
@@ -194,6 +196,9 @@ def generate(engine, requests: Sequence[Request], max_batch: int = 64,
                 else:
                     st.passes += 1
                     st.decode_seconds += now - t0
+                    st.h2d_bytes += getattr(engine, "h2d_bytes", 0) - h2d0
+                    st.d2h_bytes += 4 * len(active)
+                h2d0 = getattr(engine, "h2d_bytes", 0)
                 t0 = now
                 st.forced_tokens += forced
                 nxt, entries = [], []

@@ -238,38 +238,35 @@ def sample(row: np.ndarray, temperature: float, top_k: int, top_p: float, min_p:
     mx = row[argmax_first(row)]
     floor = np.float32(mx - np.float32(30.0) * t)
     ids = np.nonzero(row >= floor)[0]
-    order = sorted(ids.tolist(), key=lambda i: (-float(row[i]), i))
+    order = ids[np.lexsort((ids, -row[ids].astype(np.float64)))]   # falling logit, rising id
     nv = row.shape[0]
     k = top_k if 0 < top_k < nv else nv
     order = order[:k]
     top = row[order[0]]
-    p = [float(np.exp(np.float32((row[i] - top) / t), dtype=np.float32)) for i in order]
-    total = 0.0
-    for v in p:
-        total += v
+    p = np.exp(((row[order] - top) / t).astype(np.float32)).astype(np.float32)
+    csum = np.cumsum(p.astype(np.float64))          # added one by one, in order
+    total = float(csum[-1])
     nc = len(p)
     if 0 < top_p < 1:
-        c, kk = 0.0, 0
         lim = float(np.float32(top_p)) * total
-        while kk < nc and c < lim:
-            c += p[kk]
-            kk += 1
-        nc, total = kk, c
+        # the shortest prefix whose mass reaches lim (at least one candidate)
+        kk = int(np.searchsorted(csum, lim, side="left")) + 1
+        kk = min(max(kk, 1), nc)
+        nc, total = kk, float(csum[kk - 1])
     if min_p > 0:
-        kk = 1
-        lim = np.float32(min_p) * np.float32(p[0])
-        while kk < nc and np.float32(p[kk]) >= lim:
-            kk += 1
+        lim = np.float32(min_p) * p[0]
+        below = np.nonzero(p[1:nc] < lim)[0]
+        kk = int(below[0]) + 1 if below.size else nc
         for i in range(kk, nc):
-            total -= p[i]
+            total -= float(p[i])
         nc = kk
     rng_state, z = splitmix64(rng_state)
     u = float(z >> 11) * (2.0 ** -53) * total
     for i in range(nc - 1):
-        u -= p[i]
+        u -= float(p[i])
         if u < 0:
-            return order[i], rng_state
-    return order[nc - 1], rng_state
+            return int(order[i]), rng_state
+    return int(order[nc - 1]), rng_state
 
 
 def generate(c: Dict, w: Dict[str, torch.Tensor], prompt: Sequence[int], max_new: int,

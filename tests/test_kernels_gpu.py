@@ -1,0 +1,255 @@
+"""Each kernel alone against a plain float32 restatement of the same operation,
+at sizes other than the tiny models'."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as plain
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def ops():
+    from janas_b200.csrc import ops as o
+    return o
+
+
+def rnd(*shape, dtype=torch.float32, scale=1.0, seed=0):
+    g = torch.Generator().manual_seed(seed + sum(shape))
+    return (torch.randn(*shape, generator=g) * scale).to(dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("dm", [100, 2560])
+def test_embed(dtype, dm):
+    table = rnd(300, dm, dtype=dtype)
+    toks = torch.tensor([5, 299, 0, 5, 123], dtype=torch.int32)
+    got = ops().embed(table.to(DEV), toks.to(DEV)).cpu()
+    assert torch.equal(got, table[toks.long()].float())
+
+
+@pytest.mark.parametrize("wdt", DTYPES)
+@pytest.mark.parametrize("odt", DTYPES)
+@pytest.mark.parametrize("n,dm", [(1, 40), (5, 2560), (33, 1000)])
+def test_rmsnorm(wdt, odt, n, dm):
+    x = rnd(n, dm, scale=3.0)
+    w = (1 + 0.1 * rnd(dm)).to(wdt)
+    want = plain.rms_norm(x, w.float(), 1e-5)
+    got = ops().rmsnorm(x.to(DEV), w.to(DEV), 1e-5, odt).cpu().float()
+    tol = 2e-6 if odt == torch.float32 else 2 ** -8
+    assert (got - want).abs().max() <= tol * want.abs().max()
+    # with a stack of partial sums added first, and x updated in place
+    delta = rnd(3, n, dm, seed=1)
+    xd = x.to(DEV).clone()
+    got = ops().rmsnorm(xd, w.to(DEV), 1e-5, odt, delta=delta.to(DEV)).cpu().float()
+    x2 = x + delta[0] + delta[1] + delta[2]
+    assert torch.equal(xd.cpu(), x2)
+    want = plain.rms_norm(x2, w.float(), 1e-5)
+    assert (got - want).abs().max() <= tol * want.abs().max()
+    # chosen rows only
+    rows = torch.tensor([n - 1, 0], dtype=torch.int32)
+    got = ops().rmsnorm(x.to(DEV), w.to(DEV), 1e-5, odt, rows=rows.to(DEV)).cpu().float()
+    want = plain.rms_norm(x[rows.long()], w.float(), 1e-5)
+    assert (got - want).abs().max() <= tol * want.abs().max()
+
+
+@pytest.mark.parametrize("odt", DTYPES)
+def test_swiglu(odt):
+    n, ff = 7, 300
+    gu = rnd(2, n, 2 * ff, scale=4.0)
+    s = gu[0] + gu[1]
+    g, u = s[:, :ff], s[:, ff:]
+    want = g / (1 + torch.exp(-g)) * u
+    got = ops().swiglu(gu.to(DEV), odt).cpu().float()
+    tol = 2e-6 if odt == torch.float32 else 2 ** -8
+    assert (got - want).abs().max() <= tol * want.abs().max()
+
+
+@pytest.mark.parametrize("adt", DTYPES)
+@pytest.mark.parametrize("wdt", DTYPES)
+@pytest.mark.parametrize("n,m,k", [(1, 1, 1), (3, 70, 50), (65, 129, 33), (130, 64, 256),
+                                   (2, 300, 2560)])
+def test_gemm_simt(adt, wdt, n, m, k):
+    a, w = rnd(n, k, dtype=adt), rnd(m, k, dtype=wdt, seed=3)
+    want = (a.double() @ w.double().T).float()
+    got = ops().linear(a.to(DEV), w.to(DEV))
+    assert got.shape == (1, n, m)
+    assert (got[0].cpu() - want).abs().max() <= 1e-6 * math.sqrt(k) * max(1.0, want.abs().max())
+
+
+def test_gemm_rows_do_not_depend_on_the_batch():
+    a, w = rnd(70, 96), rnd(200, 96, seed=4)
+    whole = ops().linear(a.to(DEV), w.to(DEV))[0]
+    one = ops().linear(a[37:38].contiguous().to(DEV), w.to(DEV))[0]
+    assert torch.equal(whole[37:38], one)
+
+
+def test_rope_table():
+    for theta, hd in ((10000.0, 16), (1e6, 128), (50000.0, 48)):
+        half = hd // 2
+        expo = np.float32(-2.0) * np.arange(half, dtype=np.float32) / np.float32(hd)
+        inv = np.power(np.float64(np.float32(theta)), expo.astype(np.float64)).astype(np.float32)
+        cs, sn = ops().rope_table(torch.from_numpy(inv).to(DEV), 9000)
+        pos = [0, 1, 63, 64, 1000, 8999]
+        c, s = plain.rope_table(pos, hd, theta)
+        assert torch.equal(cs.cpu()[pos], c) and torch.equal(sn.cpu()[pos], s)
+
+
+def paged(k, v, n_pages, perm_seed=0):
+    """Lays [n, nkv, hd] keys and values of ONE sequence out in pages in a
+    shuffled order; returns caches and the block table."""
+    n, nkv, hd = k.shape
+    need = (n + 63) // 64
+    order = np.random.default_rng(perm_seed).permutation(n_pages)[:need]
+    kc = torch.zeros(n_pages, nkv, 64, hd, dtype=k.dtype)
+    vc = torch.zeros_like(kc)
+    for t in range(n):
+        kc[order[t // 64], :, t % 64] = k[t]
+        vc[order[t // 64], :, t % 64] = v[t]
+    bt = torch.full((1, (need + 7) // 8 * 8), -1, dtype=torch.int32)
+    bt[0, :need] = torch.from_numpy(order.astype(np.int32))
+    return kc, vc, bt
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,hd,window", [(8, 2, 128, 0), (8, 1, 64, 0), (5, 5, 80, 0),
+                                              (6, 2, 32, 50), (4, 4, 16, 130), (16, 2, 256, 0)])
+def test_attention_whole_sequence(dtype, nh, nkv, hd, window):
+    n = 300
+    q, k, v = rnd(n, nh, hd, dtype=dtype), rnd(n, nkv, hd, dtype=dtype, seed=1), \
+        rnd(n, nkv, hd, dtype=dtype, seed=2)
+    want = plain.attention(q.float(), k.float(), v.float(), window)
+    kc, vc, bt = paged(k, v, 9)
+    pos = torch.arange(n, dtype=torch.int32)
+    seq = torch.zeros(n, dtype=torch.int32)
+    chunk = ops().attention_chunk()
+    mc = (n - 1) // chunk + 1 if not window else min((n - 1) // chunk + 1, (window - 1) // chunk + 2)
+    got = ops().attention(q.to(DEV), kc.to(DEV), vc.to(DEV), pos.to(DEV), seq.to(DEV), bt.to(DEV),
+                          window, 1 / math.sqrt(hd), mc).cpu().float()
+    tol = 5e-6 if dtype == torch.float32 else 2 ** -8
+    assert (got - want).abs().max() <= tol * want.abs().max()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_finds_a_far_key_and_the_window_s_edge(dtype):
+    """One key among 700 has a score that stands out: the output is its value.
+    With a window the key is seen by exactly the rows whose window holds it."""
+    n, nh, nkv, hd = 700, 4, 2, 64
+    q = torch.zeros(n, nh, hd)
+    k = torch.zeros(n, nkv, hd)
+    v = rnd(n, nkv, hd)
+    q[:, :, 3] = 24.0
+    k[133, :, 3] = 24.0        # score 576 / 8 = 72 above the others
+    if dtype == torch.bfloat16:
+        v = v.to(dtype).float()
+    kc, vc, bt = paged(k.to(dtype), v.to(dtype), 12, perm_seed=5)
+    pos = torch.arange(n, dtype=torch.int32)
+    seq = torch.zeros(n, dtype=torch.int32)
+    chunk = ops().attention_chunk()
+    for window in (0, 200):
+        mc = (n - 1) // chunk + 1 if not window else (window - 1) // chunk + 2
+        got = ops().attention(q.to(dtype).to(DEV), kc.to(DEV), vc.to(DEV), pos.to(DEV),
+                              seq.to(DEV), bt.to(DEV), window, 1 / math.sqrt(hd), mc).cpu().float()
+        tol = 1e-5 if dtype == torch.float32 else 2 ** -7
+        last_seeing = n - 1 if not window else 133 + window - 1
+        for r in (133, 134, 400 if not window else 300, last_seeing):
+            assert (got[r, 1] - v[133, 0]).abs().max() <= tol, (window, r)
+        if window:
+            r = last_seeing + 1          # the key has just left the window
+            want = v[r + 1 - window:r + 1, 1].mean(0)
+            assert (got[r, 3] - want).abs().max() <= 10 * tol, (window, r)
+        want = v[:100, 0].mean(0)        # before the key: uniform over what is visible
+        assert (got[99, 0] - want).abs().max() <= 10 * tol
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_qk_norm_rope_append(dtype):
+    nh, nkv, hd = 6, 2, 48
+    n = 40
+    width = (nh + 2 * nkv) * hd
+    qkv = rnd(2, n, width, scale=2.0)
+    qw, kw = (1 + 0.1 * rnd(hd)).to(dtype), (1 + 0.1 * rnd(hd, seed=1)).to(dtype)
+    # two sequences: rows 0..24 are positions 70..94 of sequence 0, rows 25..39
+    # positions 0..14 of sequence 1
+    pos = torch.cat([torch.arange(70, 95), torch.arange(0, 15)]).int()
+    seq = torch.cat([torch.zeros(25), torch.ones(15)]).int()
+    bt = torch.tensor([[4, 2, -1, -1, -1, -1, -1, -1], [1, -1, -1, -1, -1, -1, -1, -1]],
+                      dtype=torch.int32)
+    kc = torch.zeros(6, nkv, 64, hd, dtype=dtype, device=DEV)
+    vc = torch.zeros_like(kc)
+    half = hd // 2
+    expo = np.float32(-2.0) * np.arange(half, dtype=np.float32) / np.float32(hd)
+    inv = np.power(np.float64(np.float32(1e6)), expo.astype(np.float64)).astype(np.float32)
+    cs, sn = ops().rope_table(torch.from_numpy(inv).to(DEV), 128)
+    q = ops().qk_norm_rope_append(qkv.to(DEV), qw.to(DEV), kw.to(DEV), 1e-6, cs, sn,
+                                  pos.to(DEV), seq.to(DEV), bt.to(DEV), kc, vc, nh, nkv, hd,
+                                  dtype).cpu().float()
+    s = qkv[0] + qkv[1]
+    qs, ks, vs = s[:, :nh * hd].view(n, nh, hd), s[:, nh * hd:(nh + nkv) * hd].view(n, nkv, hd), \
+        s[:, (nh + nkv) * hd:].view(n, nkv, hd)
+    c, sgn = plain.rope_table(pos.tolist(), hd, 1e6)
+    wq = plain.rope_neox(plain.rms_norm(qs, qw.float(), 1e-6), c, sgn)
+    wk = plain.rope_neox(plain.rms_norm(ks, kw.float(), 1e-6), c, sgn)
+    tol = 3e-6 if dtype == torch.float32 else 2 ** -8
+    assert (q - wq).abs().max() <= tol * wq.abs().max()
+    kc, vc = kc.cpu().float(), vc.cpu().float()
+    for r in range(n):
+        page = bt[seq[r], pos[r] // 64]
+        assert (kc[page, :, pos[r] % 64] - wk[r]).abs().max() <= tol * wk.abs().max()
+        assert (vc[page, :, pos[r] % 64] - vs[r]).abs().max() <= tol * vs.abs().max()
+    # nothing else was written
+    written = torch.zeros(6, 64, dtype=torch.bool)
+    for r in range(n):
+        written[bt[seq[r], pos[r] // 64], pos[r] % 64] = True
+    assert float(kc[~written].abs().sum()) == 0.0 and float(vc[~written].abs().sum()) == 0.0
+
+
+def test_argmax_is_the_first_maximum():
+    lg = rnd(9, 1000)
+    lg[2, 700] = lg[2, 30] = 9.0
+    lg[5, :] = 1.0
+    got = ops().sample(lg.to(DEV)).cpu().tolist()
+    want = [int(np.argmax(r)) for r in lg.numpy()]
+    assert got == want and got[2] == 30 and got[5] == 0
+
+
+@pytest.mark.parametrize("V", [300, 5000, 151936])
+def test_sampling_kernel_equals_the_plain_sampler(V):
+    """Many rows, every setting: the same picks and the same random states."""
+    rows = 12
+    lg = rnd(rows, V, scale=2.0, seed=V)
+    lg[3, 17] = lg[3, 5] = lg[3].max() + 1       # a tie at the top
+    lg[4, 100:103] = lg[4].topk(5).values[4]     # ties around a top_k cut of 5
+    settings = [(0.8, 20, 0.8, 0.0), (0.7, 0, 0.0, 0.0), (1.0, 5, 0.0, 0.0), (1.5, 0, 0.9, 0.05),
+                (0.3, 50, 1.0, 0.2), (2.0, 3, 0.5, 0.0), (0.0, 0, 0.0, 0.0), (1.0, 3000, 0.0, 0.0)]
+    o = ops()
+    cap = 1 << (V - 1).bit_length()
+    big_k = torch.empty(rows, cap, dtype=torch.int64, device=DEV)
+    big_p = torch.empty(rows, cap, dtype=torch.float32, device=DEV)
+    dl = lg.to(DEV)
+    for si, (t, k, p, mp) in enumerate(settings):
+        seeds = [(1 << 63) + 12345 * (si + 1) + r for r in range(rows)]
+        slot = torch.arange(rows, dtype=torch.int32).flip(0).contiguous()   # row r uses slot 11 - r
+        # state of slot s is the seed of the row that uses it
+        state = torch.empty(rows, dtype=torch.int64)
+        for r in range(rows):
+            s = seeds[r]
+            state[slot[r]] = s - (1 << 64) if s >= (1 << 63) else s
+        state = state.to(DEV)
+        full = lambda val, dt: torch.full((rows,), val, dtype=dt, device=DEV)
+        forced = torch.zeros(rows, dtype=torch.int32, device=DEV)
+        for rep in range(2):
+            got = o.sample(dl, row_slot=slot.to(DEV), temperature=full(t, torch.float32),
+                           top_k=full(k, torch.int32), top_p=full(p, torch.float32),
+                           min_p=full(mp, torch.float32), rng=state, big_keys=big_k,
+                           big_probs=big_p, forced=forced).cpu().tolist()
+            for r in range(rows):
+                tok, seeds[r] = plain.sample(lg[r].numpy(), t, k, p, mp, seeds[r])
+                assert got[r] == tok, (V, (t, k, p, mp), rep, r)
+            back = [(int(x) + (1 << 64)) % (1 << 64) for x in state.cpu().tolist()]
+            assert [back[int(slot[r])] for r in range(rows)] == seeds
