@@ -1,0 +1,498 @@
+// Matrix products on the fifth-generation tensor cores (tcgen05), bfloat16 in,
+// float accumulation in tensor memory, operands staged by TMA.
+//
+//     out[n, m] = A[n, k] . W[m, k]^T
+//
+// The weight matrix is the M operand of the instruction (128 output features per
+// tile, one TMEM lane each) and the tokens are its N operand (16 to 256 per
+// tile, one TMEM column each), so that a decode step with a handful of tokens
+// still fills the 128-row instruction and a weight is read exactly once.  Both
+// operands are K-major rows of 64 bfloat16 (128 bytes) in the 128-byte swizzle
+// that TMA writes and the matrix descriptor names.
+//
+// A CTA computes one tile: 128 * MT features by BN tokens over one part of k
+// (grid.z parts; each part writes its own float partial sum, added by whoever
+// reads the product next, in a fixed order).  Warp 0 issues the TMA loads,
+// warp 1 owns the tensor memory and issues the MMAs, warps 2..5 read the
+// accumulator back (one thread per feature) and store.  With EPI_SWIGLU the two
+// weight tiles are the gate rows and the up rows of the same features and the
+// epilogue writes SiLU(gate) * up in bfloat16.
+//
+// Every wait on an mbarrier has a time limit; when it runs out the CTA records
+// it in an error word that the host reads (jb_gemm_tc_error), stops issuing
+// work, waits once more (with the same limit) for the loads it has in flight,
+// frees its tensor memory and returns.  No load uses cluster multicast.
+//
+// The reference has no counterpart: its products are quantized dot products on
+// CPU threads or dp4a (src/llm/cuda/matvec.cu:344-414).
+#include <cuda.h>
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace jb {
+
+constexpr int BK = 64;              // k per stage: 128 bytes of bfloat16, one swizzle row
+constexpr int TILE_M = 128;         // features per MMA
+constexpr int W_TILE_BYTES = TILE_M * BK * 2;
+constexpr int EPI_PARTIAL = 0;      // store float partial sums
+constexpr int EPI_SWIGLU = 1;       // two tiles: gate and up; store SiLU(gate) * up as bfloat16
+constexpr long long WAIT_CYCLES = 2000000000ll;   // about a second
+
+__device__ int g_gemm_tc_error;     // 0, or the code of the first wait that ran out
+
+// ------------------------------------------------------------------ PTX pieces
+__device__ __forceinline__ uint32_t smem_u32(const void *p)
+{
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+                 : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// Waits for the phase with this parity to complete.  Gives up when another
+// thread of the CTA has given up (*abort) or after WAIT_CYCLES; then it records
+// `code`, raises *abort and returns false.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort,
+                                          int code)
+{
+    if (mbar_try(bar, parity))
+        return true;
+    long long t0 = clock64();
+    for (;;) {
+        if (mbar_try(bar, parity))
+            return true;
+        if (*abort)
+            return false;
+        if (clock64() - t0 > WAIT_CYCLES) {
+            *abort = 1;
+            atomicCAS(&g_gemm_tc_error, 0, code);
+            return false;
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar,
+                                            int x, int y)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
+        : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tc_commit(uint32_t bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                 ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                       uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        "}\n"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, float *v)
+{
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+          "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; i++)
+        v[i] = __uint_as_float(r[i]);
+}
+
+// The shared-memory matrix descriptor of a K-major tile of 128-byte rows in the
+// 128-byte swizzle: start address, leading offset 1 (unused for this layout),
+// 1024 bytes from one group of eight rows to the next, descriptor version 1,
+// layout type 2 (128-byte swizzle); all offsets in units of 16 bytes.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((addr >> 4) & 0x3fff);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+// kind::f16 instruction descriptor: float accumulator (bits 4-5 = 1), bfloat16
+// A and B (bits 7-9 and 10-12 = 1), both K-major, N / 8 at bit 17, M / 16 at 24.
+__host__ __device__ constexpr uint32_t instr_desc(int n)
+{
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) |
+           ((uint32_t)(TILE_M >> 4) << 24);
+}
+
+template <int BN, int MT> struct TileCfg {
+    static constexpr int A_TILE_BYTES = BN * BK * 2;
+    static constexpr int STAGE_BYTES = MT * W_TILE_BYTES + A_TILE_BYTES;
+    // 2 CTAs per SM for the small tiles that stream weights, 1 for the large ones
+    static constexpr int BUDGET = (BN <= 64 && MT == 1) ? 100 * 1024 : 196 * 1024;
+    static constexpr int STAGES = BUDGET / STAGE_BYTES < 2 ? 2 : (BUDGET / STAGE_BYTES > 8 ? 8 : BUDGET / STAGE_BYTES);
+    static constexpr int TMEM_COLS = MT * BN <= 32 ? 32 : MT * BN <= 64 ? 64 : MT * BN <= 128 ? 128 : MT * BN <= 256 ? 256 : 512;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment */ + 256 /* barriers */;
+};
+
+template <int BN, int MT, int EPI>
+__global__ void __launch_bounds__(192)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
+               float *__restrict__ out, bf16 *__restrict__ out_act, int n, int m, int k,
+               int second_off, int kb_per_split)
+{
+    using Cfg = TileCfg<BN, MT>;
+    constexpr int STAGES = Cfg::STAGES;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t *bars = (uint64_t *)(smem + STAGES * Cfg::STAGE_BYTES);
+    // bars[0..STAGES): full; [STAGES..2 STAGES): empty; [2 STAGES]: accumulator ready
+    uint32_t *tmem_slot = (uint32_t *)(bars + 2 * STAGES + 1);
+    volatile int *abort = (volatile int *)(tmem_slot + 1);
+
+    int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int m0 = blockIdx.x * (EPI == EPI_SWIGLU ? TILE_M : TILE_M * MT);
+    int n0 = blockIdx.y * BN;
+    int total_kb = (k + BK - 1) / BK;
+    int kb0 = blockIdx.z * kb_per_split;
+    int nkb = min(kb_per_split, total_kb - kb0);
+
+    uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES),
+             accum = smem_u32(bars + 2 * STAGES);
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, 1);
+        }
+        mbar_init(accum, 1);
+        *abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)Cfg::TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    uint32_t tmem = *tmem_slot;
+
+    if (warp == 0 && lane == 0 && nkb > 0) {
+        // ---------------------------------------------------------- TMA loads
+        uint32_t armed = 0, last_parity = 0;
+        for (int i = 0; i < nkb; i++) {
+            int s = i % STAGES;
+            uint32_t ph = (i / STAGES) & 1;
+            if (!mbar_wait(empty0 + 8 * s, ph ^ 1, abort, 1))
+                break;
+            uint32_t dst = smem_u32(smem + s * Cfg::STAGE_BYTES);
+            uint32_t bar = full0 + 8 * s;
+            mbar_expect_tx(bar, Cfg::STAGE_BYTES);
+            int kx = (kb0 + i) * BK;
+#pragma unroll
+            for (int t = 0; t < MT; t++)
+                tma_load_2d(dst + t * W_TILE_BYTES, &map_w, bar, kx, m0 + t * second_off);
+            tma_load_2d(dst + MT * W_TILE_BYTES, &map_a, bar, kx, n0);
+            armed |= 1u << s;
+            last_parity = (last_parity & ~(1u << s)) | (ph << s);
+        }
+        if (*abort) {
+            // the loads in flight: wait for each stage armed last, once, with the limit
+            volatile int never = 0;
+            for (int s = 0; s < STAGES; s++)
+                if (armed & (1u << s))
+                    mbar_wait(full0 + 8 * s, (last_parity >> s) & 1, &never, 4);
+        }
+    } else if (warp == 1 && lane == 0 && nkb > 0) {
+        // --------------------------------------------------------------- MMAs
+        constexpr uint32_t idesc = instr_desc(BN);
+        bool ok = true;
+        for (int i = 0; i < nkb && ok; i++) {
+            int s = i % STAGES;
+            uint32_t ph = (i / STAGES) & 1;
+            ok = mbar_wait(full0 + 8 * s, ph, abort, 2);
+            if (!ok)
+                break;
+            tc_fence_after();
+            uint32_t base = smem_u32(smem + s * Cfg::STAGE_BYTES);
+            uint64_t da = smem_desc(base + MT * W_TILE_BYTES);
+#pragma unroll
+            for (int t = 0; t < MT; t++) {
+                uint64_t dw = smem_desc(base + t * W_TILE_BYTES);
+#pragma unroll
+                for (int kk = 0; kk < BK / 16; kk++)
+                    tc_mma(tmem + t * BN, dw + 2 * kk, da + 2 * kk, idesc, (i | kk) != 0);
+            }
+            tc_commit(empty0 + 8 * s);
+        }
+        tc_commit(accum);
+    } else if (warp >= 2) {
+        // ------------------------------------------------------------ epilogue
+        int q = warp & 3;                       // the TMEM lanes this warp may read
+        int f = m0 + q * 32 + lane;             // this thread's feature (of tile 0)
+        bool ok = nkb > 0 && mbar_wait(accum, 0, abort, 3);
+        ok = __all_sync(0xffffffffu, ok);   // the TMEM loads below are warp-wide
+        tc_fence_after();
+        uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16);
+        if (EPI == EPI_PARTIAL) {
+            float *dst = out + (size_t)blockIdx.z * n * m;
+#pragma unroll 1
+            for (int t = 0; t < MT; t++) {
+                int ft = f + t * second_off;
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 16) {
+                    float v[16];
+                    if (ok)
+                        tc_ld16(taddr + t * BN + c0, v);
+                    if (!ok) {
+#pragma unroll
+                        for (int j = 0; j < 16; j++)
+                            v[j] = 0.0f;
+                    }
+                    if (ft < m) {
+#pragma unroll
+                        for (int j = 0; j < 16; j++) {
+                            int tok = n0 + c0 + j;
+                            if (tok < n)
+                                dst[(size_t)tok * m + ft] = v[j];
+                        }
+                    }
+                }
+            }
+        } else {
+            int ff = second_off;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                float g[16], u[16];
+                if (ok) {
+                    tc_ld16(taddr + c0, g);
+                    tc_ld16(taddr + BN + c0, u);
+                }
+                if (ok && f < ff) {
+#pragma unroll
+                    for (int j = 0; j < 16; j++) {
+                        int tok = n0 + c0 + j;
+                        if (tok < n) {
+                            float h = g[j] / (1.0f + expf(-g[j])) * u[j];
+                            out_act[(size_t)tok * ff + f] = __float2bfloat16_rn(h);
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;"
+                     ::"r"(tmem), "r"((uint32_t)Cfg::TMEM_COLS) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiled)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiled encode_fn()
+{
+    static EncodeTiled fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) ==
+                cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiled)p;
+    });
+    return fn;
+}
+
+// A [rows, k] bfloat16 row-major matrix, read in boxes of box_rows x 64 with the
+// 128-byte swizzle; what lies outside the matrix reads as zero.
+static bool tensor_map(const void *ptr, int rows, int k, int box_rows, CUtensorMap *out)
+{
+    typedef std::tuple<const void *, int, int, int> Key;
+    static std::map<Key, CUtensorMap> cache;
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lock(mu);
+    Key key(ptr, rows, k, box_rows);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+        *out = it->second;
+        return true;
+    }
+    EncodeTiled enc = encode_fn();
+    if (!enc)
+        return false;
+    cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)k * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUtensorMap map;
+    if (enc(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(ptr), dims, strides, box,
+            estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return false;
+    if (cache.size() > 8192)
+        cache.clear();
+    cache[key] = map;
+    *out = map;
+    return true;
+}
+
+template <int BN, int MT, int EPI>
+static int launch_tc(const void *A, const void *W, float *out, bf16 *out_act, int n, int m, int k,
+                     int w_rows, int second_off, int splits, cudaStream_t st)
+{
+    using Cfg = TileCfg<BN, MT>;
+    CUtensorMap map_w, map_a;
+    if (!tensor_map(W, w_rows, k, TILE_M, &map_w) || !tensor_map(A, n, k, BN, &map_a))
+        return JB_EINVAL;
+    auto kern = gemm_tc_kernel<BN, MT, EPI>;
+    static bool attr_set = false;
+    if (!attr_set) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 Cfg::SMEM_BYTES) != cudaSuccess)
+            return JB_ELAUNCH;
+        attr_set = true;
+    }
+    int total_kb = (k + BK - 1) / BK;
+    int kbps = (total_kb + splits - 1) / splits;
+    if ((splits - 1) * kbps >= total_kb)
+        return JB_EINVAL;   // a part without work
+    int feats = EPI == EPI_SWIGLU ? second_off : m;
+    int tile_feats = EPI == EPI_SWIGLU ? TILE_M : TILE_M * MT;
+    dim3 grid((feats + tile_feats - 1) / tile_feats, (n + BN - 1) / BN, splits);
+    if (grid.y > 65535 || grid.z > 65535)
+        return JB_EINVAL;
+    kern<<<grid, 192, Cfg::SMEM_BYTES, st>>>(map_w, map_a, out, out_act, n, m, k, second_off, kbps);
+    return launch_status();
+}
+
+}  // namespace jb
+
+using namespace jb;
+
+// Whether the tensor-core product takes this shape: bfloat16 rows whose length
+// is a multiple of 8 (TMA wants 16-byte strides), 16-byte aligned bases.
+extern "C" int jb_gemm_tc_ok(const void *A, const void *W, int n, int m, int k)
+{
+    return n > 0 && m > 0 && k >= 8 && k % 8 == 0 && (uintptr_t)A % 16 == 0 &&
+           (uintptr_t)W % 16 == 0;
+}
+
+// Parts of k that a product of this shape is best cut into (>= 1): enough CTAs
+// to pull weights through every SM when there are few tokens.
+extern "C" int jb_gemm_tc_splits(int n, int m, int k)
+{
+    if (n > 128)
+        return 1;
+    int bn = n <= 16 ? 16 : n <= 32 ? 32 : n <= 64 ? 64 : 128;
+    int tiles = ((m + TILE_M - 1) / TILE_M) * ((n + bn - 1) / bn);
+    int total_kb = (k + BK - 1) / BK;
+    int want = (296 + tiles / 2) / tiles;
+    int most = total_kb / 4;
+    int s = want < 1 ? 1 : want;
+    if (s > most)
+        s = most < 1 ? 1 : most;
+    if (s > 16)
+        s = 16;
+    int kbps = (total_kb + s - 1) / s;
+    return (total_kb + kbps - 1) / kbps;
+}
+
+// out: [splits, n, m] float partial sums of A[n, k] . W[m, k]^T.
+extern "C" int jb_gemm_tc(const void *A, const void *W, float *out, int n, int m, int k, int splits,
+                          cudaStream_t st)
+{
+    if (!jb_gemm_tc_ok(A, W, n, m, k) || splits < 1)
+        return JB_EINVAL;
+    if (n > 128) {
+        if (splits != 1)
+            return JB_EINVAL;
+        return launch_tc<256, 2, EPI_PARTIAL>(A, W, out, nullptr, n, m, k, m, TILE_M, 1, st);
+    }
+    if (n <= 16)
+        return launch_tc<16, 1, EPI_PARTIAL>(A, W, out, nullptr, n, m, k, m, TILE_M, splits, st);
+    if (n <= 32)
+        return launch_tc<32, 1, EPI_PARTIAL>(A, W, out, nullptr, n, m, k, m, TILE_M, splits, st);
+    if (n <= 64)
+        return launch_tc<64, 1, EPI_PARTIAL>(A, W, out, nullptr, n, m, k, m, TILE_M, splits, st);
+    return launch_tc<128, 1, EPI_PARTIAL>(A, W, out, nullptr, n, m, k, m, TILE_M, splits, st);
+}
+
+// W: [2 ff, k], rows [0, ff) the gate and [ff, 2 ff) the up projection.
+// out_act[n, ff] = SiLU(A . gate^T) * (A . up^T) in bfloat16.
+extern "C" int jb_gemm_tc_swiglu(const void *A, const void *W, void *out_act, int n, int ff, int k,
+                                 cudaStream_t st)
+{
+    if (!jb_gemm_tc_ok(A, W, n, 2 * ff, k))
+        return JB_EINVAL;
+    if (n > 128)
+        return launch_tc<256, 2, EPI_SWIGLU>(A, W, nullptr, (bf16 *)out_act, n, 2 * ff, k, 2 * ff,
+                                             ff, 1, st);
+    return launch_tc<128, 2, EPI_SWIGLU>(A, W, nullptr, (bf16 *)out_act, n, 2 * ff, k, 2 * ff, ff,
+                                         1, st);
+}
+
+// Reads and clears the error word: 0, or which wait ran out first (1: a free
+// stage, 2: a loaded stage, 3: the accumulator, 4: a load in flight).
+// Synchronizes the device.
+extern "C" int jb_gemm_tc_error(void)
+{
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_gemm_tc_error, sizeof v) != cudaSuccess)
+        return JB_ELAUNCH;
+    if (v != 0)
+        cudaMemcpyToSymbol(g_gemm_tc_error, &zero, sizeof zero);
+    return v;
+}

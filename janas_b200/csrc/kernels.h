@@ -40,6 +40,13 @@ int jb_attention(const void *q, const void *k_cache, const void *v_cache, int dt
                  int hd, int window, float scale, int max_chunks, cudaStream_t st);
 int jb_gemm_simt(const void *A, int a_dt, const void *W, int w_dt, float *out, int n, int m, int k,
                  cudaStream_t st);
+int jb_gemm_tc_ok(const void *A, const void *W, int n, int m, int k);
+int jb_gemm_tc_splits(int n, int m, int k);
+int jb_gemm_tc(const void *A, const void *W, float *out, int n, int m, int k, int splits,
+               cudaStream_t st);
+int jb_gemm_tc_swiglu(const void *A, const void *W, void *out_act, int n, int ff, int k,
+                      cudaStream_t st);
+int jb_gemm_tc_error(void);
 int jb_sample_small_cap(void);
 int jb_sample(const float *logits, int rows, int V, const int32_t *row_slot,
               const float *temperature, const int32_t *top_k, const float *top_p,

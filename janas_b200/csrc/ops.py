@@ -264,16 +264,54 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
 
 
 # ------------------------------------------------------------------ products
-def linear(a: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
-    """a [n, k] . weight[m, k]^T as a stack [S, n, m] of float32 partial sums."""
+def _tensor_core_ok(a: torch.Tensor, weight: torch.Tensor) -> bool:
+    if a.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
+        return False
+    return bool(lib().jb_gemm_tc_ok(_p(a), _p(weight), a.shape[0], weight.shape[0], a.shape[1]))
+
+
+def linear(a: torch.Tensor, weight: torch.Tensor, force_simt: bool = False) -> torch.Tensor:
+    """a [n, k] . weight[m, k]^T as a stack [S, n, m] of float32 partial sums.
+
+    bfloat16 operands whose rows are a multiple of 8 long go to the tensor-core
+    kernel (which may cut k into S parts); everything else (float32 on either
+    side, other row lengths) goes to the plain multiply-add kernel, S = 1."""
     _need(a, "activations", _FLOATS, (None, None))
     _need(weight, "weight", _FLOATS, (None, a.shape[1]))
     n, k = a.shape
     m = weight.shape[0]
+    L = lib()
+    if not force_simt and n > 0 and _tensor_core_ok(a, weight):
+        S = int(L.jb_gemm_tc_splits(n, m, k))
+        out = torch.empty((S, n, m), dtype=torch.float32, device=a.device)
+        _check(L.jb_gemm_tc(_p(a), _p(weight), _p(out), n, m, k, S, _stream()), "linear (tcgen05)")
+        return out
     out = torch.empty((1, n, m), dtype=torch.float32, device=a.device)
-    _check(lib().jb_gemm_simt(_p(a), _DT[a.dtype], _p(weight), _DT[weight.dtype], _p(out), n, m,
-                              k, _stream()), "linear")
+    _check(L.jb_gemm_simt(_p(a), _DT[a.dtype], _p(weight), _DT[weight.dtype], _p(out), n, m,
+                          k, _stream()), "linear")
     return out
+
+
+def linear_swiglu(a: torch.Tensor, gate_up: torch.Tensor) -> Optional[torch.Tensor]:
+    """SiLU(a . gate^T) * (a . up^T) in one tensor-core kernel, for bfloat16
+    a [n, k] and gate_up [2 ff, k] (rows [gate | up]); returns bfloat16 [n, ff],
+    or None when the kernel does not take the operands."""
+    _need(a, "activations", _FLOATS, (None, None))
+    _need(gate_up, "gate_up weight", _FLOATS, (None, a.shape[1]))
+    if gate_up.shape[0] % 2 or a.shape[0] == 0 or not _tensor_core_ok(a, gate_up):
+        return None
+    n, k = a.shape
+    ff = gate_up.shape[0] // 2
+    out = torch.empty((n, ff), dtype=torch.bfloat16, device=a.device)
+    _check(lib().jb_gemm_tc_swiglu(_p(a), _p(gate_up), _p(out), n, ff, k, _stream()),
+           "linear_swiglu (tcgen05)")
+    return out
+
+
+def gemm_tc_error() -> int:
+    """0, or which bounded wait of a tensor-core product ran out since the last
+    call (the product's output is then not valid).  Synchronizes the device."""
+    return int(lib().jb_gemm_tc_error())
 
 
 # ------------------------------------------------------------------ sampling

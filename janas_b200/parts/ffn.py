@@ -19,6 +19,8 @@ from .registry import register_feed_forward
 class SwiGLU(FeedForward):
     """params: hidden_size, intermediate_size."""
 
+    FUSED_FROM = 128     # rows above which the fused gate-up-activation kernel is used
+
     def __init__(self, spec, dtype, device):
         super().__init__(spec, dtype, device)
         self.hidden = int(spec.params["hidden_size"])
@@ -41,6 +43,11 @@ class SwiGLU(FeedForward):
         self.w_down = tensors[n(prefix, "down_proj.weight")].contiguous()
 
     def forward(self, ctx: StepContext, h: torch.Tensor) -> torch.Tensor:
-        gu = product(h, self.w_gate_up)
-        act = ops.swiglu(gu, ctx.dtype)
+        act = None
+        if ctx.n_rows > self.FUSED_FROM and ctx.dtype == torch.bfloat16:
+            # enough rows to fill the SMs without cutting k: gate, up and the
+            # activation in one kernel
+            act = ops.linear_swiglu(h, self.w_gate_up)
+        if act is None:
+            act = ops.swiglu(product(h, self.w_gate_up), ctx.dtype)
         return product(act, self.w_down)

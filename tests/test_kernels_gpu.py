@@ -206,6 +206,7 @@ def test_qk_norm_rope_append(dtype):
     written = torch.zeros(6, 64, dtype=torch.bool)
     for r in range(n):
         written[bt[seq[r], pos[r] // 64], pos[r] % 64] = True
+    kc, vc = kc.permute(0, 2, 1, 3), vc.permute(0, 2, 1, 3)      # [page, position, head, value]
     assert float(kc[~written].abs().sum()) == 0.0 and float(vc[~written].abs().sum()) == 0.0
 
 
@@ -253,3 +254,70 @@ def test_sampling_kernel_equals_the_plain_sampler(V):
                 assert got[r] == tok, (V, (t, k, p, mp), rep, r)
             back = [(int(x) + (1 << 64)) % (1 << 64) for x in state.cpu().tolist()]
             assert [back[int(slot[r])] for r in range(rows)] == seeds
+
+
+TC_SHAPES = [(1, 128, 64), (8, 200, 96), (16, 6144, 2560), (17, 130, 200), (33, 2560, 4096),
+             (64, 384, 64), (100, 331, 80), (129, 300, 128), (300, 200, 2560), (700, 1000, 1096),
+             (3, 151936, 256)]
+
+
+@pytest.mark.parametrize("n,m,k", TC_SHAPES)
+def test_gemm_tensor_core(n, m, k):
+    """The tcgen05 product against a double-precision product, at every tile
+    shape (tokens 1 .. 700), with rows and features that fill no tile and k that
+    is no multiple of 64, and with k cut into parts."""
+    a, w = rnd(n, k, dtype=torch.bfloat16), rnd(m, k, dtype=torch.bfloat16, seed=3)
+    want = (a.double() @ w.double().T).float()
+    o = ops()
+    got = o.linear(a.to(DEV), w.to(DEV))
+    assert o.gemm_tc_error() == 0
+    assert got.shape[1:] == (n, m)
+    S = got.shape[0]
+    assert S == o.lib().jb_gemm_tc_splits(n, m, k)
+    if n <= 128 and m <= 6144 and k >= 2048:
+        assert S > 1                      # few tokens, long rows: k is cut
+    got = got.double().sum(0).float().cpu()
+    assert (got - want).abs().max() <= 2e-6 * math.sqrt(k) * max(1.0, want.abs().max())
+    # and the plain kernel agrees with it
+    simt = o.linear(a.to(DEV), w.to(DEV), force_simt=True)[0].cpu()
+    assert (got - simt).abs().max() <= 2e-6 * math.sqrt(k) * max(1.0, want.abs().max())
+
+
+def test_gemm_tensor_core_finds_one_large_product():
+    """A single large entry far along k, in the last rows and features: it lands
+    in the right place of the output and nowhere else."""
+    n, m, k = 300, 260, 1096
+    a = torch.zeros(n, k, dtype=torch.bfloat16)
+    w = torch.zeros(m, k, dtype=torch.bfloat16)
+    a[299, 1090] = 3.0
+    w[259, 1090] = 5.0
+    a[7, 3] = 2.0
+    w[128, 3] = -4.0
+    got = ops().linear(a.to(DEV), w.to(DEV)).sum(0).cpu()
+    want = torch.zeros(n, m)
+    want[299, 259] = 15.0
+    want[7, 128] = -8.0
+    assert torch.equal(got, want)
+
+
+@pytest.mark.parametrize("n,ff,k", [(5, 100, 64), (128, 224, 96), (129, 136, 80), (600, 300, 2560)])
+def test_gemm_tensor_core_swiglu(n, ff, k):
+    a = rnd(n, k, dtype=torch.bfloat16)
+    w = rnd(2 * ff, k, dtype=torch.bfloat16, seed=5, scale=0.3)
+    got = ops().linear_swiglu(a.to(DEV), w.to(DEV))
+    assert ops().gemm_tc_error() == 0
+    gu = a.double() @ w.double().T
+    g, u = gu[:, :ff], gu[:, ff:]
+    want = (g / (1 + torch.exp(-g)) * u).float()
+    assert got.dtype == torch.bfloat16 and got.shape == (n, ff)
+    assert (got.float().cpu() - want).abs().max() <= 2 ** -8 * want.abs().max()
+
+
+def test_products_that_the_tensor_core_kernel_refuses_go_the_plain_way():
+    o = ops()
+    a, w = rnd(4, 100, dtype=torch.bfloat16), rnd(30, 100, dtype=torch.bfloat16)   # 100 % 8 != 0
+    got = o.linear(a.to(DEV), w.to(DEV))
+    assert got.shape == (1, 4, 30)
+    want = (a.double() @ w.double().T).float()
+    assert (got[0].cpu() - want).abs().max() <= 1e-5 * want.abs().max()
+    assert o.linear_swiglu(a.to(DEV), w.to(DEV)) is None
