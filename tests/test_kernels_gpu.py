@@ -77,7 +77,7 @@ def test_swiglu(odt):
 def test_gemm_simt(adt, wdt, n, m, k):
     a, w = rnd(n, k, dtype=adt), rnd(m, k, dtype=wdt, seed=3)
     want = (a.double() @ w.double().T).float()
-    got = ops().linear(a.to(DEV), w.to(DEV))
+    got = ops().linear(a.to(DEV), w.to(DEV), force_simt=True)
     assert got.shape == (1, n, m)
     assert (got[0].cpu() - want).abs().max() <= 1e-6 * math.sqrt(k) * max(1.0, want.abs().max())
 
