@@ -17,8 +17,11 @@
 // scale: :107-118; causal and window limits: :734-739).  Its cut-off of
 // weights below exp(-80) (:574-588) is left out: such a weight is under 2e-35
 // of the largest one and cannot change a float result.
+#include <stdio.h>
+
 #include "common.cuh"
 #include "kernels.h"
+#include "no_alloc.h"
 
 namespace jb {
 
@@ -285,4 +288,64 @@ extern "C" int jb_attention(const void *q, const void *k_cache, const void *v_ca
                                      bt_stride, scratch, (bf16 *)out, row0, n_rows, nh, nkv, hd,
                                      window, scale, max_chunks, st);
     return JB_EINVAL;
+}
+
+// ------------------------------------------------------ without any allocation
+// See no_alloc.h.  The partial results of jb_attention_noalloc() live here.  In
+// host code this name is only a stand-in for the array: the device address is
+// looked up once per device below and handed to the kernels.
+static __device__ __align__(256) float g_noalloc_scratch[JB_NOALLOC_SCRATCH_FLOATS];
+
+static thread_local char t_noalloc_error[160] = "";
+
+extern "C" const char *jb_attention_noalloc_error(void) { return t_noalloc_error; }
+
+extern "C" int jb_attention_noalloc(const void *q, const void *k_cache, const void *v_cache,
+                                    int dt, const int32_t *row_pos, const int32_t *row_seq,
+                                    const int32_t *block_table, int bt_stride, void *out, int row0,
+                                    int n_rows, int nh, int nkv, int hd, int window, float scale,
+                                    int max_chunks, cudaStream_t st)
+{
+    constexpr int MAX_DEVICES = 64;
+    static float *scratch_of[MAX_DEVICES];   // the array's address on each device, once known
+    t_noalloc_error[0] = 0;
+    if (n_rows <= 0)
+        return JB_OK;
+    if (nh <= 0 || hd <= 0 || max_chunks <= 0) {
+        snprintf(t_noalloc_error, sizeof t_noalloc_error, "sizes must be positive");
+        return JB_EINVAL;
+    }
+    long long need = jb_attention_scratch(n_rows, nh, hd, max_chunks);
+    if (need > JB_NOALLOC_SCRATCH_FLOATS) {
+        snprintf(t_noalloc_error, sizeof t_noalloc_error,
+                 "%d rows need %lld floats of scratch, the fixed array has %lld: "
+                 "call with fewer rows", n_rows, need, (long long)JB_NOALLOC_SCRATCH_FLOATS);
+        return JB_ETOOBIG;
+    }
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) {
+        snprintf(t_noalloc_error, sizeof t_noalloc_error, "no current device (or beyond %d)",
+                 MAX_DEVICES);
+        return JB_EDEVICE;
+    }
+    float *scratch = scratch_of[dev];
+    if (scratch == nullptr) {
+        // first call on this device: the device address of the array
+        void *p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+        if (e != cudaSuccess || p == nullptr) {
+            snprintf(t_noalloc_error, sizeof t_noalloc_error,
+                     "cudaGetSymbolAddress failed on device %d: %s", dev, cudaGetErrorString(e));
+            return JB_EDEVICE;
+        }
+        scratch = scratch_of[dev] = (float *)p;
+    }
+    int rc = jb_attention(q, k_cache, v_cache, dt, row_pos, row_seq, block_table, bt_stride,
+                          scratch, out, row0, n_rows, nh, nkv, hd, window, scale, max_chunks, st);
+    if (rc == JB_EINVAL)
+        snprintf(t_noalloc_error, sizeof t_noalloc_error,
+                 "the kernel does not take these sizes or types");
+    else if (rc != JB_OK)
+        snprintf(t_noalloc_error, sizeof t_noalloc_error, "the launch failed");
+    return rc;
 }
