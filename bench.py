@@ -144,16 +144,15 @@ def fill(eng, batch, context, rng):
 
 
 def decode_device_timed(eng, slots, tokens, steps, warmup):
-    """K decode steps of the whole batch timed on the device; the chosen tokens
-    stay on the host side of the step function (they are read back every step,
-    as the step function takes host tokens)."""
+    """K decode steps of the whole batch (the engine's decode step: the step
+    function's kernels and the choice of the next token, replayed from a CUDA
+    graph), timed on the device; the chosen tokens are read back every step."""
     import torch
     from janas_b200.csrc import ops
     from janas_b200.engine import StepEntry
 
     def one(tokens):
-        logits = eng.step([StepEntry(s, [t], [0]) for s, t in zip(slots, tokens)])
-        return ops.sample(logits).cpu().tolist()
+        return eng.decode(slots, tokens).tolist()
 
     for _ in range(warmup):
         tokens = one(tokens)
@@ -201,6 +200,8 @@ def main():
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--no-points", action="store_true", help="skip decoding at batch 1 and 64")
+    ap.add_argument("--only", default="", choices=["", "decode", "prefill"],
+                    help="run one part only and print its time (for profiling; no JSON line)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -228,6 +229,13 @@ def main():
     eng = build_engine(args, args.layers, room * max(big_batch, args.batch), max(big_batch, args.batch))
     cfg = dict(QWEN3_4B)
 
+    if args.only == "decode":
+        slots, toks = fill(eng, args.batch, args.context, rng)
+        ms, launches, _ = decode_device_timed(eng, slots, toks, args.steps, args.warmup)
+        print(f"decode batch {args.batch} context {args.context}: {ms:.4f} ms a step, "
+              f"{launches // args.steps} kernels a step")
+        return 0
+
     # ---- prefill of one prompt
     from janas_b200.engine import StepEntry
     T = args.prefill_tokens
@@ -244,6 +252,9 @@ def main():
         times.append(a.elapsed_time(b))
         eng.free_sequence(s)
     pre_ms = min(times[1:])
+    if args.only == "prefill":
+        print(f"prefill {T} tokens: {pre_ms:.3f} ms")
+        return 0
     flops = prefill_flops(cfg, args.layers, T)
     dense_peak = pk["bf16_tflops"] * 1e12 * (1.0 if args.dtype == "bfloat16" else 1.0)
     prefill = {"value": round(T / (pre_ms / 1e3), 1), "tokens": T, "ms": round(pre_ms, 3),

@@ -19,6 +19,8 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Tuple
 
+import os
+
 import numpy as np
 import torch
 
@@ -71,6 +73,10 @@ class Engine:
         self.max_positions = min(model.spec.max_positions, self.cache.max_tokens)
         model.prepare(self.max_positions)
         self.h2d_bytes = 0       # bytes of step inputs copied to the device so far
+        self.use_graphs = os.environ.get("JANAS_B200_GRAPHS", "1") != "0" and all(
+            getattr(b.mixer, "graph_safe", False) for b in model.blocks)
+        self._graphs: Dict[Tuple[int, int, bool], "DecodeGraph"] = {}
+        self._graph_pool = None
         # run-order entry -> (group, index within the group) of the cache it uses
         self._cache_entry: List[Optional[int]] = []
         for e, entry in enumerate(model.spec.run_order):
@@ -200,3 +206,128 @@ class Engine:
                 lc.k, lc.v, lc.block_table = g.k[i], g.v[i], bt_dev[id(g)]
             out.append(lc)
         return out
+
+    # ---------------------------------------------------------------- decode
+    def decode(self, slots: Sequence[int], tokens: Sequence[int], sampled: bool = False,
+               big=None) -> np.ndarray:
+        """One decode step for sequences that each go on by one token, with the
+        choice of the next token on the device; returns the chosen tokens on the
+        host.  The step's kernels are the step function's; when every mixer allows
+        it they are replayed from a CUDA graph captured for this batch size and
+        context bound, else they are launched one by one."""
+        from ..csrc import ops
+        entries = [StepEntry(s, [int(t)], [0]) for s, t in zip(slots, tokens)]
+        if not self.use_graphs or big is not None:
+            logits = self.step(entries)
+            return self._sample(logits, list(slots), sampled, big)
+        kind, toks, pos0, lens = self.plan(entries)
+        slots = list(slots)
+        self.cache.reserve(slots, lens.tolist())
+        need = int(pos0.max()) + 1
+        bound = 256
+        while bound < need:
+            bound *= 2
+        bound = min(bound, self.max_positions)
+        key = (len(slots), bound, bool(sampled))
+        g = self._graphs.get(key)
+        if g is None:
+            g = self._graphs[key] = DecodeGraph(self, len(slots), bound, bool(sampled))
+        out = g.run(slots, toks, pos0)
+        self.cache.advance(slots, lens.tolist())
+        return out
+
+    def _sample(self, logits: torch.Tensor, slots: List[int], sampled: bool, big) -> np.ndarray:
+        from ..csrc import ops
+        if not sampled:
+            return ops.sample(logits).cpu().numpy()
+        c = self.cache
+        row_slot = torch.tensor(slots, dtype=torch.int32).to(self.device, non_blocking=True)
+        toks = ops.sample(logits, row_slot=row_slot, temperature=c.temperature, top_k=c.top_k,
+                          top_p=c.top_p, min_p=c.min_p, rng=c.rng,
+                          big_keys=None if big is None else big[0],
+                          big_probs=None if big is None else big[1])
+        return toks.cpu().numpy()
+
+
+class DecodeGraph:
+    """The decode step of ``batch`` sequences at positions below ``bound``,
+    captured once and replayed.
+
+    All that changes from step to step (tokens, positions, slots, block tables)
+    lies in one pinned host buffer that the graph copies to the device first; the
+    chosen tokens come back through another pinned buffer.  Launch sizes that
+    depend on the context (the attention's chunk count) are fixed at ``bound``;
+    rows whose range is shorter leave those chunks at once."""
+
+    def __init__(self, engine: "Engine", batch: int, bound: int, sampled: bool):
+        from ..cache.pages import pages_for
+        self.engine, self.batch, self.bound, self.sampled = engine, batch, bound, sampled
+        self.width = (pages_for(bound) + 7) // 8 * 8
+        n_groups = len(engine.cache.groups)
+        total = 4 * batch + n_groups * batch * self.width
+        self.host = torch.zeros(total, dtype=torch.int32).pin_memory()
+        self.host_np = self.host.numpy()
+        self.dev = torch.zeros(total, dtype=torch.int32, device=engine.device)
+        self.out_dev = torch.zeros(batch, dtype=torch.int32, device=engine.device)
+        self.out_host = torch.zeros(batch, dtype=torch.int32).pin_memory()
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+
+    def _launch(self) -> None:
+        from ..csrc import ops
+        eng, B = self.engine, self.batch
+        self.dev.copy_(self.host, non_blocking=True)
+        v = lambda i: self.dev[i * B:(i + 1) * B]
+        bt = {}
+        for gi, g in enumerate(eng.cache.groups):
+            a = 4 * B + gi * B * self.width
+            bt[id(g)] = self.dev[a:a + B * self.width].view(B, self.width)
+        ctx = StepContext(kind=DECODE, dtype=eng.dtype, device=eng.device, n_rows=B, n_seqs=B,
+                          row_pos=v(1), row_seq=v(2), seq_slot_dev=v(3), seq_slots=[],
+                          seq_pos0=None, seq_len=None, seq_row0=None, max_pos=self.bound - 1)
+        logits = eng.model.forward(ctx, v(0), eng._layer_caches(bt), None)
+        c = eng.cache
+        if self.sampled:
+            ops.sample(logits, out=self.out_dev, row_slot=v(3), temperature=c.temperature,
+                       top_k=c.top_k, top_p=c.top_p, min_p=c.min_p, rng=c.rng)
+        else:
+            ops.sample(logits, out=self.out_dev)
+        self.out_host.copy_(self.out_dev, non_blocking=True)
+
+    def run(self, slots: List[int], tokens: np.ndarray, pos0: np.ndarray) -> np.ndarray:
+        eng, B = self.engine, self.batch
+        h = self.host_np
+        h[0:B] = tokens
+        h[B:2 * B] = pos0
+        h[2 * B:3 * B] = np.arange(B, dtype=np.int32)
+        h[3 * B:4 * B] = slots
+        for gi, g in enumerate(eng.cache.groups):
+            a = 4 * B + gi * B * self.width
+            tab = h[a:a + B * self.width].reshape(B, self.width)
+            tab.fill(-1)
+            for i, s in enumerate(slots):
+                pg = g.pages[s]
+                tab[i, :len(pg)] = pg
+        eng.h2d_bytes += self.host.numel() * 4
+        with torch.cuda.device(eng.device):
+            if self.graph is None:
+                # the first step runs eagerly (it sizes every scratch buffer and is a
+                # real step); the capture that follows records without running
+                self._launch()
+                torch.cuda.current_stream().synchronize()
+                out = self.out_host.numpy().copy()
+                graph = torch.cuda.CUDAGraph()
+                if eng._graph_pool is None:
+                    eng._graph_pool = torch.cuda.graph_pool_handle()
+                from ..csrc import ops
+                before = ops.COUNTERS["launches"]
+                with torch.cuda.graph(graph, pool=eng._graph_pool):
+                    self._launch()
+                self.kernels = ops.COUNTERS["launches"] - before   # kernels per replay
+                ops.COUNTERS["launches"] = before
+                self.graph = graph
+                return out
+            self.graph.replay()
+            from ..csrc import ops
+            ops.COUNTERS["launches"] += self.kernels
+            torch.cuda.current_stream().synchronize()
+        return self.out_host.numpy().copy()

@@ -179,29 +179,16 @@ def generate(engine, requests: Sequence[Request], max_batch: int = 64,
             stops = {i: requests[i].options.stop_set() for i in live}
 
             t0 = time.perf_counter()
-            entries = [StepEntry(slots[i], requests[i].prompt, [len(requests[i].prompt) - 1])
-                       for i in live]
             st.prompt_tokens += sum(len(requests[i].prompt) for i in live)
+            logits = engine.step([StepEntry(slots[i], requests[i].prompt,
+                                            [len(requests[i].prompt) - 1]) for i in live])
+            toks, forced = _pick(engine, logits, [slots[i] for i in live], sampled, big)
+            now = time.perf_counter()
+            st.prefill_seconds += now - t0
             active = list(live)
-            first = True
-            while active:
-                logits = engine.step(entries)
-                ts = time.perf_counter()
-                toks, forced = _pick(engine, logits, [slots[i] for i in active], sampled, big)
-                now = time.perf_counter()
-                st.sample_seconds += now - ts
-                if first:
-                    st.prefill_seconds += now - t0
-                    first = False
-                else:
-                    st.passes += 1
-                    st.decode_seconds += now - t0
-                    st.h2d_bytes += getattr(engine, "h2d_bytes", 0) - h2d0
-                    st.d2h_bytes += 4 * len(active)
-                h2d0 = getattr(engine, "h2d_bytes", 0)
-                t0 = now
+            while True:
                 st.forced_tokens += forced
-                nxt, entries = [], []
+                nxt, feed = [], []
                 for i, tok in zip(active, toks):
                     out[i].append(int(tok))
                     st.new_tokens += 1
@@ -209,15 +196,35 @@ def generate(engine, requests: Sequence[Request], max_batch: int = 64,
                                         engine.length(slots[i]), engine.max_positions, stops[i])
                     if why is None:
                         nxt.append(i)
-                        entries.append(StepEntry(slots[i], [int(tok)], [0]))
+                        feed.append(int(tok))
                     else:
                         results[i] = Result(out[i], why)
                         engine.free_sequence(slots.pop(i))
                 active = nxt
+                if not active:
+                    break
+                t0 = time.perf_counter()
+                h2d0 = getattr(engine, "h2d_bytes", 0)
+                toks, forced = _decode(engine, [slots[i] for i in active], feed, sampled, big)
+                st.passes += 1
+                st.decode_seconds += time.perf_counter() - t0
+                st.h2d_bytes += getattr(engine, "h2d_bytes", 0) - h2d0
+                st.d2h_bytes += 4 * len(active)
         finally:
             for s in slots.values():
                 engine.free_sequence(s)
     return results  # type: ignore[return-value]
+
+
+def _decode(engine, slots: List[int], tokens: List[int], sampled: bool, big
+            ) -> Tuple[np.ndarray, int]:
+    """One decode step and the choice of the next tokens; returns them on the
+    host (and how many draws had one candidate only, where that is counted)."""
+    if hasattr(engine, "decode"):
+        return engine.decode(slots, tokens, sampled, big), 0
+    from .engine import StepEntry
+    logits = engine.step([StepEntry(s, [t], [0]) for s, t in zip(slots, tokens)])
+    return _pick(engine, logits, slots, sampled, big)
 
 
 def _pick(engine, logits, slots: List[int], sampled: bool, big) -> Tuple[np.ndarray, int]:

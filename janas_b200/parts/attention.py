@@ -30,6 +30,10 @@ class GQAAttention(Mixer):
     """params: hidden_size, num_heads, num_kv_heads, head_dim, qk_norm_eps (None: no
     q/k norm), window (0: none), position (a PartSpec)."""
 
+    # everything that changes from step to step is read from device arrays, so a
+    # captured decode step can be replayed
+    graph_safe = True
+
     def __init__(self, spec, dtype, device):
         super().__init__(spec, dtype, device)
         p = spec.params

@@ -101,6 +101,11 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    # True when forward() reads everything that changes between decode steps
+    # (positions, slots, block tables) from the context's device arrays only, so
+    # that a captured decode step can be replayed with new contents
+    graph_safe = False
+
     def kv_spec(self) -> Optional[KVSpec]:
         """Keys and values per position that the cache should hold, or None."""
         return None

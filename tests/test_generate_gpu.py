@@ -162,3 +162,26 @@ def test_cli_prints_the_same_tokens(tmp_path):
                         "--ctx", "128", "--stats"], capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stderr
     assert [int(t) for t in r.stdout.split()] == plain.generate(c, w, [5, 17, 3, 200], 6)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_replayed_decode_steps_equal_launched_ones(dtype):
+    """The decode step replayed from a CUDA graph gives the tokens that the same
+    kernels give when launched one by one: greedy and sampled, while sequences
+    end at different times (the batch shrinks) and positions cross pages."""
+    import janas_b200
+    rng = np.random.default_rng(31)
+    v = TINY["C"]["vocab_size"]
+    ps = [tokens(rng, n, v) for n in (60, 3, 250, 17)]
+    news = [40, 12, 30, 70]
+    for opts in (None, [janas_b200.GenOptions(temperature=0.9, top_k=30, top_p=0.9, seed=5 + i)
+                        for i in range(4)]):
+        m = janas_b200.open(model_dir("C"), janas_b200.LLMParams(n_ctx=512, dtype=dtype,
+                                                                max_batch=4, max_tokens=2048))
+        assert m.engine.use_graphs
+        a, _ = m.generate_batch(ps, news, opts)
+        assert len(m.engine._graphs) >= 3            # several batch sizes were captured
+        m.engine.use_graphs = False
+        b, _ = m.generate_batch(ps, news, opts)
+        assert a == b
+        m.engine.cache.check()
