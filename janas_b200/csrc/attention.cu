@@ -204,15 +204,27 @@ __global__ void attn_merge_kernel(const float *__restrict__ part,
     int lo = window > 0 && pos + 1 > window ? pos + 1 - window : 0;
     int n_chunks = pos / ATT_CHUNK - lo / ATT_CHUNK + 1;
     float m = -INFINITY, l = 0.0f, o = 0.0f;
-    for (int ci = 0; ci < n_chunks; ci++) {
-        const float *p = part + part_at((size_t)lrow, nh, h, max_chunks, ci, hd);
-        float mc = p[0], lc = p[1];
-        float oc = d < hd ? p[2 + d] : 0.0f;
-        float mn = fmaxf(m, mc);
-        float a = expf(m - mn), b = expf(mc - mn);
-        l = l * a + lc * b;
-        o = o * a + oc * b;
-        m = mn;
+    // four partials are fetched together and then joined in chunk order
+    for (int c0 = 0; c0 < n_chunks; c0 += 4) {
+        float mc[4], lc[4], oc[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            int ci = min(c0 + u, n_chunks - 1);
+            const float *p = part + part_at((size_t)lrow, nh, h, max_chunks, ci, hd);
+            mc[u] = p[0];
+            lc[u] = p[1];
+            oc[u] = d < hd ? p[2 + d] : 0.0f;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            if (c0 + u >= n_chunks)
+                break;
+            float mn = fmaxf(m, mc[u]);
+            float a = expf(m - mn), b = expf(mc[u] - mn);
+            l = l * a + lc[u] * b;
+            o = o * a + oc[u] * b;
+            m = mn;
+        }
     }
     if (d < hd)
         out[((size_t)row * nh + h) * hd + d] = from_f<T>(o / l);
@@ -288,6 +300,30 @@ extern "C" int jb_attention(const void *q, const void *k_cache, const void *v_ca
                                      bt_stride, scratch, (bf16 *)out, row0, n_rows, nh, nkv, hd,
                                      window, scale, max_chunks, st);
     return JB_EINVAL;
+}
+
+// Joins per-chunk partials that are already in `scratch` (written by
+// jb_attention's first kernel or by the tensor-core decode kernel, same layout)
+// for rows row0 .. row0 + n_rows - 1.
+extern "C" int jb_attention_merge(const float *scratch, const int32_t *row_pos, void *out, int dt,
+                                  int row0, int n_rows, int nh, int hd, int window, int max_chunks,
+                                  cudaStream_t st)
+{
+    if (n_rows <= 0)
+        return JB_OK;
+    if (hd <= 0 || hd > 512 || nh <= 0 || nh > 65535 || max_chunks <= 0)
+        return JB_EINVAL;
+    dim3 grid(n_rows, nh);
+    int threads = (hd + 31) / 32 * 32;
+    if (dt == JB_F32)
+        attn_merge_kernel<float><<<grid, threads, 0, st>>>(scratch, row_pos, (float *)out, row0, nh,
+                                                           hd, window, max_chunks);
+    else if (dt == JB_BF16)
+        attn_merge_kernel<bf16><<<grid, threads, 0, st>>>(scratch, row_pos, (bf16 *)out, row0, nh,
+                                                          hd, window, max_chunks);
+    else
+        return JB_EINVAL;
+    return launch_status();
 }
 
 // ------------------------------------------------------ without any allocation

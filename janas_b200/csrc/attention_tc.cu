@@ -1,0 +1,524 @@
+// Causal grouped-query attention over the paged cache on the tensor cores
+// (tcgen05), for bfloat16 heads of 64 or 128 values.
+//
+// A CTA works for one KV head on a block of 128 rows: the G query heads of the
+// group for R = 128 / G consecutive positions of one sequence (prefill), or the
+// G heads of one decoded token (decode; the other rows of the block are idle).
+// Keys and values come in chunks of 128 positions, two cache pages, straight
+// from the pages into shared memory by TMA.  Per chunk:
+//
+//   S = Q K^T          tcgen05.mma, Q and K K-major, S in tensor memory
+//   softmax            one thread per row: scale, causal and window mask, running
+//                      maximum, exp, sum; P written to shared memory in bfloat16
+//   PV = P V           tcgen05.mma, V read as an MN-major operand as it lies in
+//                      the page ([position][value]), PV in tensor memory
+//
+// Prefill rows keep the running (m, l, o) in registers over all their chunks and
+// write o / l.  Decode rows write one partial (m, l, PV) per chunk to scratch,
+// in the layout of attention.cu, whose merge kernel then joins them in chunk
+// order; that spreads one token's long context over many SMs.
+//
+// Warp 0 issues the TMA loads, warp 1 owns the tensor memory and issues the
+// MMAs, warps 2..5 are the 128 row threads.  Every mbarrier wait has a time
+// limit (see tc_common.cuh); a wait that runs out is recorded in an error word
+// (jb_attn_tc_error) and the CTA winds down.  No load uses cluster multicast.
+//
+// Formulas as in attention.cu (reference: src/llm/attention.c:107-118,574-588,
+// 734-739,870-910).
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#include "kernels.h"
+#include "tc_common.cuh"
+
+namespace jb {
+
+constexpr int AT_ROWS = 128;        // rows of a block (TMEM lanes)
+constexpr int AT_KEYS = 128;        // keys per chunk (= ATT_CHUNK of attention.cu)
+constexpr int AT_STAGES = 2;        // K/V chunks in flight
+constexpr int BLK_BYTES = 128 * 128;  // a 128-row block of 64 bfloat16 columns
+
+__device__ int g_attn_tc_error;
+
+template <int HD> struct AttnCfg {
+    static constexpr int NB = HD / 64;                 // 64-column blocks per head
+    static constexpr int Q_BYTES = NB * BLK_BYTES;
+    static constexpr int P_BYTES = 2 * BLK_BYTES;      // 128 rows x 128 keys
+    static constexpr int KV_STAGE = 2 * NB * BLK_BYTES;  // K and V of one chunk
+    static constexpr int SMEM_BYTES = Q_BYTES + P_BYTES + AT_STAGES * KV_STAGE + 1024 + 256;
+    static constexpr int TMEM_COLS = 256;              // S: 128 columns, PV: HD <= 128
+};
+
+// Byte offset of (row, 16-byte chunk j of the row's 128 bytes) inside a block of
+// 128-byte rows in the 128-byte swizzle.
+__device__ __forceinline__ uint32_t swz(int row, int j)
+{
+    return (uint32_t)(row * 128 + ((j ^ (row & 7)) << 4));
+}
+
+template <int HD, bool DECODE>
+__global__ void __launch_bounds__(192)
+attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+               const __grid_constant__ CUtensorMap map_v, const int32_t *__restrict__ qblk,
+               const int32_t *__restrict__ row_pos, const int32_t *__restrict__ row_seq,
+               const int32_t *__restrict__ block_table, int bt_stride, bf16 *__restrict__ out,
+               float *__restrict__ part, int nh, int nkv, int G, int R, int window, float scale,
+               int max_chunks, int chunks_per_cta, int row0)
+{
+    using Cfg = AttnCfg<HD>;
+    constexpr int NB = Cfg::NB;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t *q_s = smem;
+    uint8_t *p_s = q_s + Cfg::Q_BYTES;
+    uint8_t *kv_s = p_s + Cfg::P_BYTES;
+    uint64_t *bars = (uint64_t *)(kv_s + AT_STAGES * Cfg::KV_STAGE);
+    // bars: 0 q_full | 1,2 kv_full | 3,4 kv_empty | 5 s_full | 6 p_full | 7 o_full | 8 pv_free
+    uint32_t *tmem_slot = (uint32_t *)(bars + 9);
+    volatile int *abort = (volatile int *)(tmem_slot + 1);
+
+    int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int kvh = blockIdx.y;
+
+    // ---- what this CTA works on
+    int q_row, q_count, q_pos, seq, c_first, c_last, lrow = 0;
+    if (DECODE) {
+        lrow = blockIdx.x / ((max_chunks + chunks_per_cta - 1) / chunks_per_cta);
+        int part_i = blockIdx.x % ((max_chunks + chunks_per_cta - 1) / chunks_per_cta);
+        q_row = row0 + lrow;
+        q_count = 1;
+        q_pos = row_pos[q_row];
+        seq = row_seq[q_row];
+        int lo = window > 0 && q_pos + 1 > window ? q_pos + 1 - window : 0;
+        c_first = lo / AT_KEYS + part_i * chunks_per_cta;
+        c_last = min(q_pos / AT_KEYS, c_first + chunks_per_cta - 1);
+    } else {
+        const int32_t *b = qblk + 4 * (gridDim.x - 1 - blockIdx.x);   // long blocks first
+        q_row = b[0];
+        q_count = b[1];
+        q_pos = b[2];
+        seq = b[3];
+        int lo = window > 0 && q_pos + 1 > window ? q_pos + 1 - window : 0;
+        c_first = lo / AT_KEYS;
+        c_last = (q_pos + q_count - 1) / AT_KEYS;
+    }
+    int n_chunks = c_last - c_first + 1;
+    if (n_chunks <= 0)
+        return;                        // nothing to do: before any barrier or tensor memory
+    int c_base = 0;                    // decode: the row's first chunk (index 0 of its partials)
+    if (DECODE) {
+        int lo = window > 0 && q_pos + 1 > window ? q_pos + 1 - window : 0;
+        c_base = lo / AT_KEYS;
+    }
+
+    uint32_t bar0 = smem_u32(bars);
+    auto bar = [&](int i) { return bar0 + 8 * i; };
+    if (threadIdx.x == 0) {
+        mbar_init(bar(0), 1);
+        for (int s = 0; s < AT_STAGES; s++) {
+            mbar_init(bar(1 + s), 1);
+            mbar_init(bar(3 + s), 1);
+        }
+        mbar_init(bar(5), 1);
+        mbar_init(bar(6), AT_ROWS);
+        mbar_init(bar(7), 1);
+        mbar_init(bar(8), AT_ROWS);
+        *abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)Cfg::TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    uint32_t tmem = *tmem_slot;
+    uint32_t tmem_s = tmem, tmem_pv = tmem + AT_KEYS;
+    int *err = &g_attn_tc_error;
+
+    if (warp == 0 && lane == 0) {
+        // ---------------------------------------------------------- TMA loads
+        int rbox = DECODE ? 1 : R;
+        mbar_expect_tx(bar(0), (uint32_t)(rbox * G * HD * 2));
+#pragma unroll
+        for (int b = 0; b < NB; b++)
+            tma_load_3d(smem_u32(q_s + b * BLK_BYTES), &map_q, bar(0), b * 64, kvh * G, q_row);
+        const int32_t *bt = block_table + (size_t)seq * bt_stride;
+        uint32_t armed = 0, last_parity = 0;
+        for (int it = 0; it < n_chunks; it++) {
+            int s = it % AT_STAGES;
+            uint32_t ph = (it / AT_STAGES) & 1;
+            if (!mbar_wait(bar(3 + s), ph ^ 1, abort, err, 1))
+                break;
+            mbar_expect_tx(bar(1 + s), Cfg::KV_STAGE);
+            uint32_t k_dst = smem_u32(kv_s + s * Cfg::KV_STAGE);
+            uint32_t v_dst = k_dst + NB * BLK_BYTES;
+            int c = c_first + it;
+#pragma unroll
+            for (int pg = 0; pg < 2; pg++) {
+                int idx = 2 * c + pg;
+                int page = idx < bt_stride ? bt[idx] : -1;
+                if (page < 0)
+                    page = 0;          // not there: every position of it is masked
+                int y = (page * nkv + kvh) * PAGE;
+#pragma unroll
+                for (int b = 0; b < NB; b++) {
+                    tma_load_2d(k_dst + b * BLK_BYTES + pg * (PAGE * 128), &map_k, bar(1 + s),
+                                b * 64, y);
+                    tma_load_2d(v_dst + b * BLK_BYTES + pg * (PAGE * 128), &map_v, bar(1 + s),
+                                b * 64, y);
+                }
+            }
+            armed |= 1u << s;
+            last_parity = (last_parity & ~(1u << s)) | (ph << s);
+        }
+        if (*abort) {
+            volatile int never = 0;
+            for (int s = 0; s < AT_STAGES; s++)
+                if (armed & (1u << s))
+                    mbar_wait(bar(1 + s), (last_parity >> s) & 1, &never, err, 4);
+        }
+    } else if (warp == 1 && lane == 0) {
+        // --------------------------------------------------------------- MMAs
+        constexpr uint32_t idesc_s = instr_desc_bf16(AT_ROWS, AT_KEYS, false);
+        constexpr uint32_t idesc_pv = instr_desc_bf16(AT_ROWS, HD, true);
+        bool ok = mbar_wait(bar(0), 0, abort, err, 2);
+        uint32_t q_a = smem_u32(q_s), p_a = smem_u32(p_s);
+        for (int it = 0; it < n_chunks && ok; it++) {
+            int s = it % AT_STAGES;
+            uint32_t ph = (it / AT_STAGES) & 1;
+            ok = mbar_wait(bar(1 + s), ph, abort, err, 3);
+            if (!ok)
+                break;
+            tc_fence_after();
+            uint32_t k_a = smem_u32(kv_s + s * Cfg::KV_STAGE);
+            uint32_t v_a = k_a + NB * BLK_BYTES;
+            // S = Q K^T over the head's values, 16 at a time
+#pragma unroll
+            for (int kk = 0; kk < HD / 16; kk++) {
+                uint32_t off = (kk / 4) * BLK_BYTES + (kk % 4) * 32;
+                tc_mma(tmem_s, smem_desc_sw128(q_a + off, 16, 1024),
+                       smem_desc_sw128(k_a + off, 16, 1024), idesc_s, kk != 0);
+            }
+            tc_commit(bar(5));
+            ok = mbar_wait(bar(6), it & 1, abort, err, 5);       // P is in shared memory
+            if (ok && it > 0)
+                ok = mbar_wait(bar(8), (it - 1) & 1, abort, err, 6);   // the last PV was read
+            if (!ok)
+                break;
+            tc_fence_after();
+            // PV = P V over the chunk's keys, 16 at a time; V is MN-major: blocks of 64
+            // values BLK_BYTES apart, groups of eight keys 1024 bytes apart
+#pragma unroll
+            for (int kk = 0; kk < AT_KEYS / 16; kk++) {
+                uint32_t p_off = (kk / 4) * BLK_BYTES + (kk % 4) * 32;
+                tc_mma(tmem_pv, smem_desc_sw128(p_a + p_off, 16, 1024),
+                       smem_desc_sw128(v_a + kk * 16 * 128, BLK_BYTES, 1024), idesc_pv, kk != 0);
+            }
+            tc_commit(bar(7));
+            tc_commit(bar(3 + s));
+        }
+    } else if (warp >= 2) {
+        // ------------------------------------------------------------ row threads
+        int qw = warp & 3;                      // the TMEM lanes this warp may read
+        int r = qw * 32 + lane;                 // this thread's row of the block
+        int j = r / G, g = r - j * G;           // position within the block, head of the group
+        bool live = DECODE ? (r < G) : (j < q_count && j < R);
+        bool warp_live = __any_sync(0xffffffffu, live);
+        int pos = q_pos + j;
+        int lo = window > 0 && pos + 1 > window ? pos + 1 - window : 0;
+        uint32_t lane_addr = (uint32_t)(qw * 32) << 16;
+        const float c2 = scale * 1.4426950408889634f;      // scores in units of log2(e)
+        float m_run = -INFINITY, l_run = 0.0f;
+        float o[DECODE ? 1 : HD];
+        if (!DECODE) {
+#pragma unroll
+            for (int i = 0; i < HD; i++)
+                o[i] = 0.0f;
+        }
+        bool ok = true;
+        for (int it = 0; it < n_chunks; it++) {
+            int c = c_first + it;
+            int t0 = c * AT_KEYS;
+            ok = ok && mbar_wait(bar(5), it & 1, abort, err, 7);
+            ok = __all_sync(0xffffffffu, ok);
+            tc_fence_after();
+            float m_new = m_run, l_chunk = 0.0f, alpha = 1.0f;
+            if (ok && warp_live) {
+                // first pass: the largest visible score of the chunk
+                float mx = -INFINITY;
+#pragma unroll 1
+                for (int cb = 0; cb < AT_KEYS / 32; cb++) {
+                    float sc[32];
+                    tc_ld32(tmem_s + lane_addr + cb * 32, sc);
+#pragma unroll
+                    for (int i = 0; i < 32; i++) {
+                        int t = t0 + cb * 32 + i;
+                        if (live && t <= pos && t >= lo)
+                            mx = fmaxf(mx, sc[i] * c2);
+                    }
+                }
+                m_new = DECODE ? mx : fmaxf(m_run, mx);
+                alpha = (m_run == -INFINITY || DECODE) ? 0.0f : exp2f(m_run - m_new);
+                if (m_new == -INFINITY)
+                    alpha = 1.0f;
+                // second pass: the weights, their sum, and P in bfloat16
+#pragma unroll 1
+                for (int cb = 0; cb < AT_KEYS / 32; cb++) {
+                    float sc[32];
+                    tc_ld32(tmem_s + lane_addr + cb * 32, sc);
+                    uint32_t packed[16];
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        int t = t0 + cb * 32 + i;
+                        float p0 = (live && t <= pos && t >= lo) ? exp2f(sc[i] * c2 - m_new) : 0.0f;
+                        float p1 = (live && t + 1 <= pos && t + 1 >= lo)
+                                       ? exp2f(sc[i + 1] * c2 - m_new) : 0.0f;
+                        l_chunk += p0 + p1;
+                        __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
+                        packed[i / 2] = *reinterpret_cast<uint32_t *>(&pk);
+                    }
+                    // 32 keys = 64 bytes = four 16-byte chunks of this row
+                    uint8_t *blk = p_s + (cb / 2) * BLK_BYTES;
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; q4++) {
+                        uint4 v = make_uint4(packed[4 * q4], packed[4 * q4 + 1],
+                                             packed[4 * q4 + 2], packed[4 * q4 + 3]);
+                        *reinterpret_cast<uint4 *>(blk + swz(r, (cb % 2) * 4 + q4)) = v;
+                    }
+                }
+            } else if (ok) {
+                // an idle warp's rows of P must still be finite: zero them once
+                if (it == 0) {
+#pragma unroll 1
+                    for (int b = 0; b < 2; b++)
+#pragma unroll
+                        for (int q8 = 0; q8 < 8; q8++)
+                            *reinterpret_cast<uint4 *>(p_s + b * BLK_BYTES + swz(r, q8)) =
+                                make_uint4(0, 0, 0, 0);
+                }
+            }
+            fence_async_smem();
+            tc_fence_before();
+            mbar_arrive(bar(6));
+            if (!DECODE) {
+                l_run = l_run * alpha + l_chunk;
+                m_run = m_new;
+            }
+            ok = ok && mbar_wait(bar(7), it & 1, abort, err, 8);
+            ok = __all_sync(0xffffffffu, ok);
+            tc_fence_after();
+            if (ok && warp_live) {
+                if (DECODE) {
+                    float *dst = nullptr;
+                    if (live) {
+                        size_t at = (((size_t)lrow * nh + kvh * G + g) * max_chunks + (c - c_base)) *
+                                    (size_t)(HD + 2);
+                        dst = part + at;
+                        // the merge works with exp(): natural-log units
+                        dst[0] = m_new * 0.6931471805599453f;
+                        dst[1] = l_chunk;
+                    }
+#pragma unroll 1
+                    for (int db = 0; db < HD / 32; db++) {
+                        float pv[32];
+                        tc_ld32(tmem_pv + lane_addr + db * 32, pv);
+                        if (live) {
+#pragma unroll
+                            // a partial is hd + 2 floats long: 8-byte aligned, not 16
+                            for (int i = 0; i < 32; i += 2)
+                                *reinterpret_cast<float2 *>(dst + 2 + db * 32 + i) =
+                                    make_float2(pv[i], pv[i + 1]);
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int db = 0; db < HD / 32; db++) {
+                        float pv[32];
+                        tc_ld32(tmem_pv + lane_addr + db * 32, pv);
+#pragma unroll
+                        for (int i = 0; i < 32; i++)
+                            o[db * 32 + i] = o[db * 32 + i] * alpha + pv[i];
+                    }
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(bar(8));
+        }
+        if (!DECODE && ok && live) {
+            float inv = 1.0f / l_run;
+            bf16 *dst = out + ((size_t)(q_row + j) * nh + kvh * G + g) * HD;
+#pragma unroll
+            for (int i = 0; i < HD; i += 8) {
+                uint32_t w[4];
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    __nv_bfloat162 pk =
+                        __floats2bfloat162_rn(o[i + 2 * e] * inv, o[i + 2 * e + 1] * inv);
+                    w[e] = *reinterpret_cast<uint32_t *>(&pk);
+                }
+                *reinterpret_cast<uint4 *>(dst + i) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;"
+                     ::"r"(tmem), "r"((uint32_t)Cfg::TMEM_COLS) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------ host side
+struct MapKey {
+    const void *ptr;
+    long long d0, d1, d2;
+    int b0, b1, b2;
+    bool operator<(const MapKey &o) const
+    {
+        return std::tie(ptr, d0, d1, d2, b0, b1, b2) <
+               std::tie(o.ptr, o.d0, o.d1, o.d2, o.b0, o.b1, o.b2);
+    }
+};
+
+// A bfloat16 tensor of rank 2 or 3 (dims innermost first, d2 = 0 for rank 2),
+// dense, read in boxes of (64, b1[, b2]) with the 128-byte swizzle.
+static bool attn_tensor_map(const void *ptr, long long d0, long long d1, long long d2, int b1,
+                            int b2, CUtensorMap *out)
+{
+    static std::map<MapKey, CUtensorMap> cache;
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lock(mu);
+    MapKey key{ptr, d0, d1, d2, 64, b1, b2};
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+        *out = it->second;
+        return true;
+    }
+    EncodeTiled enc = tensor_map_encoder();
+    if (!enc)
+        return false;
+    int rank = d2 > 0 ? 3 : 2;
+    cuuint64_t dims[3] = {(cuuint64_t)d0, (cuuint64_t)d1, (cuuint64_t)(d2 > 0 ? d2 : 1)};
+    cuuint64_t strides[2] = {(cuuint64_t)d0 * 2, (cuuint64_t)d0 * d1 * 2};
+    cuuint32_t box[3] = {64, (cuuint32_t)b1, (cuuint32_t)(b2 > 0 ? b2 : 1)};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUtensorMap map;
+    if (enc(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void *>(ptr), dims, strides,
+            box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return false;
+    if (cache.size() > 8192)
+        cache.clear();
+    cache[key] = map;
+    *out = map;
+    return true;
+}
+
+template <int HD, bool DECODE>
+static int launch_attn_tc(const void *q, const void *k_cache, const void *v_cache,
+                          long long n_pages, const int32_t *qblk, int n_blocks,
+                          const int32_t *row_pos, const int32_t *row_seq,
+                          const int32_t *block_table, int bt_stride, void *out, float *part, int n,
+                          int nh, int nkv, int R, int window, float scale, int max_chunks,
+                          int chunks_per_cta, int row0, int n_rows, cudaStream_t st)
+{
+    using Cfg = AttnCfg<HD>;
+    int G = nh / nkv;
+    CUtensorMap mq, mk, mv;
+    if (!attn_tensor_map(q, HD, nh, n, G, DECODE ? 1 : R, &mq) ||
+        !attn_tensor_map(k_cache, HD, n_pages * nkv * PAGE, 0, PAGE, 0, &mk) ||
+        !attn_tensor_map(v_cache, HD, n_pages * nkv * PAGE, 0, PAGE, 0, &mv))
+        return JB_EINVAL;
+    auto kern = attn_tc_kernel<HD, DECODE>;
+    static bool attr_set = false;
+    if (!attr_set) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 Cfg::SMEM_BYTES) != cudaSuccess)
+            return JB_ELAUNCH;
+        attr_set = true;
+    }
+    unsigned gx = DECODE ? (unsigned)n_rows * ((max_chunks + chunks_per_cta - 1) / chunks_per_cta)
+                         : (unsigned)n_blocks;
+    if (gx == 0)
+        return JB_OK;
+    kern<<<dim3(gx, nkv), 192, Cfg::SMEM_BYTES, st>>>(mq, mk, mv, qblk, row_pos, row_seq,
+                                                      block_table, bt_stride, (bf16 *)out, part,
+                                                      nh, nkv, G, R, window, scale, max_chunks,
+                                                      chunks_per_cta, row0);
+    return launch_status();
+}
+
+}  // namespace jb
+
+using namespace jb;
+
+// Whether the tensor-core attention takes these sizes: heads of 64 or 128
+// values, at most 128 query heads per KV head.
+extern "C" int jb_attn_tc_ok(int nh, int nkv, int hd)
+{
+    return nkv > 0 && nh % nkv == 0 && nh / nkv <= AT_ROWS && (hd == 64 || hd == 128) &&
+           nkv <= 65535;
+}
+
+// Positions of one sequence that a prefill block holds: 128 rows / heads per group.
+extern "C" int jb_attn_tc_block_positions(int nh, int nkv)
+{
+    int G = nh / nkv;
+    int R = AT_ROWS / G;
+    return R > 256 ? 256 : R;
+}
+
+// Prefill rows.  q, out: [n, nh, hd] bfloat16; caches [n_pages, nkv, PAGE, hd].
+// qblk: int32 [n_blocks][4] = first row, positions (<= block positions), the
+// first row's position, the sequence's index in block_table.
+extern "C" int jb_attn_tc_prefill(const void *q, const void *k_cache, const void *v_cache,
+                                  long long n_pages, const int32_t *qblk, int n_blocks,
+                                  const int32_t *block_table, int bt_stride, void *out, int n,
+                                  int nh, int nkv, int hd, int window, float scale, cudaStream_t st)
+{
+    if (!jb_attn_tc_ok(nh, nkv, hd) || n <= 0)
+        return JB_EINVAL;
+    int R = jb_attn_tc_block_positions(nh, nkv);
+    if (hd == 128)
+        return launch_attn_tc<128, false>(q, k_cache, v_cache, n_pages, qblk, n_blocks, nullptr,
+                                          nullptr, block_table, bt_stride, out, nullptr, n, nh,
+                                          nkv, R, window, scale, 0, 1, 0, 0, st);
+    return launch_attn_tc<64, false>(q, k_cache, v_cache, n_pages, qblk, n_blocks, nullptr, nullptr,
+                                     block_table, bt_stride, out, nullptr, n, nh, nkv, R, window,
+                                     scale, 0, 1, 0, 0, st);
+}
+
+// Decode rows row0 .. row0 + n_rows - 1 (one token each): writes the per-chunk
+// partials of attention.cu's layout into `part`; jb_attention_merge joins them.
+extern "C" int jb_attn_tc_decode(const void *q, const void *k_cache, const void *v_cache,
+                                 long long n_pages, const int32_t *row_pos, const int32_t *row_seq,
+                                 const int32_t *block_table, int bt_stride, float *part, int n,
+                                 int row0, int n_rows, int nh, int nkv, int hd, int window,
+                                 float scale, int max_chunks, int chunks_per_cta, cudaStream_t st)
+{
+    if (!jb_attn_tc_ok(nh, nkv, hd) || n_rows <= 0 || max_chunks <= 0 || chunks_per_cta <= 0)
+        return JB_EINVAL;
+    if (hd == 128)
+        return launch_attn_tc<128, true>(q, k_cache, v_cache, n_pages, nullptr, 0, row_pos, row_seq,
+                                         block_table, bt_stride, nullptr, part, n, nh, nkv, 0,
+                                         window, scale, max_chunks, chunks_per_cta, row0, n_rows,
+                                         st);
+    return launch_attn_tc<64, true>(q, k_cache, v_cache, n_pages, nullptr, 0, row_pos, row_seq,
+                                    block_table, bt_stride, nullptr, part, n, nh, nkv, 0, window,
+                                    scale, max_chunks, chunks_per_cta, row0, n_rows, st);
+}
+
+extern "C" int jb_attn_tc_error(void)
+{
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_attn_tc_error, sizeof v) != cudaSuccess)
+        return JB_ELAUNCH;
+    if (v != 0)
+        cudaMemcpyToSymbol(g_attn_tc_error, &zero, sizeof zero);
+    return v;
+}

@@ -62,6 +62,23 @@ __device__ __forceinline__ float block_sum(float v, float *red)
     return warp_sum(t);
 }
 
+// p[0] + p[stride] + ... + p[(S - 1) stride], added in that order to `v`.  The
+// loads of four terms are issued together, so the chain of additions does not
+// also become a chain of memory latencies.
+__device__ __forceinline__ float add_partials(float v, const float *__restrict__ p, int S,
+                                              size_t stride)
+{
+    int s = 0;
+    for (; s + 4 <= S; s += 4) {
+        float a = p[(size_t)s * stride], b = p[(size_t)(s + 1) * stride],
+              c = p[(size_t)(s + 2) * stride], d = p[(size_t)(s + 3) * stride];
+        v = (((v + a) + b) + c) + d;
+    }
+    for (; s < S; s++)
+        v += p[(size_t)s * stride];
+    return v;
+}
+
 inline int launch_status()
 {
     return cudaGetLastError() == cudaSuccess ? JB_OK : JB_ELAUNCH;

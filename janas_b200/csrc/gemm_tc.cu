@@ -25,14 +25,12 @@
 //
 // The reference has no counterpart: its products are quantized dot products on
 // CPU threads or dp4a (src/llm/cuda/matvec.cu:344-414).
-#include <cuda.h>
-
 #include <map>
 #include <mutex>
 #include <tuple>
 
-#include "common.cuh"
 #include "kernels.h"
+#include "tc_common.cuh"
 
 namespace jb {
 
@@ -41,111 +39,8 @@ constexpr int TILE_M = 128;         // features per MMA
 constexpr int W_TILE_BYTES = TILE_M * BK * 2;
 constexpr int EPI_PARTIAL = 0;      // store float partial sums
 constexpr int EPI_SWIGLU = 1;       // two tiles: gate and up; store SiLU(gate) * up as bfloat16
-constexpr long long WAIT_CYCLES = 2000000000ll;   // about a second
 
 __device__ int g_gemm_tc_error;     // 0, or the code of the first wait that ran out
-
-// ------------------------------------------------------------------ PTX pieces
-__device__ __forceinline__ uint32_t smem_u32(const void *p)
-{
-    return (uint32_t)__cvta_generic_to_shared(p);
-}
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
-{
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
-{
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
-                 : "memory");
-}
-
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity)
-{
-    uint32_t ok;
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t"
-        "}\n"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-
-// Waits for the phase with this parity to complete.  Gives up when another
-// thread of the CTA has given up (*abort) or after WAIT_CYCLES; then it records
-// `code`, raises *abort and returns false.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort,
-                                          int code)
-{
-    if (mbar_try(bar, parity))
-        return true;
-    long long t0 = clock64();
-    for (;;) {
-        if (mbar_try(bar, parity))
-            return true;
-        if (*abort)
-            return false;
-        if (clock64() - t0 > WAIT_CYCLES) {
-            *abort = 1;
-            atomicCAS(&g_gemm_tc_error, 0, code);
-            return false;
-        }
-    }
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar,
-                                            int x, int y)
-{
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
-        " [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
-        : "memory");
-}
-
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void tc_commit(uint32_t bar)
-{
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
-                 ::"r"(bar) : "memory");
-}
-
-__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
-                                       uint32_t idesc, uint32_t accumulate)
-{
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
-        "}\n"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-
-__device__ __forceinline__ void tc_ld16(uint32_t taddr, float *v)
-{
-    uint32_t r[16];
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
-          "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 16; i++)
-        v[i] = __uint_as_float(r[i]);
-}
 
 // The shared-memory matrix descriptor of a K-major tile of 128-byte rows in the
 // 128-byte swizzle: start address, leading offset 1 (unused for this layout),
@@ -229,7 +124,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         for (int i = 0; i < nkb; i++) {
             int s = i % STAGES;
             uint32_t ph = (i / STAGES) & 1;
-            if (!mbar_wait(empty0 + 8 * s, ph ^ 1, abort, 1))
+            if (!mbar_wait(empty0 + 8 * s, ph ^ 1, abort, &g_gemm_tc_error, 1))
                 break;
             uint32_t dst = smem_u32(smem + s * Cfg::STAGE_BYTES);
             uint32_t bar = full0 + 8 * s;
@@ -247,7 +142,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             volatile int never = 0;
             for (int s = 0; s < STAGES; s++)
                 if (armed & (1u << s))
-                    mbar_wait(full0 + 8 * s, (last_parity >> s) & 1, &never, 4);
+                    mbar_wait(full0 + 8 * s, (last_parity >> s) & 1, &never, &g_gemm_tc_error, 4);
         }
     } else if (warp == 1 && lane == 0 && nkb > 0) {
         // --------------------------------------------------------------- MMAs
@@ -256,7 +151,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         for (int i = 0; i < nkb && ok; i++) {
             int s = i % STAGES;
             uint32_t ph = (i / STAGES) & 1;
-            ok = mbar_wait(full0 + 8 * s, ph, abort, 2);
+            ok = mbar_wait(full0 + 8 * s, ph, abort, &g_gemm_tc_error, 2);
             if (!ok)
                 break;
             tc_fence_after();
@@ -276,7 +171,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         // ------------------------------------------------------------ epilogue
         int q = warp & 3;                       // the TMEM lanes this warp may read
         int f = m0 + q * 32 + lane;             // this thread's feature (of tile 0)
-        bool ok = nkb > 0 && mbar_wait(accum, 0, abort, 3);
+        bool ok = nkb > 0 && mbar_wait(accum, 0, abort, &g_gemm_tc_error, 3);
         ok = __all_sync(0xffffffffu, ok);   // the TMEM loads below are warp-wide
         tc_fence_after();
         uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16);
@@ -337,12 +232,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 }
 
 // ------------------------------------------------------------------ host side
-typedef CUresult (*EncodeTiled)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
-                                const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
-                                const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiled encode_fn()
+EncodeTiled tensor_map_encoder()
 {
     static EncodeTiled fn = nullptr;
     static std::once_flag once;
@@ -370,7 +260,7 @@ static bool tensor_map(const void *ptr, int rows, int k, int box_rows, CUtensorM
         *out = it->second;
         return true;
     }
-    EncodeTiled enc = encode_fn();
+    EncodeTiled enc = tensor_map_encoder();
     if (!enc)
         return false;
     cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};

@@ -38,6 +38,20 @@ int jb_attention(const void *q, const void *k_cache, const void *v_cache, int dt
                  const int32_t *row_pos, const int32_t *row_seq, const int32_t *block_table,
                  int bt_stride, float *scratch, void *out, int row0, int n_rows, int nh, int nkv,
                  int hd, int window, float scale, int max_chunks, cudaStream_t st);
+int jb_attention_merge(const float *scratch, const int32_t *row_pos, void *out, int dt, int row0,
+                       int n_rows, int nh, int hd, int window, int max_chunks, cudaStream_t st);
+int jb_attn_tc_ok(int nh, int nkv, int hd);
+int jb_attn_tc_block_positions(int nh, int nkv);
+int jb_attn_tc_prefill(const void *q, const void *k_cache, const void *v_cache, long long n_pages,
+                       const int32_t *qblk, int n_blocks, const int32_t *block_table,
+                       int bt_stride, void *out, int n, int nh, int nkv, int hd, int window,
+                       float scale, cudaStream_t st);
+int jb_attn_tc_decode(const void *q, const void *k_cache, const void *v_cache, long long n_pages,
+                      const int32_t *row_pos, const int32_t *row_seq, const int32_t *block_table,
+                      int bt_stride, float *part, int n, int row0, int n_rows, int nh, int nkv,
+                      int hd, int window, float scale, int max_chunks, int chunks_per_cta,
+                      cudaStream_t st);
+int jb_attn_tc_error(void);
 int jb_gemm_simt(const void *A, int a_dt, const void *W, int w_dt, float *out, int n, int m, int k,
                  cudaStream_t st);
 int jb_gemm_tc_ok(const void *A, const void *W, int n, int m, int k);

@@ -231,16 +231,40 @@ def _scratch(device: torch.device, floats: int) -> torch.Tensor:
     return buf
 
 
+def attention_block_positions(num_heads: int, num_kv_heads: int) -> int:
+    """Positions of one sequence that a block of the tensor-core prefill kernel holds."""
+    return int(lib().jb_attn_tc_block_positions(num_heads, num_kv_heads))
+
+
+def attention_blocks(seq_row0, seq_pos0, seq_len, positions_per_block: int,
+                     device: torch.device) -> torch.Tensor:
+    """The blocks a prefill step is cut into for the tensor-core kernel: int32
+    [blocks, 4] = first row, positions, the first row's position, sequence."""
+    import numpy as np
+    rows = []
+    for i, (r0, p0, n) in enumerate(zip(seq_row0, seq_pos0, seq_len)):
+        for a in range(0, int(n), positions_per_block):
+            rows.append((int(r0) + a, min(positions_per_block, int(n) - a), int(p0) + a, i))
+    return torch.from_numpy(np.asarray(rows, dtype=np.int32).reshape(-1, 4)).to(device)
+
+
 def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
               row_pos: torch.Tensor, row_seq: torch.Tensor, block_table: torch.Tensor,
-              window: int, scale: float, max_chunks: int) -> torch.Tensor:
+              window: int, scale: float, max_chunks: int, blocks: Optional[torch.Tensor] = None,
+              decode: bool = False, force_simt: bool = False) -> torch.Tensor:
     """Causal GQA attention of every row over its sequence's cache pages.
 
     q: [n, heads, hd]; caches [pages, kv_heads, PAGE, hd] of q's dtype.  Row r
     is at position row_pos[r] of sequence row_seq[r], whose pages are
     block_table[row_seq[r]]; it sees positions max(0, pos + 1 - window) .. pos
     (all of 0 .. pos when window is 0).  max_chunks: the most chunks of
-    ``attention_chunk()`` positions that any row's range touches."""
+    ``attention_chunk()`` positions that any row's range touches.
+
+    bfloat16 heads of 64 or 128 values run on the tensor cores when the caller
+    says how the rows are arranged: ``decode=True`` (every row is the one new
+    token of its sequence) or ``blocks`` (from ``attention_blocks``: runs of
+    consecutive positions of one sequence).  Everything else, and float32, runs on
+    the plain kernel."""
     _need(q, "q", _FLOATS, (None, None, None))
     n, nh, hd = q.shape
     _need(k_cache, "k_cache", q.dtype, (None, None, PAGE, hd))
@@ -251,16 +275,45 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
     _need(block_table, "block_table", torch.int32, (None, None))
     out = torch.empty_like(q)
     L = lib()
+    tc = (not force_simt and q.dtype == torch.bfloat16 and (decode or blocks is not None)
+          and bool(L.jb_attn_tc_ok(nh, nkv, hd)))
+    if tc and not decode:
+        _need(blocks, "blocks", torch.int32, (None, 4))
+        _check(L.jb_attn_tc_prefill(_p(q), _p(k_cache), _p(v_cache),
+                                    ctypes.c_longlong(k_cache.shape[0]), _p(blocks),
+                                    blocks.shape[0], _p(block_table), block_table.shape[1],
+                                    _p(out), n, nh, nkv, hd, window, ctypes.c_float(scale),
+                                    _stream()), "attention (tcgen05, prefill)")
+        return out
     per_row = int(L.jb_attention_scratch(1, nh, hd, max_chunks))
     rows_per_call = max(1, min(n, (_ATT_SCRATCH_BYTES // 4) // max(per_row, 1)))
     scratch = _scratch(q.device, per_row * rows_per_call)
     for row0 in range(0, n, rows_per_call):
         cnt = min(rows_per_call, n - row0)
-        _check(L.jb_attention(_p(q), _p(k_cache), _p(v_cache), _DT[q.dtype], _p(row_pos),
-                              _p(row_seq), _p(block_table), block_table.shape[1], _p(scratch),
-                              _p(out), row0, cnt, nh, nkv, hd, window, ctypes.c_float(scale),
-                              max_chunks, _stream()), "attention", kernels=2)
+        if tc:
+            # enough CTAs to keep every SM streaming keys and values
+            parts = min(max_chunks, max(1, 444 // (cnt * nkv)))
+            per_cta = (max_chunks + parts - 1) // parts
+            _check(L.jb_attn_tc_decode(_p(q), _p(k_cache), _p(v_cache),
+                                       ctypes.c_longlong(k_cache.shape[0]), _p(row_pos),
+                                       _p(row_seq), _p(block_table), block_table.shape[1],
+                                       _p(scratch), n, row0, cnt, nh, nkv, hd, window,
+                                       ctypes.c_float(scale), max_chunks, per_cta, _stream()),
+                   "attention (tcgen05, decode)")
+            _check(L.jb_attention_merge(_p(scratch), _p(row_pos), _p(out), _DT[q.dtype], row0, cnt,
+                                        nh, hd, window, max_chunks, _stream()), "attention merge")
+        else:
+            _check(L.jb_attention(_p(q), _p(k_cache), _p(v_cache), _DT[q.dtype], _p(row_pos),
+                                  _p(row_seq), _p(block_table), block_table.shape[1], _p(scratch),
+                                  _p(out), row0, cnt, nh, nkv, hd, window, ctypes.c_float(scale),
+                                  max_chunks, _stream()), "attention", kernels=2)
     return out
+
+
+def attn_tc_error() -> int:
+    """0, or which bounded wait of a tensor-core attention kernel ran out since
+    the last call.  Synchronizes the device."""
+    return int(lib().jb_attn_tc_error())
 
 
 # ------------------------------------------------------------------ products

@@ -69,10 +69,7 @@ __global__ void qk_norm_rope_append_kernel(
 
     if (hs >= nh + nkv) {  // V: the sum of the partial sums, as it is
         for (int i = lane; i < hd; i += 32) {
-            float v = 0.0f;
-            for (int s = 0; s < S; s++)
-                v += src[(size_t)s * split_stride + i];
-            dst[i] = from_f<TC>(v);
+            dst[i] = from_f<TC>(add_partials(0.0f, src + i, S, split_stride));
         }
         return;
     }
@@ -88,10 +85,8 @@ __global__ void qk_norm_rope_append_kernel(
         int i = lane + 32 * j;
         lo[j] = hi[j] = 0.0f;
         if (i < half) {
-            for (int s = 0; s < S; s++) {
-                lo[j] += src[(size_t)s * split_stride + i];
-                hi[j] += src[(size_t)s * split_stride + i + half];
-            }
+            lo[j] = add_partials(0.0f, src + i, S, split_stride);
+            hi[j] = add_partials(0.0f, src + i + half, S, split_stride);
             ss = fmaf(lo[j], lo[j], ss);
             ss = fmaf(hi[j], hi[j], ss);
         }

@@ -43,8 +43,7 @@ __global__ void rmsnorm_kernel(float *__restrict__ x, const float *__restrict__ 
     for (int i = threadIdx.x; i < dm; i += blockDim.x) {
         float v = xr[i];
         if (delta) {
-            for (int s = 0; s < S; s++)
-                v += delta[(size_t)s * delta_stride + row * dm + i];
+            v = add_partials(v, delta + row * dm + i, S, delta_stride);
             xr[i] = v;
         }
         ss = fmaf(v, v, ss);
@@ -69,12 +68,9 @@ __global__ void swiglu_kernel(const float *__restrict__ gu, int S, size_t stride
         return;
     size_t row = i / ff;
     int c = (int)(i % ff);
-    float g = 0.0f, u = 0.0f;
-    for (int s = 0; s < S; s++) {
-        const float *p = gu + (size_t)s * stride + row * 2 * ff;
-        g += p[c];
-        u += p[ff + c];
-    }
+    const float *p = gu + row * 2 * ff;
+    float g = add_partials(0.0f, p + c, S, stride);
+    float u = add_partials(0.0f, p + ff + c, S, stride);
     float h = g / (1.0f + expf(-g)) * u;
     out[i] = from_f<TO>(h);
 }

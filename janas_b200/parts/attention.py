@@ -20,7 +20,7 @@ from ..cache import KVSpec
 from ..config import ConfigError
 from ..csrc import ops
 from ..weights import MATRIX, NORM, TensorSpec
-from .base import EXTEND, LayerCache, Mixer, StepContext
+from .base import DECODE, EXTEND, LayerCache, Mixer, StepContext
 from .linear import fuse_rows, product
 from .registry import build_part, register_mixer
 
@@ -111,6 +111,17 @@ class GQAAttention(Mixer):
         max_chunks = ctx.max_pos // self.chunk + 1
         if self.window:
             max_chunks = min(max_chunks, (self.window - 1) // self.chunk + 2)
+        decode = ctx.kind == DECODE
+        blocks = None
+        if not decode and ctx.dtype == torch.bfloat16 and self.hd in (64, 128):
+            # runs of consecutive positions, for the tensor-core kernel; the same
+            # for every layer of the step with this grouping of heads
+            per = ops.attention_block_positions(self.nh, self.nkv)
+            blocks = ctx.extras.get(("attention_blocks", per))
+            if blocks is None:
+                blocks = ops.attention_blocks(ctx.seq_row0[:-1], ctx.seq_pos0, ctx.seq_len, per,
+                                              ctx.device)
+                ctx.extras[("attention_blocks", per)] = blocks
         a = ops.attention(q, cache.k, cache.v, ctx.row_pos, ctx.row_seq, cache.block_table,
-                          self.window, self.scale, max_chunks)
+                          self.window, self.scale, max_chunks, blocks=blocks, decode=decode)
         return product(a.view(ctx.n_rows, self.nh * self.hd), self.w_o)

@@ -321,3 +321,118 @@ def test_products_that_the_tensor_core_kernel_refuses_go_the_plain_way():
     want = (a.double() @ w.double().T).float()
     assert (got[0].cpu() - want).abs().max() <= 1e-5 * want.abs().max()
     assert o.linear_swiglu(a.to(DEV), w.to(DEV)) is None
+
+
+def _paged_many(ks, vs, n_pages, seed=0):
+    """Several sequences' keys and values laid out in shuffled pages."""
+    nkv, hd = ks[0].shape[1:]
+    kc = (torch.randn(n_pages, nkv, 64, hd) * 3).to(ks[0].dtype)    # stale finite values elsewhere
+    vc = (torch.randn(n_pages, nkv, 64, hd) * 3).to(ks[0].dtype)
+    order = np.random.default_rng(seed).permutation(n_pages).tolist()
+    need = max((k.shape[0] + 63) // 64 for k in ks)
+    bt = torch.full((len(ks), (need + 7) // 8 * 8), -1, dtype=torch.int32)
+    for i, (k, v) in enumerate(zip(ks, vs)):
+        for p in range((k.shape[0] + 63) // 64):
+            page = order.pop()
+            bt[i, p] = page
+            cnt = min(64, k.shape[0] - 64 * p)
+            kc[page, :, :cnt] = k[64 * p:64 * p + cnt].transpose(0, 1)
+            vc[page, :, :cnt] = v[64 * p:64 * p + cnt].transpose(0, 1)
+    return kc, vc, bt
+
+
+@pytest.mark.parametrize("nh,nkv,hd,window", [(8, 2, 128, 0), (32, 8, 128, 0), (8, 1, 128, 0),
+                                              (6, 2, 64, 0), (5, 1, 128, 70), (4, 4, 64, 200),
+                                              (64, 8, 128, 0), (12, 4, 128, 129)])
+def test_attention_tensor_core_prefill(nh, nkv, hd, window):
+    """Whole prompts of unequal lengths in one call, and tokens appended to
+    sequences that already hold some, on the tensor-core kernel."""
+    o = ops()
+    lens, pos0 = [300, 1, 129, 64, 40], [0, 0, 0, 0, 170]     # the last one goes on from 170
+    qs, ks, vs = [], [], []
+    for i, (n, p0) in enumerate(zip(lens, pos0)):
+        qs.append(rnd(p0 + n, nh, hd, dtype=torch.bfloat16, seed=10 * i))
+        ks.append(rnd(p0 + n, nkv, hd, dtype=torch.bfloat16, seed=10 * i + 1))
+        vs.append(rnd(p0 + n, nkv, hd, dtype=torch.bfloat16, seed=10 * i + 2))
+    want = torch.cat([plain.attention(q.float(), k.float(), v.float(), window)[p0:]
+                      for q, k, v, p0 in zip(qs, ks, vs, pos0)])
+    q = torch.cat([q[p0:] for q, p0 in zip(qs, pos0)])
+    kc, vc, bt = _paged_many(ks, vs, 20)
+    row_pos = torch.cat([torch.arange(p0, p0 + n) for n, p0 in zip(lens, pos0)]).int()
+    row_seq = torch.cat([torch.full((n,), i) for i, n in enumerate(lens)]).int()
+    row0 = np.concatenate([[0], np.cumsum(lens)])
+    per = o.attention_block_positions(nh, nkv)
+    blocks = o.attention_blocks(row0[:-1], pos0, lens, per, torch.device(DEV))
+    chunk = o.attention_chunk()
+    mc = 299 // chunk + 1
+    got = o.attention(q.to(DEV), kc.to(DEV), vc.to(DEV), row_pos.to(DEV), row_seq.to(DEV),
+                      bt.to(DEV), window, 1 / math.sqrt(hd), mc, blocks=blocks).cpu().float()
+    assert o.attn_tc_error() == 0
+    err = (got - want).abs().max() / want.abs().max()
+    assert err <= 2 ** -7, err           # P and the output are bfloat16
+    simt = o.attention(q.to(DEV), kc.to(DEV), vc.to(DEV), row_pos.to(DEV), row_seq.to(DEV),
+                       bt.to(DEV), window, 1 / math.sqrt(hd), mc, force_simt=True).cpu().float()
+    assert (got - simt).abs().max() / want.abs().max() <= 2 ** -7
+
+
+@pytest.mark.parametrize("nh,nkv,hd,window", [(32, 8, 128, 0), (8, 1, 128, 0), (6, 2, 64, 0),
+                                              (5, 1, 128, 70), (64, 8, 128, 300)])
+def test_attention_tensor_core_decode(nh, nkv, hd, window):
+    """One new token for each of several sequences of very different lengths."""
+    o = ops()
+    lens = [1, 64, 65, 128, 129, 700, 2050, 333]
+    qs, ks, vs = [], [], []
+    for i, n in enumerate(lens):
+        qs.append(rnd(n, nh, hd, dtype=torch.bfloat16, seed=7 * i))
+        ks.append(rnd(n, nkv, hd, dtype=torch.bfloat16, seed=7 * i + 1))
+        vs.append(rnd(n, nkv, hd, dtype=torch.bfloat16, seed=7 * i + 2))
+    want = torch.stack([plain.attention(q.float(), k.float(), v.float(), window)[-1]
+                        for q, k, v in zip(qs, ks, vs)])
+    q = torch.stack([q[-1] for q in qs])
+    kc, vc, bt = _paged_many(ks, vs, 70, seed=3)
+    row_pos = torch.tensor([n - 1 for n in lens], dtype=torch.int32)
+    row_seq = torch.arange(len(lens), dtype=torch.int32)
+    chunk = o.attention_chunk()
+    for mc in (2049 // chunk + 1, 4096 // chunk):          # exact, and a looser bound
+        got = o.attention(q.to(DEV), kc.to(DEV), vc.to(DEV), row_pos.to(DEV), row_seq.to(DEV),
+                          bt.to(DEV), window, 1 / math.sqrt(hd), mc, decode=True).cpu().float()
+        assert o.attn_tc_error() == 0
+        err = (got - want).abs().max() / want.abs().max()
+        assert err <= 2 ** -7, (mc, err)
+
+
+def test_attention_tensor_core_finds_a_far_key():
+    """As for the plain kernel: one key among 700 stands out, with and without a
+    window, for prefill rows and for a decoded token."""
+    o = ops()
+    n, nh, nkv, hd = 700, 8, 2, 128
+    q = torch.zeros(n, nh, hd)
+    k = torch.zeros(n, nkv, hd)
+    v = rnd(n, nkv, hd).to(torch.bfloat16).float()
+    q[:, :, 3] = 24.0
+    k[133, :, 3] = 24.0
+    kc, vc, bt = _paged_many([k.bfloat16()], [v.bfloat16()], 12, seed=5)
+    pos = torch.arange(n, dtype=torch.int32)
+    seq = torch.zeros(n, dtype=torch.int32)
+    chunk = o.attention_chunk()
+    per = o.attention_block_positions(nh, nkv)
+    blocks = o.attention_blocks([0], [0], [n], per, torch.device(DEV))
+    for window in (0, 200):
+        mc = (n - 1) // chunk + 1
+        got = o.attention(q.bfloat16().to(DEV), kc.to(DEV), vc.to(DEV), pos.to(DEV), seq.to(DEV),
+                          bt.to(DEV), window, 1 / math.sqrt(hd), mc, blocks=blocks).cpu().float()
+        last_seeing = n - 1 if not window else 133 + window - 1
+        for r in (133, 134, 300, last_seeing):
+            assert (got[r, 5] - v[133, 1]).abs().max() <= 2 ** -7, (window, r)
+        if window:
+            r = last_seeing + 1
+            want = v[r + 1 - window:r + 1, 0].mean(0)
+            assert (got[r, 3] - want).abs().max() <= 2 ** -6, (window, r)
+        assert (got[99, 0] - v[:100, 0].mean(0)).abs().max() <= 2 ** -6
+        # the same rows as decoded tokens
+        for r in (133, last_seeing, last_seeing + 1 if window else 500):
+            one = o.attention(q[r:r + 1].bfloat16().to(DEV), kc.to(DEV), vc.to(DEV),
+                              pos[r:r + 1].to(DEV), seq[:1].to(DEV), bt.to(DEV), window,
+                              1 / math.sqrt(hd), mc, decode=True).cpu().float()
+            assert (one[0] - got[r]).abs().max() <= 2 ** -6, (window, r)
+    assert o.attn_tc_error() == 0
