@@ -75,6 +75,8 @@ attn_partial_kernel(const T *__restrict__ q, const T *__restrict__ k_cache,
                     int hd, int window, float scale, int max_chunks)
 {
     constexpr int KPW = 32 / LPK;
+    pdl_trigger();
+    pdl_wait();
     int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     size_t item = (size_t)blockIdx.x * 4 + warp;
     if (item >= (size_t)n_rows * max_chunks)
@@ -198,6 +200,8 @@ __global__ void attn_merge_kernel(const float *__restrict__ part,
                                   const int32_t *__restrict__ row_pos, T *__restrict__ out,
                                   int row0, int nh, int hd, int window, int max_chunks)
 {
+    pdl_trigger();
+    pdl_wait();
     int lrow = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
     int row = row0 + lrow;
     int pos = row_pos[row];
@@ -243,9 +247,8 @@ static int attention_typed(const T *q, const T *k_cache, const T *v_cache, const
     size_t items = (size_t)n_rows * max_chunks;
     dim3 grid((unsigned)((items + 3) / 4), nkv, (group + ATT_GT - 1) / ATT_GT);
 #define JB_ATT(L)                                                                            \
-    attn_partial_kernel<T, L><<<grid, 128, 0, st>>>(q, k_cache, v_cache, row_pos, row_seq,   \
-                                                    block_table, bt_stride, part, row0, n_rows, \
-                                                    nh, nkv, hd, window, scale, max_chunks)
+    launch(attn_partial_kernel<T, L>, grid, 128, 0, st, q, k_cache, v_cache, row_pos, row_seq, \
+           block_table, bt_stride, part, row0, n_rows, nh, nkv, hd, window, scale, max_chunks)
     switch (lpk) {
     case 1: JB_ATT(1); break;
     case 2: JB_ATT(2); break;
@@ -258,8 +261,8 @@ static int attention_typed(const T *q, const T *k_cache, const T *v_cache, const
 #undef JB_ATT
     if (cudaGetLastError() != cudaSuccess)
         return JB_ELAUNCH;
-    attn_merge_kernel<T><<<dim3(n_rows, nh), (hd + 31) / 32 * 32, 0, st>>>(
-        part, row_pos, out, row0, nh, hd, window, max_chunks);
+    launch(attn_merge_kernel<T>, dim3(n_rows, nh), (hd + 31) / 32 * 32, 0, st, (const float *)part,
+           row_pos, out, row0, nh, hd, window, max_chunks);
     return launch_status();
 }
 
@@ -316,11 +319,11 @@ extern "C" int jb_attention_merge(const float *scratch, const int32_t *row_pos, 
     dim3 grid(n_rows, nh);
     int threads = (hd + 31) / 32 * 32;
     if (dt == JB_F32)
-        attn_merge_kernel<float><<<grid, threads, 0, st>>>(scratch, row_pos, (float *)out, row0, nh,
-                                                           hd, window, max_chunks);
+        launch(attn_merge_kernel<float>, grid, threads, 0, st, scratch, row_pos, (float *)out, row0,
+               nh, hd, window, max_chunks);
     else if (dt == JB_BF16)
-        attn_merge_kernel<bf16><<<grid, threads, 0, st>>>(scratch, row_pos, (bf16 *)out, row0, nh,
-                                                          hd, window, max_chunks);
+        launch(attn_merge_kernel<bf16>, grid, threads, 0, st, scratch, row_pos, (bf16 *)out, row0,
+               nh, hd, window, max_chunks);
     else
         return JB_EINVAL;
     return launch_status();

@@ -138,6 +138,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     uint32_t tmem = *tmem_slot;
     uint32_t tmem_s = tmem, tmem_pv = tmem + AT_KEYS;
     int *err = &g_attn_tc_error;
+    // q, the keys and the values were written by the kernel before this one
+    pdl_trigger();
+    pdl_wait();
 
     if (warp == 0 && lane == 0) {
         // ---------------------------------------------------------- TMA loads
@@ -373,6 +376,260 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     }
 }
 
+// ---------------------------------------------------------------- decode rows
+// One decoded token (G <= 16 query heads of one KV head) against chunks of 128
+// keys, with the keys as the M operand so that all 128 row threads have work:
+//
+//   S^T[key, head] = K Q^T     M = 128 keys, N = 16 (the group's heads, padded)
+//   softmax over the keys      one thread per key; the maximum and the sum go
+//                              through warp shuffles and shared memory
+//   O^T[value, head] = V^T P   M = 128 values (V MN-major as it lies), N = 16
+//
+// One partial (m, l, O) per chunk and head goes to scratch, as in attention.cu.
+constexpr int DQ_N = 16;                 // heads per MMA (N)
+constexpr int DQ_BLK = DQ_N * 128;       // a block of 16 rows of 128 bytes
+constexpr int DQ_STAGES = 3;
+constexpr int DQ_KV_STAGE = 4 * BLK_BYTES;   // K and V of one chunk, 128 values each
+constexpr int DQ_SMEM = 2 * DQ_BLK + 2 * DQ_BLK + DQ_STAGES * DQ_KV_STAGE + 1024 + 1024;
+
+// GP: the group's heads rounded up to a power of two (the row threads' loops).
+template <int GP>
+__global__ void __launch_bounds__(192)
+attn_tc_decode_kernel(const __grid_constant__ CUtensorMap map_q,
+                      const __grid_constant__ CUtensorMap map_k,
+                      const __grid_constant__ CUtensorMap map_v,
+                      const int32_t *__restrict__ row_pos, const int32_t *__restrict__ row_seq,
+                      const int32_t *__restrict__ block_table, int bt_stride,
+                      float *__restrict__ part, int nh, int nkv, int G, int window, float scale,
+                      int max_chunks, int chunks_per_cta, int row0)
+{
+    constexpr int HD = 128;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t *q_s = smem;                       // 2 blocks of [16 heads][64 values]
+    uint8_t *p_s = q_s + 2 * DQ_BLK;           // 2 blocks of [16 heads][64 keys]
+    uint8_t *kv_s = p_s + 2 * DQ_BLK;
+    uint64_t *bars = (uint64_t *)(kv_s + DQ_STAGES * DQ_KV_STAGE);
+    // bars: 0 q_full | 1..3 kv_full | 4..6 kv_empty | 7 s_full | 8 p_full | 9 o_full | 10 pv_free
+    uint32_t *tmem_slot = (uint32_t *)(bars + 11);
+    volatile int *abort = (volatile int *)(tmem_slot + 1);
+    float *red_m = (float *)(tmem_slot + 4);   // [4 warps][16 heads]
+    float *red_l = red_m + 4 * DQ_N;
+
+    int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int kvh = blockIdx.y;
+    int parts = (max_chunks + chunks_per_cta - 1) / chunks_per_cta;
+    int lrow = blockIdx.x / parts, part_i = blockIdx.x % parts;
+    int q_row = row0 + lrow;
+    int q_pos = row_pos[q_row];
+    int seq = row_seq[q_row];
+    int lo = window > 0 && q_pos + 1 > window ? q_pos + 1 - window : 0;
+    int c_base = lo / AT_KEYS;
+    int c_first = c_base + part_i * chunks_per_cta;
+    int c_last = min(q_pos / AT_KEYS, c_first + chunks_per_cta - 1);
+    int n_chunks = c_last - c_first + 1;
+    if (n_chunks <= 0)
+        return;
+
+    uint32_t bar0 = smem_u32(bars);
+    auto bar = [&](int i) { return bar0 + 8 * i; };
+    if (threadIdx.x == 0) {
+        mbar_init(bar(0), 1);
+        for (int s = 0; s < DQ_STAGES; s++) {
+            mbar_init(bar(1 + s), 1);
+            mbar_init(bar(4 + s), 1);
+        }
+        mbar_init(bar(7), 1);
+        mbar_init(bar(8), AT_ROWS);
+        mbar_init(bar(9), 1);
+        mbar_init(bar(10), AT_ROWS);
+        *abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(tmem_slot)), "r"(32u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    uint32_t tmem = *tmem_slot;
+    uint32_t tmem_s = tmem, tmem_pv = tmem + DQ_N;
+    int *err = &g_attn_tc_error;
+    // q, the keys and the values were written by the kernel before this one
+    pdl_trigger();
+    pdl_wait();
+
+    if (warp == 0 && lane == 0) {
+        // ---------------------------------------------------------- TMA loads
+        mbar_expect_tx(bar(0), (uint32_t)(G * HD * 2));
+        tma_load_3d(smem_u32(q_s), &map_q, bar(0), 0, kvh * G, q_row);
+        tma_load_3d(smem_u32(q_s + DQ_BLK), &map_q, bar(0), 64, kvh * G, q_row);
+        const int32_t *bt = block_table + (size_t)seq * bt_stride;
+        uint32_t armed = 0, last_parity = 0;
+        for (int it = 0; it < n_chunks; it++) {
+            int s = it % DQ_STAGES;
+            uint32_t ph = (it / DQ_STAGES) & 1;
+            if (!mbar_wait(bar(4 + s), ph ^ 1, abort, err, 11))
+                break;
+            mbar_expect_tx(bar(1 + s), DQ_KV_STAGE);
+            uint32_t k_dst = smem_u32(kv_s + s * DQ_KV_STAGE);
+            uint32_t v_dst = k_dst + 2 * BLK_BYTES;
+            int c = c_first + it;
+#pragma unroll
+            for (int pg = 0; pg < 2; pg++) {
+                int idx = 2 * c + pg;
+                int page = idx < bt_stride ? bt[idx] : -1;
+                if (page < 0)
+                    page = 0;          // not there: every position of it is masked
+                int y = (page * nkv + kvh) * PAGE;
+#pragma unroll
+                for (int b = 0; b < 2; b++) {
+                    tma_load_2d(k_dst + b * BLK_BYTES + pg * (PAGE * 128), &map_k, bar(1 + s),
+                                b * 64, y);
+                    tma_load_2d(v_dst + b * BLK_BYTES + pg * (PAGE * 128), &map_v, bar(1 + s),
+                                b * 64, y);
+                }
+            }
+            armed |= 1u << s;
+            last_parity = (last_parity & ~(1u << s)) | (ph << s);
+        }
+        if (*abort) {
+            volatile int never = 0;
+            for (int s = 0; s < DQ_STAGES; s++)
+                if (armed & (1u << s))
+                    mbar_wait(bar(1 + s), (last_parity >> s) & 1, &never, err, 14);
+        }
+    } else if (warp == 1 && lane == 0) {
+        // --------------------------------------------------------------- MMAs
+        constexpr uint32_t idesc_s = instr_desc_bf16(AT_KEYS, DQ_N, false, false);
+        constexpr uint32_t idesc_pv = instr_desc_bf16(HD, DQ_N, false, true);
+        bool ok = mbar_wait(bar(0), 0, abort, err, 12);
+        uint32_t q_a = smem_u32(q_s), p_a = smem_u32(p_s);
+        for (int it = 0; it < n_chunks && ok; it++) {
+            int s = it % DQ_STAGES;
+            uint32_t ph = (it / DQ_STAGES) & 1;
+            ok = mbar_wait(bar(1 + s), ph, abort, err, 13);
+            if (!ok)
+                break;
+            tc_fence_after();
+            uint32_t k_a = smem_u32(kv_s + s * DQ_KV_STAGE);
+            uint32_t v_a = k_a + 2 * BLK_BYTES;
+#pragma unroll
+            for (int kk = 0; kk < HD / 16; kk++)
+                tc_mma(tmem_s,
+                       smem_desc_sw128(k_a + (kk / 4) * BLK_BYTES + (kk % 4) * 32, 16, 1024),
+                       smem_desc_sw128(q_a + (kk / 4) * DQ_BLK + (kk % 4) * 32, 16, 1024),
+                       idesc_s, kk != 0);
+            tc_commit(bar(7));
+            ok = mbar_wait(bar(8), it & 1, abort, err, 15);       // P is in shared memory
+            if (ok && it > 0)
+                ok = mbar_wait(bar(10), (it - 1) & 1, abort, err, 16);  // the last O^T was read
+            if (!ok)
+                break;
+            tc_fence_after();
+#pragma unroll
+            for (int kk = 0; kk < AT_KEYS / 16; kk++)
+                tc_mma(tmem_pv, smem_desc_sw128(v_a + kk * 16 * 128, BLK_BYTES, 1024),
+                       smem_desc_sw128(p_a + (kk / 4) * DQ_BLK + (kk % 4) * 32, 16, 1024),
+                       idesc_pv, kk != 0);
+            tc_commit(bar(9));
+            tc_commit(bar(4 + s));
+        }
+    } else if (warp >= 2) {
+        // ---------------------------------------------- key threads / value threads
+        int qw = warp & 3;
+        int r = qw * 32 + lane;                 // this thread's key of the chunk, then its value
+        uint32_t lane_addr = (uint32_t)(qw * 32) << 16;
+        const float c2 = scale * 1.4426950408889634f;
+        bool ok = true;
+        for (int it = 0; it < n_chunks; it++) {
+            int c = c_first + it;
+            int t = c * AT_KEYS + r;
+            bool visible = t <= q_pos && t >= lo;
+            ok = ok && mbar_wait(bar(7), it & 1, abort, err, 17);
+            ok = __all_sync(0xffffffffu, ok);
+            tc_fence_after();
+            float sc[DQ_N], m[GP], l[GP];
+            if (ok)
+                tc_ld16(tmem_s + lane_addr, sc);
+#pragma unroll
+            for (int g = 0; g < GP; g++) {
+                float v = (ok && visible && g < G) ? sc[g] * c2 : -INFINITY;
+                sc[g] = v;
+                m[g] = warp_max(v);
+            }
+            if (lane == 0) {
+#pragma unroll
+                for (int g = 0; g < GP; g++)
+                    red_m[qw * DQ_N + g] = m[g];
+            }
+            named_barrier(1, AT_ROWS);
+#pragma unroll
+            for (int g = 0; g < GP; g++) {
+                float mm = fmaxf(fmaxf(red_m[g], red_m[DQ_N + g]),
+                                 fmaxf(red_m[2 * DQ_N + g], red_m[3 * DQ_N + g]));
+                m[g] = mm;
+                float p = sc[g] == -INFINITY ? 0.0f : exp2f(sc[g] - mm);
+                sc[g] = p;
+                l[g] = warp_sum(p);
+            }
+            if (lane == 0) {
+#pragma unroll
+                for (int g = 0; g < GP; g++)
+                    red_l[qw * DQ_N + g] = l[g];
+            }
+            // P[head][key] in bfloat16: block r / 64, row g, 16-byte chunk (r % 64) / 8
+            {
+                uint8_t *blk = p_s + (r / 64) * DQ_BLK;
+                int j = (r % 64) / 8, e = (r % 8) * 2;
+#pragma unroll
+                for (int g = 0; g < GP; g++)
+                    if (g < G)
+                        *reinterpret_cast<bf16 *>(blk + swz(g, j) + e) = __float2bfloat16_rn(sc[g]);
+            }
+            fence_async_smem();
+            named_barrier(1, AT_ROWS);
+            tc_fence_before();
+            mbar_arrive(bar(8));
+            if (ok && r < G) {
+                float ll = red_l[r] + red_l[DQ_N + r] + red_l[2 * DQ_N + r] + red_l[3 * DQ_N + r];
+                float *dst = part + (((size_t)lrow * nh + kvh * G + r) * max_chunks + (c - c_base)) *
+                                        (size_t)(HD + 2);
+                // m[] is indexed at compile time only: pick this thread's head
+                float mine = -INFINITY;
+#pragma unroll
+                for (int g = 0; g < GP; g++)
+                    mine = g == r ? m[g] : mine;
+                dst[0] = mine * 0.6931471805599453f;    // the merge works in natural-log units
+                dst[1] = ll;
+            }
+            ok = ok && mbar_wait(bar(9), it & 1, abort, err, 18);
+            ok = __all_sync(0xffffffffu, ok);
+            tc_fence_after();
+            if (ok) {
+                float ov[DQ_N];
+                tc_ld16(tmem_pv + lane_addr, ov);
+#pragma unroll
+                for (int g = 0; g < GP; g++)
+                    if (g < G)
+                        part[(((size_t)lrow * nh + kvh * G + g) * max_chunks + (c - c_base)) *
+                                 (size_t)(HD + 2) + 2 + r] = ov[g];
+            }
+            tc_fence_before();
+            mbar_arrive(bar(10));
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;"
+                     ::"r"(tmem), "r"(32u) : "memory");
+    }
+}
+
 // ------------------------------------------------------------------ host side
 struct MapKey {
     const void *ptr;
@@ -446,10 +703,9 @@ static int launch_attn_tc(const void *q, const void *k_cache, const void *v_cach
                          : (unsigned)n_blocks;
     if (gx == 0)
         return JB_OK;
-    kern<<<dim3(gx, nkv), 192, Cfg::SMEM_BYTES, st>>>(mq, mk, mv, qblk, row_pos, row_seq,
-                                                      block_table, bt_stride, (bf16 *)out, part,
-                                                      nh, nkv, G, R, window, scale, max_chunks,
-                                                      chunks_per_cta, row0);
+    launch(kern, dim3(gx, nkv), 192, Cfg::SMEM_BYTES, st, mq, mk, mv, qblk, row_pos, row_seq,
+           block_table, bt_stride, (bf16 *)out, part, nh, nkv, G, R, window, scale, max_chunks,
+           chunks_per_cta, row0);
     return launch_status();
 }
 
@@ -503,6 +759,41 @@ extern "C" int jb_attn_tc_decode(const void *q, const void *k_cache, const void 
 {
     if (!jb_attn_tc_ok(nh, nkv, hd) || n_rows <= 0 || max_chunks <= 0 || chunks_per_cta <= 0)
         return JB_EINVAL;
+    if (hd == 128 && nh / nkv <= DQ_N) {
+        int G = nh / nkv;
+        CUtensorMap mq, mk, mv;
+        if (!attn_tensor_map(q, hd, nh, n, G, 1, &mq) ||
+            !attn_tensor_map(k_cache, hd, n_pages * nkv * PAGE, 0, PAGE, 0, &mk) ||
+            !attn_tensor_map(v_cache, hd, n_pages * nkv * PAGE, 0, PAGE, 0, &mv))
+            return JB_EINVAL;
+        unsigned gx = (unsigned)n_rows * ((max_chunks + chunks_per_cta - 1) / chunks_per_cta);
+#define JB_DQ(GP)                                                                              \
+    do {                                                                                       \
+        static bool attr_set = false;                                                          \
+        if (!attr_set) {                                                                       \
+            if (cudaFuncSetAttribute(attn_tc_decode_kernel<GP>,                                \
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize,              \
+                                     DQ_SMEM) != cudaSuccess)                                  \
+                return JB_ELAUNCH;                                                             \
+            attr_set = true;                                                                   \
+        }                                                                                      \
+        launch(attn_tc_decode_kernel<GP>, dim3(gx, nkv), 192, DQ_SMEM, st,                     \
+               mq, mk, mv, row_pos, row_seq, block_table, bt_stride, part, nh, nkv, G, window, \
+               scale, max_chunks, chunks_per_cta, row0);                                       \
+    } while (0)
+        if (G <= 1)
+            JB_DQ(1);
+        else if (G <= 2)
+            JB_DQ(2);
+        else if (G <= 4)
+            JB_DQ(4);
+        else if (G <= 8)
+            JB_DQ(8);
+        else
+            JB_DQ(16);
+#undef JB_DQ
+        return launch_status();
+    }
     if (hd == 128)
         return launch_attn_tc<128, true>(q, k_cache, v_cache, n_pages, nullptr, 0, row_pos, row_seq,
                                          block_table, bt_stride, nullptr, part, n, nh, nkv, 0,

@@ -79,6 +79,37 @@ __device__ __forceinline__ float add_partials(float v, const float *__restrict__
     return v;
 }
 
+// Programmatic dependent launch.  Every kernel of this library is launched with
+// the attribute that lets its CTAs start while the kernel before it in the
+// stream is still running.  pdl_trigger() (early in a kernel) allows the next
+// kernel's CTAs to be scheduled once all of this kernel's CTAs have started;
+// pdl_wait() blocks until the kernel before this one has completed and its
+// writes are visible.  What a kernel does before pdl_wait() must not touch
+// anything an earlier kernel writes or reads-and-frees: only its own shared and
+// tensor memory and the (immutable) weights.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger()
+{
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                          cudaStream_t st, Args... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}
+
 inline int launch_status()
 {
     return cudaGetLastError() == cudaSuccess ? JB_OK : JB_ELAUNCH;

@@ -51,6 +51,8 @@ gemm_simt_kernel(const TA *__restrict__ A, const TW *__restrict__ W, float *__re
 {
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
+    pdl_trigger();
+    pdl_wait();
     int tid = threadIdx.x;
     int tx = tid % 16, ty = tid / 16;
     size_t n0 = (size_t)blockIdx.y * BM, m0 = (size_t)blockIdx.x * BN;
@@ -119,7 +121,7 @@ extern "C" int jb_gemm_simt(const void *A, int a_dt, const void *W, int w_dt, fl
         return JB_EINVAL;
     bool vec = k % 4 == 0 && ((uintptr_t)A % 16 == 0) && ((uintptr_t)W % 16 == 0);
 #define JB_GEMM(TA, TW)                                                                       \
-    gemm_simt_kernel<TA, TW><<<grid, 256, 0, st>>>((const TA *)A, (const TW *)W, out, n, m, k, vec)
+    launch(gemm_simt_kernel<TA, TW>, grid, 256, 0, st, (const TA *)A, (const TW *)W, out, n, m, k, vec)
     if (a_dt == JB_F32 && w_dt == JB_F32)
         JB_GEMM(float, float);
     else if (a_dt == JB_F32 && w_dt == JB_BF16)

@@ -118,10 +118,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     tc_fence_after();
     uint32_t tmem = *tmem_slot;
 
+    pdl_trigger();
     if (warp == 0 && lane == 0 && nkb > 0) {
         // ---------------------------------------------------------- TMA loads
+        // The weights do not depend on the kernel before this one: their first
+        // stages are on their way before that kernel has finished.  The
+        // activations do: they are loaded after the dependency wait.
         uint32_t armed = 0, last_parity = 0;
-        for (int i = 0; i < nkb; i++) {
+        int pre = min(nkb, STAGES);
+        for (int i = 0; i < pre; i++) {
+            uint32_t dst = smem_u32(smem + i * Cfg::STAGE_BYTES);
+            uint32_t bar = full0 + 8 * i;
+            mbar_expect_tx(bar, Cfg::STAGE_BYTES);
+#pragma unroll
+            for (int t = 0; t < MT; t++)
+                tma_load_2d(dst + t * W_TILE_BYTES, &map_w, bar, (kb0 + i) * BK,
+                            m0 + t * second_off);
+            armed |= 1u << i;
+        }
+        pdl_wait();
+        for (int i = 0; i < pre; i++)
+            tma_load_2d(smem_u32(smem + i * Cfg::STAGE_BYTES) + MT * W_TILE_BYTES, &map_a,
+                        full0 + 8 * i, (kb0 + i) * BK, n0);
+        for (int i = pre; i < nkb; i++) {
             int s = i % STAGES;
             uint32_t ph = (i / STAGES) & 1;
             if (!mbar_wait(empty0 + 8 * s, ph ^ 1, abort, &g_gemm_tc_error, 1))
@@ -171,6 +190,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         // ------------------------------------------------------------ epilogue
         int q = warp & 3;                       // the TMEM lanes this warp may read
         int f = m0 + q * 32 + lane;             // this thread's feature (of tile 0)
+        pdl_wait();                         // no store before the kernel before this one is done
         bool ok = nkb > 0 && mbar_wait(accum, 0, abort, &g_gemm_tc_error, 3);
         ok = __all_sync(0xffffffffu, ok);   // the TMEM loads below are warp-wide
         tc_fence_after();
@@ -304,7 +324,8 @@ static int launch_tc(const void *A, const void *W, float *out, bf16 *out_act, in
     dim3 grid((feats + tile_feats - 1) / tile_feats, (n + BN - 1) / BN, splits);
     if (grid.y > 65535 || grid.z > 65535)
         return JB_EINVAL;
-    kern<<<grid, 192, Cfg::SMEM_BYTES, st>>>(map_w, map_a, out, out_act, n, m, k, second_off, kbps);
+    launch(kern, grid, 192, Cfg::SMEM_BYTES, st, map_w, map_a, out, out_act, n, m, k, second_off,
+           kbps);
     return launch_status();
 }
 
@@ -320,24 +341,31 @@ extern "C" int jb_gemm_tc_ok(const void *A, const void *W, int n, int m, int k)
            (uintptr_t)W % 16 == 0;
 }
 
-// Parts of k that a product of this shape is best cut into (>= 1): enough CTAs
-// to pull weights through every SM when there are few tokens.
+// Parts of k that a product of this shape is best cut into (>= 1).  With few
+// tokens the product is a stream of weights, and what one CTA pulls is limited
+// by the loads it can keep in flight: measured on B200, the products of a
+// decode step run fastest when their CTAs (feature tiles x parts of k) just
+// fill the SMs' 2 x 148 places for this kernel at once, as long as a part
+// keeps at least four 64-wide blocks of k.  More CTAs than places come in waves
+// whose last one straggles, so a product with more tiles than that is not cut.
 extern "C" int jb_gemm_tc_splits(int n, int m, int k)
 {
     if (n > 128)
         return 1;
+    const int PLACES = 2 * 148;
     int bn = n <= 16 ? 16 : n <= 32 ? 32 : n <= 64 ? 64 : 128;
-    int tiles = ((m + TILE_M - 1) / TILE_M) * ((n + bn - 1) / bn);
+    long tiles = (long)((m + TILE_M - 1) / TILE_M) * ((n + bn - 1) / bn);
     int total_kb = (k + BK - 1) / BK;
-    int want = (296 + tiles / 2) / tiles;
-    int most = total_kb / 4;
-    int s = want < 1 ? 1 : want;
-    if (s > most)
-        s = most < 1 ? 1 : most;
-    if (s > 16)
-        s = 16;
-    int kbps = (total_kb + s - 1) / s;
-    return (total_kb + kbps - 1) / kbps;
+    int best = 1;
+    for (int s = 2; s <= 16 && tiles * s <= PLACES; s++) {
+        int kbps = (total_kb + s - 1) / s;
+        if (kbps < 4)
+            break;
+        if ((s - 1) * kbps >= total_kb)
+            continue;                              // a part without work
+        best = s;
+    }
+    return best;
 }
 
 // out: [splits, n, m] float partial sums of A[n, k] . W[m, k]^T.

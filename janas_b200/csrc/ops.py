@@ -291,8 +291,7 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
     for row0 in range(0, n, rows_per_call):
         cnt = min(rows_per_call, n - row0)
         if tc:
-            # enough CTAs to keep every SM streaming keys and values
-            parts = min(max_chunks, max(1, 444 // (cnt * nkv)))
+            parts = _decode_parts(cnt * nkv, max_chunks)
             per_cta = (max_chunks + parts - 1) // parts
             _check(L.jb_attn_tc_decode(_p(q), _p(k_cache), _p(v_cache),
                                        ctypes.c_longlong(k_cache.shape[0]), _p(row_pos),
@@ -310,6 +309,20 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
     return out
 
 
+def _decode_parts(pairs: int, chunks: int, sms: int = 148) -> int:
+    """Into how many CTAs the chunks of one (token, KV head) pair are cut.  A CTA
+    costs about three chunks' time to set up, and CTAs beyond one per SM come in
+    waves: the cut that finishes first by that estimate."""
+    best, best_t = 1, None
+    for parts in range(1, chunks + 1):
+        per_cta = -(-chunks // parts)
+        waves = -(-(pairs * -(-chunks // per_cta)) // sms)
+        t = waves * (3.0 + per_cta)
+        if best_t is None or t < best_t:
+            best, best_t = parts, t
+    return best
+
+
 def attn_tc_error() -> int:
     """0, or which bounded wait of a tensor-core attention kernel ran out since
     the last call.  Synchronizes the device."""
@@ -323,19 +336,25 @@ def _tensor_core_ok(a: torch.Tensor, weight: torch.Tensor) -> bool:
     return bool(lib().jb_gemm_tc_ok(_p(a), _p(weight), a.shape[0], weight.shape[0], a.shape[1]))
 
 
-def linear(a: torch.Tensor, weight: torch.Tensor, force_simt: bool = False) -> torch.Tensor:
+def linear(a: torch.Tensor, weight: torch.Tensor, force_simt: bool = False,
+           whole: bool = False, splits: Optional[int] = None) -> torch.Tensor:
     """a [n, k] . weight[m, k]^T as a stack [S, n, m] of float32 partial sums.
 
     bfloat16 operands whose rows are a multiple of 8 long go to the tensor-core
     kernel (which may cut k into S parts); everything else (float32 on either
-    side, other row lengths) goes to the plain multiply-add kernel, S = 1."""
+    side, other row lengths) goes to the plain multiply-add kernel, S = 1.
+    ``whole=True`` asks for S = 1 in every case (the result itself, not parts).
+
+    The tensor-core kernel starts fetching ``weight`` before the kernel launched
+    just before it has finished; weights must therefore not be the output of that
+    kernel (model weights never are)."""
     _need(a, "activations", _FLOATS, (None, None))
     _need(weight, "weight", _FLOATS, (None, a.shape[1]))
     n, k = a.shape
     m = weight.shape[0]
     L = lib()
     if not force_simt and n > 0 and _tensor_core_ok(a, weight):
-        S = int(L.jb_gemm_tc_splits(n, m, k))
+        S = 1 if whole else int(splits or L.jb_gemm_tc_splits(n, m, k))
         out = torch.empty((S, n, m), dtype=torch.float32, device=a.device)
         _check(L.jb_gemm_tc(_p(a), _p(weight), _p(out), n, m, k, S, _stream()), "linear (tcgen05)")
         return out

@@ -18,6 +18,8 @@ namespace jb {
 __global__ void rope_table_kernel(float *__restrict__ cs, float *__restrict__ sn,
                                   const float *__restrict__ inv_freq, int n_pos, int half)
 {
+    pdl_trigger();
+    pdl_wait();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (size_t)n_pos * half)
         return;
@@ -45,6 +47,8 @@ __global__ void qk_norm_rope_append_kernel(
     TC *__restrict__ q_out, TC *__restrict__ k_cache, TC *__restrict__ v_cache, int n, int nh,
     int nkv, int hd, int table_half)
 {
+    pdl_trigger();
+    pdl_wait();
     int slots = nh + 2 * nkv;
     size_t task = (size_t)blockIdx.x * blockDim.y + threadIdx.y;
     if (task >= (size_t)n * slots)
@@ -132,8 +136,8 @@ extern "C" int jb_rope_table(float *cs, float *sn, const float *inv_freq, int n_
     size_t total = (size_t)n_pos * half;
     if (total == 0)
         return JB_OK;
-    rope_table_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(cs, sn, inv_freq, n_pos,
-                                                                     half);
+    launch(rope_table_kernel, (unsigned)((total + 255) / 256), 256, 0, st, cs, sn, inv_freq, n_pos,
+           half);
     return launch_status();
 }
 
@@ -157,7 +161,7 @@ extern "C" int jb_qk_norm_rope_append(const float *qkv, int S, long long split_s
     unsigned grid = (unsigned)((tasks + 3) / 4);
     int table_half = rot_half;
 #define JB_ROPE(TC, TW)                                                                        \
-    qk_norm_rope_append_kernel<TC, TW><<<grid, block, 0, st>>>(                                \
+    launch(qk_norm_rope_append_kernel<TC, TW>, grid, block, 0, st,                             \
         qkv, S, (size_t)split_stride, (const TW *)q_w, (const TW *)k_w, eps, cs, sn, rot_half, \
         row_pos, row_seq, block_table, bt_stride, (TC *)q_out, (TC *)k_cache, (TC *)v_cache, n, \
         nh, nkv, hd, table_half)

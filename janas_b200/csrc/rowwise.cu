@@ -19,6 +19,8 @@ template <typename TT>
 __global__ void embed_kernel(const TT *__restrict__ table, const int32_t *__restrict__ tokens,
                              float *__restrict__ x, int dm)
 {
+    pdl_trigger();
+    pdl_wait();
     size_t row = blockIdx.x;
     const TT *src = table + (size_t)tokens[row] * dm;
     float *dst = x + row * dm;
@@ -36,6 +38,8 @@ __global__ void rmsnorm_kernel(float *__restrict__ x, const float *__restrict__ 
                                const TW *__restrict__ w, TO *__restrict__ out, int dm, float eps)
 {
     __shared__ float red[32];
+    pdl_trigger();
+    pdl_wait();
     size_t orow = blockIdx.x;
     size_t row = row_idx ? (size_t)row_idx[orow] : orow;
     float *xr = x + row * dm;
@@ -63,6 +67,8 @@ template <typename TO>
 __global__ void swiglu_kernel(const float *__restrict__ gu, int S, size_t stride,
                               TO *__restrict__ out, int ff, size_t total)
 {
+    pdl_trigger();
+    pdl_wait();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total)
         return;
@@ -94,9 +100,9 @@ extern "C" int jb_embed(const void *table, int table_dt, const int32_t *tokens, 
         return JB_OK;
     int threads = norm_threads(dm);
     if (table_dt == JB_F32)
-        embed_kernel<float><<<n, threads, 0, st>>>((const float *)table, tokens, x, dm);
+        launch(embed_kernel<float>, n, threads, 0, st, (const float *)table, tokens, x, dm);
     else if (table_dt == JB_BF16)
-        embed_kernel<bf16><<<n, threads, 0, st>>>((const bf16 *)table, tokens, x, dm);
+        launch(embed_kernel<bf16>, n, threads, 0, st, (const bf16 *)table, tokens, x, dm);
     else
         return JB_EINVAL;
     return launch_status();
@@ -112,8 +118,8 @@ extern "C" int jb_rmsnorm(float *x, const float *delta, int S, long long delta_s
         return JB_EINVAL;
     int threads = norm_threads(dm);
 #define JB_NORM(TW, TO)                                                                       \
-    rmsnorm_kernel<TW, TO><<<n_out, threads, 0, st>>>(x, delta, S, (size_t)delta_stride,      \
-                                                      row_idx, (const TW *)w, (TO *)out, dm, eps)
+    launch(rmsnorm_kernel<TW, TO>, n_out, threads, 0, st, x, delta, S, (size_t)delta_stride,   \
+           row_idx, (const TW *)w, (TO *)out, dm, eps)
     if (out == nullptr)
         JB_NORM(float, float);
     else if (w_dt == JB_F32 && out_dt == JB_F32)
@@ -138,9 +144,9 @@ extern "C" int jb_swiglu(const float *gu, int S, long long stride, void *out, in
         return JB_OK;
     unsigned blocks = (unsigned)((total + 255) / 256);
     if (out_dt == JB_F32)
-        swiglu_kernel<float><<<blocks, 256, 0, st>>>(gu, S, (size_t)stride, (float *)out, ff, total);
+        launch(swiglu_kernel<float>, blocks, 256, 0, st, gu, S, (size_t)stride, (float *)out, ff, total);
     else if (out_dt == JB_BF16)
-        swiglu_kernel<bf16><<<blocks, 256, 0, st>>>(gu, S, (size_t)stride, (bf16 *)out, ff, total);
+        launch(swiglu_kernel<bf16>, blocks, 256, 0, st, gu, S, (size_t)stride, (bf16 *)out, ff, total);
     else
         return JB_EINVAL;
     return launch_status();

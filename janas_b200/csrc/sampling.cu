@@ -76,6 +76,8 @@ sample_kernel(const float *__restrict__ logits, int V, const int32_t *__restrict
     __shared__ float small_probs[SMALL_CAP];
     __shared__ unsigned n_fill, n_elig, sh_prefix, sh_remain;
 
+    pdl_trigger();
+    pdl_wait();
     int row = blockIdx.x, tid = threadIdx.x;
     int lane = tid & 31, warp = tid >> 5;
     const float *lg = logits + (size_t)row * V;
@@ -301,8 +303,7 @@ extern "C" int jb_sample(const float *logits, int rows, int V, const int32_t *ro
         return JB_OK;
     if (V <= 0 || (temperature != nullptr && rng == nullptr))
         return JB_EINVAL;
-    sample_kernel<<<rows, SAMPLE_THREADS, 0, st>>>(logits, V, row_slot, temperature, top_k, top_p,
-                                                   min_p, (uint64_t *)rng, (uint64_t *)big_keys,
-                                                   big_probs, big_cap, out, forced);
+    launch(sample_kernel, rows, SAMPLE_THREADS, 0, st, logits, V, row_slot, temperature, top_k, top_p,
+           min_p, (uint64_t *)rng, (uint64_t *)big_keys, big_probs, big_cap, out, forced);
     return launch_status();
 }

@@ -173,12 +173,20 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr, uint32_t lbo_
 }
 
 // kind::f16 instruction descriptor: float accumulator (bits 4-5 = 1), bfloat16
-// A and B (bits 7-9 and 10-12 = 1), A K-major, B K-major or MN-major (bit 16),
-// N / 8 at bit 17, M / 16 at bit 24.
-__host__ __device__ constexpr uint32_t instr_desc_bf16(int m, int n, bool b_mn_major)
+// A and B (bits 7-9 and 10-12 = 1), A and B each K-major or MN-major (bits 15
+// and 16), N / 8 at bit 17, M / 16 at bit 24.
+__host__ __device__ constexpr uint32_t instr_desc_bf16(int m, int n, bool b_mn_major,
+                                                       bool a_mn_major = false)
 {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) |
-           ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((a_mn_major ? 1u : 0u) << 15) |
+           ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) |
+           ((uint32_t)(m >> 4) << 24);
+}
+
+// A barrier among `count` threads of the CTA (count a multiple of 32), by number.
+__device__ __forceinline__ void named_barrier(int id, int count)
+{
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
 }
 
 // cuTensorMapEncodeTiled, found through the runtime (no link against libcuda).

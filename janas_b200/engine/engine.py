@@ -223,11 +223,10 @@ class Engine:
         kind, toks, pos0, lens = self.plan(entries)
         slots = list(slots)
         self.cache.reserve(slots, lens.tolist())
+        # launch sizes are fixed for positions below ``bound``: a new graph every
+        # 256 positions keeps them close to what the step needs
         need = int(pos0.max()) + 1
-        bound = 256
-        while bound < need:
-            bound *= 2
-        bound = min(bound, self.max_positions)
+        bound = min((need + 255) // 256 * 256, self.max_positions)
         key = (len(slots), bound, bool(sampled))
         g = self._graphs.get(key)
         if g is None:

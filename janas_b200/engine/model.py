@@ -21,7 +21,6 @@ from ..cache import KVSpec, StateSpec
 from ..config import ModelSpec
 from ..csrc import ops
 from ..parts import Block, LayerCache, StepContext, block_class, build_part
-from ..parts.linear import product
 from ..weights import EMBEDDING, MATRIX, TensorSpec
 
 
@@ -137,10 +136,7 @@ class DecoderModel:
         if want_rows is not None and want_rows.numel() == 0:
             return None
         h = self.final_norm.apply(x, ctx.dtype, delta=pending, rows=want_rows)
-        logits = product(h, self.head)
-        if logits.shape[0] != 1:
-            raise RuntimeError("the head's product must not be split")
-        return logits[0]
+        return ops.linear(h, self.head, whole=True)[0]
 
 
 def expected_tensors(spec: ModelSpec) -> Dict[str, TensorSpec]:
