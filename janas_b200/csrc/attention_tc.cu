@@ -46,7 +46,7 @@ template <int HD> struct AttnCfg {
     static constexpr int Q_BYTES = NB * BLK_BYTES;
     static constexpr int P_BYTES = 2 * BLK_BYTES;      // 128 rows x 128 keys
     static constexpr int KV_STAGE = 2 * NB * BLK_BYTES;  // K and V of one chunk
-    static constexpr int SMEM_BYTES = Q_BYTES + P_BYTES + AT_STAGES * KV_STAGE + 1024 + 256;
+    static constexpr int SMEM_BYTES = Q_BYTES + P_BYTES + AT_STAGES * KV_STAGE + 1024 + 2048;
     static constexpr int TMEM_COLS = 256;              // S: 128 columns, PV: HD <= 128
 };
 
@@ -376,6 +376,289 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     }
 }
 
+// --------------------------------------------------------------- prefill rows
+// The block of 128 rows with two threads per row: warps 2..5 take keys 0..63 of
+// a chunk and the first half of the head's values, warps 6..9 keys 64..127 and
+// the second half.  A row's two threads agree on the chunk's maximum through
+// shared memory; each keeps the sum of its own weights, joined at the end.  The
+// scores of a chunk stay in registers between the maximum and the weights, so
+// tensor memory is read once.
+constexpr int PF_THREADS = 320;
+
+__device__ __forceinline__ void tc_ld32_nowait(uint32_t taddr, uint32_t *r)
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+          "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
+          "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
+          "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
+
+__device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+template <int HD>
+__global__ void __launch_bounds__(PF_THREADS)
+attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
+                       const __grid_constant__ CUtensorMap map_k,
+                       const __grid_constant__ CUtensorMap map_v, const int32_t *__restrict__ qblk,
+                       const int32_t *__restrict__ block_table, int bt_stride,
+                       bf16 *__restrict__ out, int nh, int nkv, int G, int R, int window,
+                       float scale)
+{
+    using Cfg = AttnCfg<HD>;
+    constexpr int NB = Cfg::NB;
+    constexpr int HH = HD / 2;                 // values a row thread owns
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t *q_s = smem;
+    uint8_t *p_s = q_s + Cfg::Q_BYTES;
+    uint8_t *kv_s = p_s + Cfg::P_BYTES;
+    uint64_t *bars = (uint64_t *)(kv_s + AT_STAGES * Cfg::KV_STAGE);
+    // bars: 0 q_full | 1,2 kv_full | 3,4 kv_empty | 5 s_full | 6 p_full | 7 o_full | 8 pv_free
+    uint32_t *tmem_slot = (uint32_t *)(bars + 9);
+    volatile int *abort = (volatile int *)(tmem_slot + 1);
+    float *pair = (float *)(tmem_slot + 4);    // [2 halves][128 rows]: what a row's threads swap
+
+    int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int kvh = blockIdx.y;
+    const int32_t *b = qblk + 4 * (gridDim.x - 1 - blockIdx.x);   // long blocks first
+    int q_row = b[0], q_count = b[1], q_pos = b[2], seq = b[3];
+    int lo0 = window > 0 && q_pos + 1 > window ? q_pos + 1 - window : 0;
+    int c_first = lo0 / AT_KEYS;
+    int c_last = (q_pos + q_count - 1) / AT_KEYS;
+    int n_chunks = c_last - c_first + 1;
+    if (n_chunks <= 0)
+        return;
+
+    uint32_t bar0 = smem_u32(bars);
+    auto bar = [&](int i) { return bar0 + 8 * i; };
+    if (threadIdx.x == 0) {
+        mbar_init(bar(0), 1);
+        for (int s = 0; s < AT_STAGES; s++) {
+            mbar_init(bar(1 + s), 1);
+            mbar_init(bar(3 + s), 1);
+        }
+        mbar_init(bar(5), 1);
+        mbar_init(bar(6), 2 * AT_ROWS);
+        mbar_init(bar(7), 1);
+        mbar_init(bar(8), 2 * AT_ROWS);
+        *abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)Cfg::TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    uint32_t tmem = *tmem_slot;
+    uint32_t tmem_s = tmem, tmem_pv = tmem + AT_KEYS;
+    int *err = &g_attn_tc_error;
+    // q, the keys and the values were written by the kernel before this one
+    pdl_trigger();
+    pdl_wait();
+
+    if (warp == 0 && lane == 0) {
+        // ---------------------------------------------------------- TMA loads
+        mbar_expect_tx(bar(0), (uint32_t)(R * G * HD * 2));
+#pragma unroll
+        for (int bb = 0; bb < NB; bb++)
+            tma_load_3d(smem_u32(q_s + bb * BLK_BYTES), &map_q, bar(0), bb * 64, kvh * G, q_row);
+        const int32_t *bt = block_table + (size_t)seq * bt_stride;
+        uint32_t armed = 0, last_parity = 0;
+        for (int it = 0; it < n_chunks; it++) {
+            int s = it % AT_STAGES;
+            uint32_t ph = (it / AT_STAGES) & 1;
+            if (!mbar_wait(bar(3 + s), ph ^ 1, abort, err, 21))
+                break;
+            mbar_expect_tx(bar(1 + s), Cfg::KV_STAGE);
+            uint32_t k_dst = smem_u32(kv_s + s * Cfg::KV_STAGE);
+            uint32_t v_dst = k_dst + NB * BLK_BYTES;
+            int c = c_first + it;
+#pragma unroll
+            for (int pg = 0; pg < 2; pg++) {
+                int idx = 2 * c + pg;
+                int page = idx < bt_stride ? bt[idx] : -1;
+                if (page < 0)
+                    page = 0;          // not there: every position of it is masked
+                int y = (page * nkv + kvh) * PAGE;
+#pragma unroll
+                for (int bb = 0; bb < NB; bb++) {
+                    tma_load_2d(k_dst + bb * BLK_BYTES + pg * (PAGE * 128), &map_k, bar(1 + s),
+                                bb * 64, y);
+                    tma_load_2d(v_dst + bb * BLK_BYTES + pg * (PAGE * 128), &map_v, bar(1 + s),
+                                bb * 64, y);
+                }
+            }
+            armed |= 1u << s;
+            last_parity = (last_parity & ~(1u << s)) | (ph << s);
+        }
+        if (*abort) {
+            volatile int never = 0;
+            for (int s = 0; s < AT_STAGES; s++)
+                if (armed & (1u << s))
+                    mbar_wait(bar(1 + s), (last_parity >> s) & 1, &never, err, 24);
+        }
+    } else if (warp == 1 && lane == 0) {
+        // --------------------------------------------------------------- MMAs
+        constexpr uint32_t idesc_s = instr_desc_bf16(AT_ROWS, AT_KEYS, false);
+        constexpr uint32_t idesc_pv = instr_desc_bf16(AT_ROWS, HD, true);
+        bool ok = mbar_wait(bar(0), 0, abort, err, 22);
+        uint32_t q_a = smem_u32(q_s), p_a = smem_u32(p_s);
+        for (int it = 0; it < n_chunks && ok; it++) {
+            int s = it % AT_STAGES;
+            uint32_t ph = (it / AT_STAGES) & 1;
+            ok = mbar_wait(bar(1 + s), ph, abort, err, 23);
+            if (!ok)
+                break;
+            tc_fence_after();
+            uint32_t k_a = smem_u32(kv_s + s * Cfg::KV_STAGE);
+            uint32_t v_a = k_a + NB * BLK_BYTES;
+#pragma unroll
+            for (int kk = 0; kk < HD / 16; kk++) {
+                uint32_t off = (kk / 4) * BLK_BYTES + (kk % 4) * 32;
+                tc_mma(tmem_s, smem_desc_sw128(q_a + off, 16, 1024),
+                       smem_desc_sw128(k_a + off, 16, 1024), idesc_s, kk != 0);
+            }
+            tc_commit(bar(5));
+            ok = mbar_wait(bar(6), it & 1, abort, err, 25);       // P is in shared memory
+            if (ok && it > 0)
+                ok = mbar_wait(bar(8), (it - 1) & 1, abort, err, 26);   // the last PV was read
+            if (!ok)
+                break;
+            tc_fence_after();
+#pragma unroll
+            for (int kk = 0; kk < AT_KEYS / 16; kk++) {
+                uint32_t p_off = (kk / 4) * BLK_BYTES + (kk % 4) * 32;
+                tc_mma(tmem_pv, smem_desc_sw128(p_a + p_off, 16, 1024),
+                       smem_desc_sw128(v_a + kk * 16 * 128, BLK_BYTES, 1024), idesc_pv, kk != 0);
+            }
+            tc_commit(bar(7));
+            tc_commit(bar(3 + s));
+        }
+    } else if (warp >= 2) {
+        // ------------------------------------------------------------ row threads
+        int qw = warp & 3;                      // the TMEM lanes this warp may read
+        int hf = (warp - 2) >> 2;               // which half of the keys and of the values
+        int r = qw * 32 + lane;                 // this thread's row of the block
+        int j = r / G, g = r - j * G;           // position within the block, head of the group
+        bool live = j < q_count && j < R;
+        int pos = q_pos + j;
+        int lo = window > 0 && pos + 1 > window ? pos + 1 - window : 0;
+        uint32_t lane_addr = (uint32_t)(qw * 32) << 16;
+        const float c2 = scale * 1.4426950408889634f;      // scores in units of log2(e)
+        float m_run = -INFINITY, l_run = 0.0f;              // l_run: this thread's keys only
+        float o[HH];
+#pragma unroll
+        for (int i = 0; i < HH; i++)
+            o[i] = 0.0f;
+        bool ok = true;
+        for (int it = 0; it < n_chunks; it++) {
+            int t0 = (c_first + it) * AT_KEYS + hf * 64;    // this thread's first key
+            ok = ok && mbar_wait(bar(5), it & 1, abort, err, 27);
+            ok = __all_sync(0xffffffffu, ok);
+            tc_fence_after();
+            uint32_t raw[64];
+            float mx = -INFINITY;
+            if (ok) {
+                tc_ld32_nowait(tmem_s + lane_addr + hf * 64, raw);
+                tc_ld32_nowait(tmem_s + lane_addr + hf * 64 + 32, raw + 32);
+                tc_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 64; i++) {
+                    int t = t0 + i;
+                    float v = (live && t <= pos && t >= lo) ? __uint_as_float(raw[i]) * c2 : -INFINITY;
+                    raw[i] = __float_as_uint(v);
+                    mx = fmaxf(mx, v);
+                }
+            }
+            pair[hf * AT_ROWS + r] = mx;
+            named_barrier(1, 2 * AT_ROWS);
+            mx = fmaxf(mx, pair[(hf ^ 1) * AT_ROWS + r]);
+            float m_new = fmaxf(m_run, mx);
+            float alpha = m_run == -INFINITY ? 0.0f : exp2f(m_run - m_new);
+            if (m_new == -INFINITY)
+                alpha = 1.0f;
+            float l_chunk = 0.0f;
+            if (ok) {
+                uint8_t *blk = p_s + hf * BLK_BYTES;
+#pragma unroll
+                for (int q8 = 0; q8 < 8; q8++) {
+                    uint32_t w[4];
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        float s0 = __uint_as_float(raw[8 * q8 + 2 * e]);
+                        float s1 = __uint_as_float(raw[8 * q8 + 2 * e + 1]);
+                        float p0 = s0 == -INFINITY ? 0.0f : exp2f(s0 - m_new);
+                        float p1 = s1 == -INFINITY ? 0.0f : exp2f(s1 - m_new);
+                        l_chunk += p0 + p1;
+                        __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
+                        w[e] = *reinterpret_cast<uint32_t *>(&pk);
+                    }
+                    *reinterpret_cast<uint4 *>(blk + swz(r, q8)) = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+            }
+            fence_async_smem();
+            tc_fence_before();
+            mbar_arrive(bar(6));
+            l_run = l_run * alpha + l_chunk;
+            m_run = m_new;
+            // the pair buffer is read by the partner before the next chunk writes it:
+            // the partner passes the barrier above only after both have written, and
+            // writes again only after the barrier of the next chunk
+            ok = ok && mbar_wait(bar(7), it & 1, abort, err, 28);
+            ok = __all_sync(0xffffffffu, ok);
+            tc_fence_after();
+            if (ok) {
+#pragma unroll
+                for (int db = 0; db < HH / 32; db++) {
+                    float pv[32];
+                    tc_ld32(tmem_pv + lane_addr + hf * HH + db * 32, pv);
+#pragma unroll
+                    for (int i = 0; i < 32; i++)
+                        o[db * 32 + i] = o[db * 32 + i] * alpha + pv[i];
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(bar(8));
+        }
+        // the row's sum: both threads' keys
+        named_barrier(1, 2 * AT_ROWS);
+        pair[hf * AT_ROWS + r] = l_run;
+        named_barrier(1, 2 * AT_ROWS);
+        float l_all = l_run + pair[(hf ^ 1) * AT_ROWS + r];
+        if (ok && live) {
+            float inv = 1.0f / l_all;
+            bf16 *dst = out + ((size_t)(q_row + j) * nh + kvh * G + g) * HD + hf * HH;
+#pragma unroll
+            for (int i = 0; i < HH; i += 8) {
+                uint32_t w[4];
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    __nv_bfloat162 pk =
+                        __floats2bfloat162_rn(o[i + 2 * e] * inv, o[i + 2 * e + 1] * inv);
+                    w[e] = *reinterpret_cast<uint32_t *>(&pk);
+                }
+                *reinterpret_cast<uint4 *>(dst + i) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;"
+                     ::"r"(tmem), "r"((uint32_t)Cfg::TMEM_COLS) : "memory");
+    }
+}
+
 // ---------------------------------------------------------------- decode rows
 // One decoded token (G <= 16 query heads of one KV head) against chunks of 128
 // keys, with the keys as the M operand so that all 128 row threads have work:
@@ -390,7 +673,7 @@ constexpr int DQ_N = 16;                 // heads per MMA (N)
 constexpr int DQ_BLK = DQ_N * 128;       // a block of 16 rows of 128 bytes
 constexpr int DQ_STAGES = 3;
 constexpr int DQ_KV_STAGE = 4 * BLK_BYTES;   // K and V of one chunk, 128 values each
-constexpr int DQ_SMEM = 2 * DQ_BLK + 2 * DQ_BLK + DQ_STAGES * DQ_KV_STAGE + 1024 + 1024;
+constexpr int DQ_SMEM = 2 * DQ_BLK + 4 * DQ_BLK + DQ_STAGES * DQ_KV_STAGE + 1024 + 1024;
 
 // GP: the group's heads rounded up to a power of two (the row threads' loops).
 template <int GP>
@@ -407,11 +690,12 @@ attn_tc_decode_kernel(const __grid_constant__ CUtensorMap map_q,
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t *q_s = smem;                       // 2 blocks of [16 heads][64 values]
-    uint8_t *p_s = q_s + 2 * DQ_BLK;           // 2 blocks of [16 heads][64 keys]
-    uint8_t *kv_s = p_s + 2 * DQ_BLK;
+    uint8_t *p_s = q_s + 2 * DQ_BLK;           // 2 buffers of 2 blocks of [16 heads][64 keys]
+    uint8_t *kv_s = p_s + 4 * DQ_BLK;
     uint64_t *bars = (uint64_t *)(kv_s + DQ_STAGES * DQ_KV_STAGE);
-    // bars: 0 q_full | 1..3 kv_full | 4..6 kv_empty | 7 s_full | 8 p_full | 9 o_full | 10 pv_free
-    uint32_t *tmem_slot = (uint32_t *)(bars + 11);
+    // bars: 0 q_full | 1..3 kv_full | 4..6 kv_empty | 7,8 s_full | 9,10 p_full | 11 o_full |
+    //       12 pv_free
+    uint32_t *tmem_slot = (uint32_t *)(bars + 13);
     volatile int *abort = (volatile int *)(tmem_slot + 1);
     float *red_m = (float *)(tmem_slot + 4);   // [4 warps][16 heads]
     float *red_l = red_m + 4 * DQ_N;
@@ -439,23 +723,25 @@ attn_tc_decode_kernel(const __grid_constant__ CUtensorMap map_q,
             mbar_init(bar(1 + s), 1);
             mbar_init(bar(4 + s), 1);
         }
-        mbar_init(bar(7), 1);
-        mbar_init(bar(8), AT_ROWS);
-        mbar_init(bar(9), 1);
-        mbar_init(bar(10), AT_ROWS);
+        for (int b = 0; b < 2; b++) {
+            mbar_init(bar(7 + b), 1);
+            mbar_init(bar(9 + b), AT_ROWS);
+        }
+        mbar_init(bar(11), 1);
+        mbar_init(bar(12), AT_ROWS);
         *abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(smem_u32(tmem_slot)), "r"(32u) : "memory");
+                     ::"r"(smem_u32(tmem_slot)), "r"(64u) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     uint32_t tmem = *tmem_slot;
-    uint32_t tmem_s = tmem, tmem_pv = tmem + DQ_N;
+    uint32_t tmem_s = tmem, tmem_pv = tmem + 2 * DQ_N;    // S: two buffers of 16 columns
     int *err = &g_attn_tc_error;
     // q, the keys and the values were written by the kernel before this one
     pdl_trigger();
@@ -505,36 +791,44 @@ attn_tc_decode_kernel(const __grid_constant__ CUtensorMap map_q,
         // --------------------------------------------------------------- MMAs
         constexpr uint32_t idesc_s = instr_desc_bf16(AT_KEYS, DQ_N, false, false);
         constexpr uint32_t idesc_pv = instr_desc_bf16(HD, DQ_N, false, true);
-        bool ok = mbar_wait(bar(0), 0, abort, err, 12);
         uint32_t q_a = smem_u32(q_s), p_a = smem_u32(p_s);
-        for (int it = 0; it < n_chunks && ok; it++) {
+        // S^T of chunk `it` into S buffer it % 2
+        auto issue_s = [&](int it) -> bool {
             int s = it % DQ_STAGES;
-            uint32_t ph = (it / DQ_STAGES) & 1;
-            ok = mbar_wait(bar(1 + s), ph, abort, err, 13);
-            if (!ok)
-                break;
+            if (!mbar_wait(bar(1 + s), (it / DQ_STAGES) & 1, abort, err, 13))
+                return false;
             tc_fence_after();
             uint32_t k_a = smem_u32(kv_s + s * DQ_KV_STAGE);
-            uint32_t v_a = k_a + 2 * BLK_BYTES;
 #pragma unroll
             for (int kk = 0; kk < HD / 16; kk++)
-                tc_mma(tmem_s,
+                tc_mma(tmem_s + (it & 1) * DQ_N,
                        smem_desc_sw128(k_a + (kk / 4) * BLK_BYTES + (kk % 4) * 32, 16, 1024),
                        smem_desc_sw128(q_a + (kk / 4) * DQ_BLK + (kk % 4) * 32, 16, 1024),
                        idesc_s, kk != 0);
-            tc_commit(bar(7));
-            ok = mbar_wait(bar(8), it & 1, abort, err, 15);       // P is in shared memory
+            tc_commit(bar(7 + (it & 1)));
+            return true;
+        };
+        bool ok = mbar_wait(bar(0), 0, abort, err, 12) && issue_s(0);
+        for (int it = 0; it < n_chunks && ok; it++) {
+            // the next chunk's scores are computed while the row threads work on this
+            // one's; its S buffer was read out before P of chunk it - 1 was ready
+            if (it + 1 < n_chunks)
+                ok = issue_s(it + 1);
+            ok = ok && mbar_wait(bar(9 + (it & 1)), (it >> 1) & 1, abort, err, 15);   // P is there
             if (ok && it > 0)
-                ok = mbar_wait(bar(10), (it - 1) & 1, abort, err, 16);  // the last O^T was read
+                ok = mbar_wait(bar(12), (it - 1) & 1, abort, err, 16);   // the last O^T was read
             if (!ok)
                 break;
             tc_fence_after();
+            int s = it % DQ_STAGES;
+            uint32_t v_a = smem_u32(kv_s + s * DQ_KV_STAGE) + 2 * BLK_BYTES;
+            uint32_t pb = p_a + (it & 1) * 2 * DQ_BLK;
 #pragma unroll
             for (int kk = 0; kk < AT_KEYS / 16; kk++)
                 tc_mma(tmem_pv, smem_desc_sw128(v_a + kk * 16 * 128, BLK_BYTES, 1024),
-                       smem_desc_sw128(p_a + (kk / 4) * DQ_BLK + (kk % 4) * 32, 16, 1024),
+                       smem_desc_sw128(pb + (kk / 4) * DQ_BLK + (kk % 4) * 32, 16, 1024),
                        idesc_pv, kk != 0);
-            tc_commit(bar(9));
+            tc_commit(bar(11));
             tc_commit(bar(4 + s));
         }
     } else if (warp >= 2) {
@@ -544,16 +838,34 @@ attn_tc_decode_kernel(const __grid_constant__ CUtensorMap map_q,
         uint32_t lane_addr = (uint32_t)(qw * 32) << 16;
         const float c2 = scale * 1.4426950408889634f;
         bool ok = true;
+        // O^T of chunk `it`: read from tensor memory and stored as the chunk's partial
+        auto store_o = [&](int it) {
+            ok = ok && mbar_wait(bar(11), it & 1, abort, err, 18);
+            ok = __all_sync(0xffffffffu, ok);
+            tc_fence_after();
+            if (ok) {
+                float ov[DQ_N];
+                tc_ld16(tmem_pv + lane_addr, ov);
+                int ci = c_first + it - c_base;
+#pragma unroll
+                for (int g = 0; g < GP; g++)
+                    if (g < G)
+                        part[(((size_t)lrow * nh + kvh * G + g) * max_chunks + ci) *
+                                 (size_t)(HD + 2) + 2 + r] = ov[g];
+            }
+            tc_fence_before();
+            mbar_arrive(bar(12));
+        };
         for (int it = 0; it < n_chunks; it++) {
             int c = c_first + it;
             int t = c * AT_KEYS + r;
             bool visible = t <= q_pos && t >= lo;
-            ok = ok && mbar_wait(bar(7), it & 1, abort, err, 17);
+            ok = ok && mbar_wait(bar(7 + (it & 1)), (it >> 1) & 1, abort, err, 17);
             ok = __all_sync(0xffffffffu, ok);
             tc_fence_after();
             float sc[DQ_N], m[GP], l[GP];
             if (ok)
-                tc_ld16(tmem_s + lane_addr, sc);
+                tc_ld16(tmem_s + (it & 1) * DQ_N + lane_addr, sc);
 #pragma unroll
             for (int g = 0; g < GP; g++) {
                 float v = (ok && visible && g < G) ? sc[g] * c2 : -INFINITY;
@@ -580,9 +892,10 @@ attn_tc_decode_kernel(const __grid_constant__ CUtensorMap map_q,
                 for (int g = 0; g < GP; g++)
                     red_l[qw * DQ_N + g] = l[g];
             }
-            // P[head][key] in bfloat16: block r / 64, row g, 16-byte chunk (r % 64) / 8
+            // P[head][key] in bfloat16, buffer it % 2 (chunk it - 2's P V has been waited
+            // for): block r / 64, row g, 16-byte chunk (r % 64) / 8
             {
-                uint8_t *blk = p_s + (r / 64) * DQ_BLK;
+                uint8_t *blk = p_s + (it & 1) * 2 * DQ_BLK + (r / 64) * DQ_BLK;
                 int j = (r % 64) / 8, e = (r % 8) * 2;
 #pragma unroll
                 for (int g = 0; g < GP; g++)
@@ -592,7 +905,7 @@ attn_tc_decode_kernel(const __grid_constant__ CUtensorMap map_q,
             fence_async_smem();
             named_barrier(1, AT_ROWS);
             tc_fence_before();
-            mbar_arrive(bar(8));
+            mbar_arrive(bar(9 + (it & 1)));
             if (ok && r < G) {
                 float ll = red_l[r] + red_l[DQ_N + r] + red_l[2 * DQ_N + r] + red_l[3 * DQ_N + r];
                 float *dst = part + (((size_t)lrow * nh + kvh * G + r) * max_chunks + (c - c_base)) *
@@ -605,28 +918,18 @@ attn_tc_decode_kernel(const __grid_constant__ CUtensorMap map_q,
                 dst[0] = mine * 0.6931471805599453f;    // the merge works in natural-log units
                 dst[1] = ll;
             }
-            ok = ok && mbar_wait(bar(9), it & 1, abort, err, 18);
-            ok = __all_sync(0xffffffffu, ok);
-            tc_fence_after();
-            if (ok) {
-                float ov[DQ_N];
-                tc_ld16(tmem_pv + lane_addr, ov);
-#pragma unroll
-                for (int g = 0; g < GP; g++)
-                    if (g < G)
-                        part[(((size_t)lrow * nh + kvh * G + g) * max_chunks + (c - c_base)) *
-                                 (size_t)(HD + 2) + 2 + r] = ov[g];
-            }
-            tc_fence_before();
-            mbar_arrive(bar(10));
+            // while this chunk's P V runs, the chunk before it is read out
+            if (it > 0)
+                store_o(it - 1);
         }
+        store_o(n_chunks - 1);
     }
 
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;"
-                     ::"r"(tmem), "r"(32u) : "memory");
+                     ::"r"(tmem), "r"(64u) : "memory");
     }
 }
 
@@ -740,13 +1043,34 @@ extern "C" int jb_attn_tc_prefill(const void *q, const void *k_cache, const void
     if (!jb_attn_tc_ok(nh, nkv, hd) || n <= 0)
         return JB_EINVAL;
     int R = jb_attn_tc_block_positions(nh, nkv);
+    int G = nh / nkv;
+    CUtensorMap mq, mk, mv;
+    if (!attn_tensor_map(q, hd, nh, n, G, R, &mq) ||
+        !attn_tensor_map(k_cache, hd, n_pages * nkv * PAGE, 0, PAGE, 0, &mk) ||
+        !attn_tensor_map(v_cache, hd, n_pages * nkv * PAGE, 0, PAGE, 0, &mv))
+        return JB_EINVAL;
+    if (n_blocks <= 0)
+        return JB_OK;
+#define JB_PF(HDV)                                                                             \
+    do {                                                                                       \
+        static bool attr_set = false;                                                          \
+        if (!attr_set) {                                                                       \
+            if (cudaFuncSetAttribute(attn_tc_prefill_kernel<HDV>,                              \
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize,              \
+                                     AttnCfg<HDV>::SMEM_BYTES) != cudaSuccess)                 \
+                return JB_ELAUNCH;                                                             \
+            attr_set = true;                                                                   \
+        }                                                                                      \
+        launch(attn_tc_prefill_kernel<HDV>, dim3(n_blocks, nkv), PF_THREADS,                   \
+               AttnCfg<HDV>::SMEM_BYTES, st, mq, mk, mv, qblk, block_table, bt_stride,         \
+               (bf16 *)out, nh, nkv, G, R, window, scale);                                     \
+    } while (0)
     if (hd == 128)
-        return launch_attn_tc<128, false>(q, k_cache, v_cache, n_pages, qblk, n_blocks, nullptr,
-                                          nullptr, block_table, bt_stride, out, nullptr, n, nh,
-                                          nkv, R, window, scale, 0, 1, 0, 0, st);
-    return launch_attn_tc<64, false>(q, k_cache, v_cache, n_pages, qblk, n_blocks, nullptr, nullptr,
-                                     block_table, bt_stride, out, nullptr, n, nh, nkv, R, window,
-                                     scale, 0, 1, 0, 0, st);
+        JB_PF(128);
+    else
+        JB_PF(64);
+#undef JB_PF
+    return launch_status();
 }
 
 // Decode rows row0 .. row0 + n_rows - 1 (one token each): writes the per-chunk

@@ -91,8 +91,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     volatile int *abort = (volatile int *)(tmem_slot + 1);
 
     int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    int m0 = blockIdx.x * (EPI == EPI_SWIGLU ? TILE_M : TILE_M * MT);
-    int n0 = blockIdx.y * BN;
+    // token tiles vary fastest: the CTAs that run at the same time share weight
+    // tiles, which then come from memory once, and the (small) activations come
+    // from the L2
+    int m0 = blockIdx.y * (EPI == EPI_SWIGLU ? TILE_M : TILE_M * MT);
+    int n0 = blockIdx.x * BN;
     int total_kb = (k + BK - 1) / BK;
     int kb0 = blockIdx.z * kb_per_split;
     int nkb = min(kb_per_split, total_kb - kb0);
@@ -321,7 +324,7 @@ static int launch_tc(const void *A, const void *W, float *out, bf16 *out_act, in
         return JB_EINVAL;   // a part without work
     int feats = EPI == EPI_SWIGLU ? second_off : m;
     int tile_feats = EPI == EPI_SWIGLU ? TILE_M : TILE_M * MT;
-    dim3 grid((feats + tile_feats - 1) / tile_feats, (n + BN - 1) / BN, splits);
+    dim3 grid((n + BN - 1) / BN, (feats + tile_feats - 1) / tile_feats, splits);
     if (grid.y > 65535 || grid.z > 65535)
         return JB_EINVAL;
     launch(kern, grid, 192, Cfg::SMEM_BYTES, st, map_w, map_a, out, out_act, n, m, k, second_off,
