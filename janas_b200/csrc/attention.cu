@@ -198,7 +198,8 @@ attn_partial_kernel(const T *__restrict__ q, const T *__restrict__ k_cache,
 template <typename T>
 __global__ void attn_merge_kernel(const float *__restrict__ part,
                                   const int32_t *__restrict__ row_pos, T *__restrict__ out,
-                                  int row0, int nh, int hd, int window, int max_chunks)
+                                  int row0, int nh, int hd, int window, int max_chunks,
+                                  int chunks_per_part)
 {
     pdl_trigger();
     pdl_wait();
@@ -206,13 +207,14 @@ __global__ void attn_merge_kernel(const float *__restrict__ part,
     int row = row0 + lrow;
     int pos = row_pos[row];
     int lo = window > 0 && pos + 1 > window ? pos + 1 - window : 0;
-    int n_chunks = pos / ATT_CHUNK - lo / ATT_CHUNK + 1;
+    // a partial covers chunks_per_part chunks; max_chunks is the partials' stride
+    int n_chunks = (pos / ATT_CHUNK - lo / ATT_CHUNK + chunks_per_part) / chunks_per_part;
     float m = -INFINITY, l = 0.0f, o = 0.0f;
-    // four partials are fetched together and then joined in chunk order
-    for (int c0 = 0; c0 < n_chunks; c0 += 4) {
-        float mc[4], lc[4], oc[4];
+    // eight partials are fetched together and then joined in chunk order
+    for (int c0 = 0; c0 < n_chunks; c0 += 8) {
+        float mc[8], lc[8], oc[8];
 #pragma unroll
-        for (int u = 0; u < 4; u++) {
+        for (int u = 0; u < 8; u++) {
             int ci = min(c0 + u, n_chunks - 1);
             const float *p = part + part_at((size_t)lrow, nh, h, max_chunks, ci, hd);
             mc[u] = p[0];
@@ -220,7 +222,7 @@ __global__ void attn_merge_kernel(const float *__restrict__ part,
             oc[u] = d < hd ? p[2 + d] : 0.0f;
         }
 #pragma unroll
-        for (int u = 0; u < 4; u++) {
+        for (int u = 0; u < 8; u++) {
             if (c0 + u >= n_chunks)
                 break;
             float mn = fmaxf(m, mc[u]);
@@ -262,7 +264,7 @@ static int attention_typed(const T *q, const T *k_cache, const T *v_cache, const
     if (cudaGetLastError() != cudaSuccess)
         return JB_ELAUNCH;
     launch(attn_merge_kernel<T>, dim3(n_rows, nh), (hd + 31) / 32 * 32, 0, st, (const float *)part,
-           row_pos, out, row0, nh, hd, window, max_chunks);
+           row_pos, out, row0, nh, hd, window, max_chunks, 1);
     return launch_status();
 }
 
@@ -305,25 +307,26 @@ extern "C" int jb_attention(const void *q, const void *k_cache, const void *v_ca
     return JB_EINVAL;
 }
 
-// Joins per-chunk partials that are already in `scratch` (written by
-// jb_attention's first kernel or by the tensor-core decode kernel, same layout)
-// for rows row0 .. row0 + n_rows - 1.
+// Joins partials that are already in `scratch` (written by the tensor-core
+// decode kernels) for rows row0 .. row0 + n_rows - 1.  A row has one partial per
+// `chunks_per_part` chunks of its range; `max_parts` partials of room per
+// (row, head).
 extern "C" int jb_attention_merge(const float *scratch, const int32_t *row_pos, void *out, int dt,
-                                  int row0, int n_rows, int nh, int hd, int window, int max_chunks,
-                                  cudaStream_t st)
+                                  int row0, int n_rows, int nh, int hd, int window, int max_parts,
+                                  int chunks_per_part, cudaStream_t st)
 {
     if (n_rows <= 0)
         return JB_OK;
-    if (hd <= 0 || hd > 512 || nh <= 0 || nh > 65535 || max_chunks <= 0)
+    if (hd <= 0 || hd > 512 || nh <= 0 || nh > 65535 || max_parts <= 0 || chunks_per_part <= 0)
         return JB_EINVAL;
     dim3 grid(n_rows, nh);
     int threads = (hd + 31) / 32 * 32;
     if (dt == JB_F32)
         launch(attn_merge_kernel<float>, grid, threads, 0, st, scratch, row_pos, (float *)out, row0,
-               nh, hd, window, max_chunks);
+               nh, hd, window, max_parts, chunks_per_part);
     else if (dt == JB_BF16)
         launch(attn_merge_kernel<bf16>, grid, threads, 0, st, scratch, row_pos, (bf16 *)out, row0,
-               nh, hd, window, max_chunks);
+               nh, hd, window, max_parts, chunks_per_part);
     else
         return JB_EINVAL;
     return launch_status();

@@ -668,7 +668,8 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
 //                              through warp shuffles and shared memory
 //   O^T[value, head] = V^T P   M = 128 values (V MN-major as it lies), N = 16
 //
-// One partial (m, l, O) per chunk and head goes to scratch, as in attention.cu.
+// A CTA runs over its chunks with a running (m, l, O) and leaves one partial per
+// head in scratch; attention.cu's merge kernel joins the CTAs' partials.
 constexpr int DQ_N = 16;                 // heads per MMA (N)
 constexpr int DQ_BLK = DQ_N * 128;       // a block of 16 rows of 128 bytes
 constexpr int DQ_STAGES = 3;
@@ -703,6 +704,7 @@ attn_tc_decode_kernel(const __grid_constant__ CUtensorMap map_q,
     int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     int kvh = blockIdx.y;
     int parts = (max_chunks + chunks_per_cta - 1) / chunks_per_cta;
+    int max_parts = parts;             // partials per (row, head) in scratch
     int lrow = blockIdx.x / parts, part_i = blockIdx.x % parts;
     int q_row = row0 + lrow;
     int q_pos = row_pos[q_row];
@@ -838,20 +840,27 @@ attn_tc_decode_kernel(const __grid_constant__ CUtensorMap map_q,
         uint32_t lane_addr = (uint32_t)(qw * 32) << 16;
         const float c2 = scale * 1.4426950408889634f;
         bool ok = true;
-        // O^T of chunk `it`: read from tensor memory and stored as the chunk's partial
-        auto store_o = [&](int it) {
+        // running over this CTA's chunks: maximum, sum (every thread keeps all heads')
+        // and this thread's value of O for every head
+        float m_run[GP], l_run[GP], o_acc[GP], alpha[GP];
+#pragma unroll
+        for (int g = 0; g < GP; g++) {
+            m_run[g] = -INFINITY;
+            l_run[g] = 0.0f;
+            o_acc[g] = 0.0f;
+            alpha[g] = 0.0f;
+        }
+        // O^T of chunk `it` joins the running O (scaled by that chunk's alpha)
+        auto take_o = [&](int it) {
             ok = ok && mbar_wait(bar(11), it & 1, abort, err, 18);
             ok = __all_sync(0xffffffffu, ok);
             tc_fence_after();
             if (ok) {
                 float ov[DQ_N];
                 tc_ld16(tmem_pv + lane_addr, ov);
-                int ci = c_first + it - c_base;
 #pragma unroll
                 for (int g = 0; g < GP; g++)
-                    if (g < G)
-                        part[(((size_t)lrow * nh + kvh * G + g) * max_chunks + ci) *
-                                 (size_t)(HD + 2) + 2 + r] = ov[g];
+                    o_acc[g] = o_acc[g] * alpha[g] + ov[g];
             }
             tc_fence_before();
             mbar_arrive(bar(12));
@@ -878,12 +887,20 @@ attn_tc_decode_kernel(const __grid_constant__ CUtensorMap map_q,
                     red_m[qw * DQ_N + g] = m[g];
             }
             named_barrier(1, AT_ROWS);
+            // the chunk before this one is taken into O with ITS alpha, before alpha
+            // is overwritten below
+            if (it > 0)
+                take_o(it - 1);
 #pragma unroll
             for (int g = 0; g < GP; g++) {
-                float mm = fmaxf(fmaxf(red_m[g], red_m[DQ_N + g]),
+                float mc = fmaxf(fmaxf(red_m[g], red_m[DQ_N + g]),
                                  fmaxf(red_m[2 * DQ_N + g], red_m[3 * DQ_N + g]));
-                m[g] = mm;
-                float p = sc[g] == -INFINITY ? 0.0f : exp2f(sc[g] - mm);
+                float mn = fmaxf(m_run[g], mc);
+                alpha[g] = m_run[g] == -INFINITY ? 0.0f : exp2f(m_run[g] - mn);
+                if (mn == -INFINITY)
+                    alpha[g] = 1.0f;
+                m_run[g] = mn;
+                float p = sc[g] == -INFINITY ? 0.0f : exp2f(sc[g] - mn);
                 sc[g] = p;
                 l[g] = warp_sum(p);
             }
@@ -906,23 +923,28 @@ attn_tc_decode_kernel(const __grid_constant__ CUtensorMap map_q,
             named_barrier(1, AT_ROWS);
             tc_fence_before();
             mbar_arrive(bar(9 + (it & 1)));
-            if (ok && r < G) {
-                float ll = red_l[r] + red_l[DQ_N + r] + red_l[2 * DQ_N + r] + red_l[3 * DQ_N + r];
-                float *dst = part + (((size_t)lrow * nh + kvh * G + r) * max_chunks + (c - c_base)) *
-                                        (size_t)(HD + 2);
-                // m[] is indexed at compile time only: pick this thread's head
-                float mine = -INFINITY;
 #pragma unroll
-                for (int g = 0; g < GP; g++)
-                    mine = g == r ? m[g] : mine;
-                dst[0] = mine * 0.6931471805599453f;    // the merge works in natural-log units
-                dst[1] = ll;
-            }
-            // while this chunk's P V runs, the chunk before it is read out
-            if (it > 0)
-                store_o(it - 1);
+            for (int g = 0; g < GP; g++)
+                l_run[g] = l_run[g] * alpha[g] + (red_l[g] + red_l[DQ_N + g] + red_l[2 * DQ_N + g] +
+                                                  red_l[3 * DQ_N + g]);
         }
-        store_o(n_chunks - 1);
+        take_o(n_chunks - 1);
+        // one partial for this CTA's run of chunks
+        if (ok) {
+            int pi = part_i;
+#pragma unroll
+            for (int g = 0; g < GP; g++) {
+                if (g >= G)
+                    continue;
+                float *dst = part + (((size_t)lrow * nh + kvh * G + g) * max_parts + pi) *
+                                        (size_t)(HD + 2);
+                if (r == g) {
+                    dst[0] = m_run[g] * 0.6931471805599453f;   // the merge works in natural logs
+                    dst[1] = l_run[g];
+                }
+                dst[2 + r] = o_acc[g];
+            }
+        }
     }
 
     tc_fence_before();
@@ -1126,6 +1148,13 @@ extern "C" int jb_attn_tc_decode(const void *q, const void *k_cache, const void 
     return launch_attn_tc<64, true>(q, k_cache, v_cache, n_pages, nullptr, 0, row_pos, row_seq,
                                     block_table, bt_stride, nullptr, part, n, nh, nkv, 0, window,
                                     scale, max_chunks, chunks_per_cta, row0, n_rows, st);
+}
+
+// Whether the decode kernel for these sizes runs over several chunks per CTA and
+// leaves one partial per CTA (1), or wants one chunk per CTA (0).
+extern "C" int jb_attn_tc_decode_runs(int nh, int nkv, int hd)
+{
+    return jb_attn_tc_ok(nh, nkv, hd) && hd == 128 && nh / nkv <= DQ_N;
 }
 
 extern "C" int jb_attn_tc_error(void)

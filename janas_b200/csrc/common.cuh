@@ -62,20 +62,24 @@ __device__ __forceinline__ float block_sum(float v, float *red)
     return warp_sum(t);
 }
 
-// p[0] + p[stride] + ... + p[(S - 1) stride], added in that order to `v`.  The
-// loads of four terms are issued together, so the chain of additions does not
-// also become a chain of memory latencies.
+// p[0] + p[stride] + ... + p[(S - 1) stride], added in that order to `v`.  Up
+// to sixteen terms are fetched together, so the chain of additions does not also
+// become a chain of memory latencies.
 __device__ __forceinline__ float add_partials(float v, const float *__restrict__ p, int S,
                                               size_t stride)
 {
-    int s = 0;
-    for (; s + 4 <= S; s += 4) {
-        float a = p[(size_t)s * stride], b = p[(size_t)(s + 1) * stride],
-              c = p[(size_t)(s + 2) * stride], d = p[(size_t)(s + 3) * stride];
-        v = (((v + a) + b) + c) + d;
+    if (S == 1)
+        return v + p[0];
+    for (int s0 = 0; s0 < S; s0 += 16) {
+        float t[16];
+#pragma unroll
+        for (int u = 0; u < 16; u++)
+            t[u] = s0 + u < S ? p[(size_t)(s0 + u) * stride] : 0.0f;
+#pragma unroll
+        for (int u = 0; u < 16; u++)
+            if (s0 + u < S)
+                v += t[u];
     }
-    for (; s < S; s++)
-        v += p[(size_t)s * stride];
     return v;
 }
 

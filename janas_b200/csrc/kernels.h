@@ -39,7 +39,9 @@ int jb_attention(const void *q, const void *k_cache, const void *v_cache, int dt
                  int bt_stride, float *scratch, void *out, int row0, int n_rows, int nh, int nkv,
                  int hd, int window, float scale, int max_chunks, cudaStream_t st);
 int jb_attention_merge(const float *scratch, const int32_t *row_pos, void *out, int dt, int row0,
-                       int n_rows, int nh, int hd, int window, int max_chunks, cudaStream_t st);
+                       int n_rows, int nh, int hd, int window, int max_parts, int chunks_per_part,
+                       cudaStream_t st);
+int jb_attn_tc_decode_runs(int nh, int nkv, int hd);
 int jb_attn_tc_ok(int nh, int nkv, int hd);
 int jb_attn_tc_block_positions(int nh, int nkv);
 int jb_attn_tc_prefill(const void *q, const void *k_cache, const void *v_cache, long long n_pages,

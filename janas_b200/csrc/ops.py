@@ -285,14 +285,22 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                                     _p(out), n, nh, nkv, hd, window, ctypes.c_float(scale),
                                     _stream()), "attention (tcgen05, prefill)")
         return out
-    per_row = int(L.jb_attention_scratch(1, nh, hd, max_chunks))
+    if tc:
+        # CTAs per (token, KV head): each runs over per_cta chunks and leaves one partial
+        if L.jb_attn_tc_decode_runs(nh, nkv, hd):
+            parts = _decode_parts(min(n, 4096) * nkv, max_chunks)
+        else:
+            parts = max_chunks
+        per_cta = (max_chunks + parts - 1) // parts
+        parts = (max_chunks + per_cta - 1) // per_cta
+    else:
+        parts, per_cta = max_chunks, 1
+    per_row = int(L.jb_attention_scratch(1, nh, hd, parts))
     rows_per_call = max(1, min(n, (_ATT_SCRATCH_BYTES // 4) // max(per_row, 1)))
     scratch = _scratch(q.device, per_row * rows_per_call)
     for row0 in range(0, n, rows_per_call):
         cnt = min(rows_per_call, n - row0)
         if tc:
-            parts = _decode_parts(cnt * nkv, max_chunks)
-            per_cta = (max_chunks + parts - 1) // parts
             _check(L.jb_attn_tc_decode(_p(q), _p(k_cache), _p(v_cache),
                                        ctypes.c_longlong(k_cache.shape[0]), _p(row_pos),
                                        _p(row_seq), _p(block_table), block_table.shape[1],
@@ -300,7 +308,8 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                                        ctypes.c_float(scale), max_chunks, per_cta, _stream()),
                    "attention (tcgen05, decode)")
             _check(L.jb_attention_merge(_p(scratch), _p(row_pos), _p(out), _DT[q.dtype], row0, cnt,
-                                        nh, hd, window, max_chunks, _stream()), "attention merge")
+                                        nh, hd, window, parts, per_cta, _stream()),
+                   "attention merge")
         else:
             _check(L.jb_attention(_p(q), _p(k_cache), _p(v_cache), _DT[q.dtype], _p(row_pos),
                                   _p(row_seq), _p(block_table), block_table.shape[1], _p(scratch),
