@@ -27,7 +27,8 @@ FP32_CUT_TOL = 0.0
 # bfloat16 engine against itself under another cut
 BF16_CUT_TOL = 1.5e-2
 
-LENGTHS = {"A": [7, 1, 13, 70, 127], "B": [1, 5, 17, 33, 130, 250], "C": [3, 40, 64, 65, 200, 430]}
+LENGTHS = {"A": [7, 1, 13, 70, 127], "B": [1, 5, 17, 33, 130, 250], "C": [3, 40, 64, 65, 200, 430],
+           "D": [1, 31, 64, 129, 300, 500], "E": [2, 63, 128, 257, 600]}
 
 
 def requests(name):
@@ -60,7 +61,7 @@ def check_against_plain(name, dtype, got, reqs, ids):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_whole(name, dtype):
     reqs = requests(name)
     eng = engine(name, dtype)
@@ -71,7 +72,7 @@ def test_whole(name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_last_32_one_by_one(name, dtype):
     reqs = requests(name)
     eng = engine(name, dtype)
@@ -103,7 +104,7 @@ def batches_for(name):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_unequal_batches_with_slot_reuse(name, dtype):
     from janas_b200.engine import Engine
     batches = batches_for(name)

@@ -26,8 +26,26 @@ TINY_C = dict(
     rms_norm_eps=3e-6, tie_word_embeddings=True, max_position_embeddings=1024,
     use_sliding_window=True, sliding_window=37, max_window_layers=2)
 
-TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
-SEEDS = {"A": 0, "B": 1, "C": 2}
+# head size 64: the tensor-core attention kernels with one 64-value block per head;
+# GQA ratio 4, untied, eps and rope base different again
+TINY_D = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3",
+    num_hidden_layers=2, hidden_size=128, num_attention_heads=4, num_key_value_heads=1,
+    head_dim=64, intermediate_size=200, vocab_size=500, rope_theta=300000.0,
+    rms_norm_eps=2e-6, tie_word_embeddings=False, max_position_embeddings=512)
+
+# head size 128 as in the full-size models, 3 KV heads of 2 query heads, a window on
+# the first layer only (given as layer_types), vocabulary no multiple of 8
+TINY_E = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3",
+    num_hidden_layers=3, hidden_size=104, num_attention_heads=6, num_key_value_heads=3,
+    head_dim=128, intermediate_size=264, vocab_size=777, rope_theta=1e6,
+    rms_norm_eps=1e-6, tie_word_embeddings=True, max_position_embeddings=640,
+    use_sliding_window=True, sliding_window=150,
+    layer_types=["sliding_attention", "full_attention", "full_attention"])
+
+TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E}
+SEEDS = {"A": 0, "B": 1, "C": 2, "D": 3, "E": 4}
 
 
 def tokens(rng: np.random.Generator, n: int, vocab: int):
