@@ -32,60 +32,74 @@ __global__ void rope_table_kernel(float *__restrict__ cs, float *__restrict__ sn
 }
 
 // One warp per (row, head slot); head slots are the q heads, then the k
-// heads, then the v heads of the row's fused [q | k | v] vector.
+// heads, then the v heads of the row's fused [q | k | v] vector.  PAIRS is how
+// many (low, high) pairs of a head a lane holds: ceil(hd / 64).
 //
 // qkv: S stacked [n, (nh + 2 nkv) hd] float partial sums.
 // q_out: [n, nh, hd] in the cache's type.  K and V go to page
 // block_table[seq][pos / PAGE] of k_cache / v_cache, which are laid out
 // [page][kv head][PAGE][hd].
-template <typename TC, typename TW>
-__global__ void qk_norm_rope_append_kernel(
+template <typename TC, typename TW, int PAIRS>
+__global__ void __launch_bounds__(128)
+qk_norm_rope_append_kernel(
     const float *__restrict__ qkv, int S, size_t split_stride, const TW *__restrict__ q_w,
     const TW *__restrict__ k_w, float eps, const float *__restrict__ cs,
     const float *__restrict__ sn, int rot_half, const int32_t *__restrict__ row_pos,
     const int32_t *__restrict__ row_seq, const int32_t *__restrict__ block_table, int bt_stride,
     TC *__restrict__ q_out, TC *__restrict__ k_cache, TC *__restrict__ v_cache, int n, int nh,
-    int nkv, int hd, int table_half)
+    int nkv, int hd)
 {
     pdl_trigger();
-    pdl_wait();
-    int slots = nh + 2 * nkv;
-    size_t task = (size_t)blockIdx.x * blockDim.y + threadIdx.y;
-    if (task >= (size_t)n * slots)
+    unsigned slots = nh + 2 * nkv;
+    unsigned task = blockIdx.x * blockDim.y + threadIdx.y;
+    if (task >= (unsigned)n * slots)
         return;
-    int row = (int)(task / slots), hs = (int)(task % slots);
+    unsigned row = task / slots, hs = task - row * slots;
     int lane = threadIdx.x;
-    int pos = row_pos[row];
-    size_t width = (size_t)slots * hd;
-    const float *src = qkv + (size_t)row * width + (size_t)hs * hd;
+    int half = hd / 2;
+    bool is_v = hs >= (unsigned)(nh + nkv);
+    const TW *w = hs < (unsigned)nh ? q_w : k_w;
 
+    // Positions, page tables, rotation tables and norm weights were written long
+    // before the kernel before this one: they are fetched before the wait.
+    int pos = row_pos[row];
     TC *dst;
-    if (hs < nh) {
+    if (hs < (unsigned)nh) {
         dst = q_out + ((size_t)row * nh + hs) * hd;
     } else {
         if (k_cache == nullptr)
             return;
-        int kvh = hs < nh + nkv ? hs - nh : hs - nh - nkv;
+        int kvh = !is_v ? hs - nh : hs - nh - nkv;
         int page = block_table[(size_t)row_seq[row] * bt_stride + pos / PAGE];
         size_t at = (((size_t)page * nkv + kvh) * PAGE + (pos % PAGE)) * hd;
-        dst = (hs < nh + nkv ? k_cache : v_cache) + at;
+        dst = (!is_v ? k_cache : v_cache) + at;
     }
-
-    if (hs >= nh + nkv) {  // V: the sum of the partial sums, as it is
-        for (int i = lane; i < hd; i += 32) {
-            dst[i] = from_f<TC>(add_partials(0.0f, src + i, S, split_stride));
+    float co[PAIRS], si[PAIRS], wl[PAIRS], wh[PAIRS];
+    bool rotate = !is_v && rot_half == half;
+#pragma unroll
+    for (int j = 0; j < PAIRS; j++) {
+        int i = lane + 32 * j;
+        co[j] = 1.0f;
+        si[j] = 0.0f;
+        wl[j] = wh[j] = 1.0f;
+        if (i < half && !is_v) {
+            if (rotate) {
+                co[j] = cs[(size_t)pos * rot_half + i];
+                si[j] = sn[(size_t)pos * rot_half + i];
+            }
+            if (w != nullptr) {
+                wl[j] = to_f(w[i]);
+                wh[j] = to_f(w[i + half]);
+            }
         }
-        return;
     }
+    pdl_wait();
 
-    const TW *w = hs < nh ? q_w : k_w;
-    // a head of up to 512 values: 16 per lane, held as 8 (low, high) pairs
-    constexpr int MAXP = 8;
-    int half = hd / 2;
-    float lo[MAXP], hi[MAXP];
+    const float *src = qkv + (size_t)row * slots * hd + (size_t)hs * hd;
+    float lo[PAIRS], hi[PAIRS];
     float ss = 0.0f;
 #pragma unroll
-    for (int j = 0; j < MAXP; j++) {
+    for (int j = 0; j < PAIRS; j++) {
         int i = lane + 32 * j;
         lo[j] = hi[j] = 0.0f;
         if (i < half) {
@@ -96,28 +110,22 @@ __global__ void qk_norm_rope_append_kernel(
         }
     }
     float scale = 1.0f;
-    if (w != nullptr) {
+    if (!is_v && w != nullptr) {
         ss = warp_sum(ss);
         scale = 1.0f / sqrtf(ss / (float)hd + eps);
     }
-    const float *c = cs + (size_t)pos * table_half;
-    const float *sgn = sn + (size_t)pos * table_half;
 #pragma unroll
-    for (int j = 0; j < MAXP; j++) {
+    for (int j = 0; j < PAIRS; j++) {
         int i = lane + 32 * j;
         if (i < half) {
             float a = lo[j], b = hi[j];
-            if (w != nullptr) {
-                a = (a * scale) * to_f(w[i]);
-                b = (b * scale) * to_f(w[i + half]);
+            if (!is_v && w != nullptr) {
+                a = (a * scale) * wl[j];
+                b = (b * scale) * wh[j];
             }
-            // the rotation covers the first 2 rot_half values of the head as
-            // pairs (i, i + rot_half); with the whole head rotated that is
-            // (i, i + half)
-            if (rot_half == half) {
-                float co = c[i], si = sgn[i];
-                dst[i] = from_f<TC>(a * co - b * si);
-                dst[i + half] = from_f<TC>(a * si + b * co);
+            if (rotate) {
+                dst[i] = from_f<TC>(a * co[j] - b * si[j]);
+                dst[i + half] = from_f<TC>(a * si[j] + b * co[j]);
             } else {
                 dst[i] = from_f<TC>(a);
                 dst[i + half] = from_f<TC>(b);
@@ -157,14 +165,27 @@ extern "C" int jb_qk_norm_rope_append(const float *qkv, int S, long long split_s
     if ((q_w == nullptr) != (k_w == nullptr))
         return JB_EINVAL;
     size_t tasks = (size_t)n * (nh + 2 * nkv);
+    if (tasks > 0xffffffffu)
+        return JB_EINVAL;
     dim3 block(32, 4);
     unsigned grid = (unsigned)((tasks + 3) / 4);
-    int table_half = rot_half;
-#define JB_ROPE(TC, TW)                                                                        \
-    launch(qk_norm_rope_append_kernel<TC, TW>, grid, block, 0, st,                             \
+    int pairs = (hd / 2 + 31) / 32;
+#define JB_ROPE_P(TC, TW, P)                                                                   \
+    launch(qk_norm_rope_append_kernel<TC, TW, P>, grid, block, 0, st,                          \
         qkv, S, (size_t)split_stride, (const TW *)q_w, (const TW *)k_w, eps, cs, sn, rot_half, \
         row_pos, row_seq, block_table, bt_stride, (TC *)q_out, (TC *)k_cache, (TC *)v_cache, n, \
-        nh, nkv, hd, table_half)
+        nh, nkv, hd)
+#define JB_ROPE(TC, TW)                                                                        \
+    do {                                                                                       \
+        if (pairs <= 1)                                                                        \
+            JB_ROPE_P(TC, TW, 1);                                                              \
+        else if (pairs <= 2)                                                                   \
+            JB_ROPE_P(TC, TW, 2);                                                              \
+        else if (pairs <= 4)                                                                   \
+            JB_ROPE_P(TC, TW, 4);                                                              \
+        else                                                                                   \
+            JB_ROPE_P(TC, TW, 8);                                                              \
+    } while (0)
     if (cache_dt == JB_F32 && w_dt == JB_F32)
         JB_ROPE(float, float);
     else if (cache_dt == JB_F32 && w_dt == JB_BF16)
@@ -175,6 +196,7 @@ extern "C" int jb_qk_norm_rope_append(const float *qkv, int S, long long split_s
         JB_ROPE(bf16, bf16);
     else
         return JB_EINVAL;
+#undef JB_ROPE_P
 #undef JB_ROPE
     return launch_status();
 }

@@ -37,14 +37,39 @@ __global__ void rmsnorm_kernel(float *__restrict__ x, const float *__restrict__ 
                                size_t delta_stride, const int32_t *__restrict__ row_idx,
                                const TW *__restrict__ w, TO *__restrict__ out, int dm, float eps)
 {
+    constexpr int KEEP = 12;             // values a thread keeps between the two passes
     __shared__ float red[32];
     pdl_trigger();
+    // the norm's weight does not depend on the kernel before this one
+    float wv[KEEP];
+    if (out != nullptr) {
+#pragma unroll
+        for (int u = 0; u < KEEP; u++) {
+            int i = threadIdx.x + u * blockDim.x;
+            wv[u] = i < dm ? to_f(w[i]) : 0.0f;
+        }
+    }
     pdl_wait();
     size_t orow = blockIdx.x;
     size_t row = row_idx ? (size_t)row_idx[orow] : orow;
     float *xr = x + row * dm;
+    float xv[KEEP];
     float ss = 0.0f;
-    for (int i = threadIdx.x; i < dm; i += blockDim.x) {
+#pragma unroll
+    for (int u = 0; u < KEEP; u++) {
+        int i = threadIdx.x + u * blockDim.x;
+        float v = 0.0f;
+        if (i < dm) {
+            v = xr[i];
+            if (delta) {
+                v = add_partials(v, delta + row * dm + i, S, delta_stride);
+                xr[i] = v;
+            }
+        }
+        xv[u] = v;
+        ss = fmaf(v, v, ss);
+    }
+    for (int i = threadIdx.x + KEEP * blockDim.x; i < dm; i += blockDim.x) {   // very wide rows
         float v = xr[i];
         if (delta) {
             v = add_partials(v, delta + row * dm + i, S, delta_stride);
@@ -57,7 +82,13 @@ __global__ void rmsnorm_kernel(float *__restrict__ x, const float *__restrict__ 
         return;
     float scale = 1.0f / sqrtf(ss / (float)dm + eps);
     TO *o = out + orow * dm;
-    for (int i = threadIdx.x; i < dm; i += blockDim.x)
+#pragma unroll
+    for (int u = 0; u < KEEP; u++) {
+        int i = threadIdx.x + u * blockDim.x;
+        if (i < dm)
+            o[i] = from_f<TO>((xv[u] * scale) * wv[u]);
+    }
+    for (int i = threadIdx.x + KEEP * blockDim.x; i < dm; i += blockDim.x)
         o[i] = from_f<TO>((xr[i] * scale) * to_f(w[i]));
 }
 
@@ -81,10 +112,14 @@ __global__ void swiglu_kernel(const float *__restrict__ gu, int S, size_t stride
     out[i] = from_f<TO>(h);
 }
 
+// Threads of a block that works on one row: about eight values each.  The
+// number depends on the row's width alone, because the order in which a row's
+// squares are added depends on it and a row's result must not depend on the
+// batch it is in.
 static int norm_threads(int dm)
 {
     int t = 32;
-    while (t < 1024 && t * 4 < dm)
+    while (t < 1024 && t * 8 < dm)
         t <<= 1;
     return t;
 }
