@@ -401,6 +401,21 @@ __device__ __forceinline__ void tc_ld32_nowait(uint32_t taddr, uint32_t *r)
 
 __device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+template <int HD> struct PrefillCfg {
+    static constexpr int NB = HD / 64;
+    static constexpr int Q_BYTES = NB * BLK_BYTES;
+    static constexpr int P_BYTES = 2 * BLK_BYTES;          // 128 rows x 128 keys, two of them
+    static constexpr int KV_STAGE = 2 * NB * BLK_BYTES;
+    static constexpr int TAIL = 3072;                      // barriers, what rows' threads swap
+    static constexpr int SMEM_BYTES = Q_BYTES + 2 * P_BYTES + AT_STAGES * KV_STAGE + TAIL;
+    static constexpr int TMEM_COLS = 512;                  // S twice (2 x 128), PV (HD)
+};
+
+// The chunks are software-pipelined: while the row threads turn the scores of
+// chunk i into weights, the tensor core computes the scores of chunk i + 1 (a
+// second S buffer) and P V of chunk i - 1 (a second P buffer); P V of chunk i - 1
+// is added to the running output, scaled by that chunk's factor, after the
+// maximum of chunk i is known.
 template <int HD>
 __global__ void __launch_bounds__(PF_THREADS)
 attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
@@ -410,19 +425,18 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
                        bf16 *__restrict__ out, int nh, int nkv, int G, int R, int window,
                        float scale)
 {
-    using Cfg = AttnCfg<HD>;
+    using Cfg = PrefillCfg<HD>;
     constexpr int NB = Cfg::NB;
     constexpr int HH = HD / 2;                 // values a row thread owns
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t *q_s = smem;
-    uint8_t *p_s = q_s + Cfg::Q_BYTES;
-    uint8_t *kv_s = p_s + Cfg::P_BYTES;
+    uint8_t *p_s = q_s + Cfg::Q_BYTES;         // two buffers of P_BYTES
+    uint8_t *kv_s = p_s + 2 * Cfg::P_BYTES;
     uint64_t *bars = (uint64_t *)(kv_s + AT_STAGES * Cfg::KV_STAGE);
-    // bars: 0 q_full | 1,2 kv_full | 3,4 kv_empty | 5 s_full | 6 p_full | 7 o_full | 8 pv_free
-    uint32_t *tmem_slot = (uint32_t *)(bars + 9);
+    // bars: 0 q_full | 1,2 kv_full | 3,4 kv_empty | 5,6 s_full | 7,8 p_full | 9 o_full | 10 pv_free
+    uint32_t *tmem_slot = (uint32_t *)(bars + 11);
     volatile int *abort = (volatile int *)(tmem_slot + 1);
-    float *pair = (float *)(tmem_slot + 4);    // [2 halves][128 rows]: what a row's threads swap
+    float *pair = (float *)(tmem_slot + 4);    // [2 chunks][2 halves][128 rows]
 
     int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     int kvh = blockIdx.y;
@@ -439,14 +453,14 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
     auto bar = [&](int i) { return bar0 + 8 * i; };
     if (threadIdx.x == 0) {
         mbar_init(bar(0), 1);
-        for (int s = 0; s < AT_STAGES; s++) {
+        for (int s = 0; s < 2; s++) {
             mbar_init(bar(1 + s), 1);
             mbar_init(bar(3 + s), 1);
+            mbar_init(bar(5 + s), 1);
+            mbar_init(bar(7 + s), 2 * AT_ROWS);
         }
-        mbar_init(bar(5), 1);
-        mbar_init(bar(6), 2 * AT_ROWS);
-        mbar_init(bar(7), 1);
-        mbar_init(bar(8), 2 * AT_ROWS);
+        mbar_init(bar(9), 1);
+        mbar_init(bar(10), 2 * AT_ROWS);
         *abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -459,7 +473,7 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
     __syncthreads();
     tc_fence_after();
     uint32_t tmem = *tmem_slot;
-    uint32_t tmem_s = tmem, tmem_pv = tmem + AT_KEYS;
+    uint32_t tmem_s = tmem, tmem_pv = tmem + 2 * AT_KEYS;
     int *err = &g_attn_tc_error;
     // q, the keys and the values were written by the kernel before this one
     pdl_trigger();
@@ -510,37 +524,45 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
         // --------------------------------------------------------------- MMAs
         constexpr uint32_t idesc_s = instr_desc_bf16(AT_ROWS, AT_KEYS, false);
         constexpr uint32_t idesc_pv = instr_desc_bf16(AT_ROWS, HD, true);
-        bool ok = mbar_wait(bar(0), 0, abort, err, 22);
         uint32_t q_a = smem_u32(q_s), p_a = smem_u32(p_s);
-        for (int it = 0; it < n_chunks && ok; it++) {
+        // the scores of chunk `it` into S buffer it % 2
+        auto issue_s = [&](int it) -> bool {
             int s = it % AT_STAGES;
-            uint32_t ph = (it / AT_STAGES) & 1;
-            ok = mbar_wait(bar(1 + s), ph, abort, err, 23);
-            if (!ok)
-                break;
+            if (!mbar_wait(bar(1 + s), (it / AT_STAGES) & 1, abort, err, 23))
+                return false;
             tc_fence_after();
             uint32_t k_a = smem_u32(kv_s + s * Cfg::KV_STAGE);
-            uint32_t v_a = k_a + NB * BLK_BYTES;
 #pragma unroll
             for (int kk = 0; kk < HD / 16; kk++) {
                 uint32_t off = (kk / 4) * BLK_BYTES + (kk % 4) * 32;
-                tc_mma(tmem_s, smem_desc_sw128(q_a + off, 16, 1024),
+                tc_mma(tmem_s + (it & 1) * AT_KEYS, smem_desc_sw128(q_a + off, 16, 1024),
                        smem_desc_sw128(k_a + off, 16, 1024), idesc_s, kk != 0);
             }
-            tc_commit(bar(5));
-            ok = mbar_wait(bar(6), it & 1, abort, err, 25);       // P is in shared memory
+            tc_commit(bar(5 + (it & 1)));
+            return true;
+        };
+        bool ok = mbar_wait(bar(0), 0, abort, err, 22) && issue_s(0);
+        for (int it = 0; it < n_chunks && ok; it++) {
+            // this chunk's K and V stay in their stage until its P V is done, so the
+            // next chunk's scores need the other stage: two stages suffice
+            if (it + 1 < n_chunks)
+                ok = issue_s(it + 1);
+            ok = ok && mbar_wait(bar(7 + (it & 1)), (it >> 1) & 1, abort, err, 25);   // P is there
             if (ok && it > 0)
-                ok = mbar_wait(bar(8), (it - 1) & 1, abort, err, 26);   // the last PV was read
+                ok = mbar_wait(bar(10), (it - 1) & 1, abort, err, 26);   // the last PV was read
             if (!ok)
                 break;
             tc_fence_after();
+            int s = it % AT_STAGES;
+            uint32_t v_a = smem_u32(kv_s + s * Cfg::KV_STAGE) + NB * BLK_BYTES;
+            uint32_t pb = p_a + (it & 1) * Cfg::P_BYTES;
 #pragma unroll
             for (int kk = 0; kk < AT_KEYS / 16; kk++) {
                 uint32_t p_off = (kk / 4) * BLK_BYTES + (kk % 4) * 32;
-                tc_mma(tmem_pv, smem_desc_sw128(p_a + p_off, 16, 1024),
+                tc_mma(tmem_pv, smem_desc_sw128(pb + p_off, 16, 1024),
                        smem_desc_sw128(v_a + kk * 16 * 128, BLK_BYTES, 1024), idesc_pv, kk != 0);
             }
-            tc_commit(bar(7));
+            tc_commit(bar(9));
             tc_commit(bar(3 + s));
         }
     } else if (warp >= 2) {
@@ -555,21 +577,42 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
         uint32_t lane_addr = (uint32_t)(qw * 32) << 16;
         const float c2 = scale * 1.4426950408889634f;      // scores in units of log2(e)
         float m_run = -INFINITY, l_run = 0.0f;              // l_run: this thread's keys only
+        float alpha = 0.0f;                                 // of the chunk whose P V is pending
         float o[HH];
 #pragma unroll
         for (int i = 0; i < HH; i++)
             o[i] = 0.0f;
         bool ok = true;
+        // P V of chunk `it` joins the running output, scaled by that chunk's factor
+        auto take_o = [&](int it) {
+            ok = ok && mbar_wait(bar(9), it & 1, abort, err, 28);
+            ok = __all_sync(0xffffffffu, ok);
+            tc_fence_after();
+            if (ok) {
+#pragma unroll
+                for (int db = 0; db < HH / 32; db++) {
+                    float pv[32];
+                    tc_ld32(tmem_pv + lane_addr + hf * HH + db * 32, pv);
+#pragma unroll
+                    for (int i = 0; i < 32; i++)
+                        o[db * 32 + i] = o[db * 32 + i] * alpha + pv[i];
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(bar(10));
+        };
         for (int it = 0; it < n_chunks; it++) {
             int t0 = (c_first + it) * AT_KEYS + hf * 64;    // this thread's first key
-            ok = ok && mbar_wait(bar(5), it & 1, abort, err, 27);
+            float *swap = pair + (it & 1) * 2 * AT_ROWS;
+            ok = ok && mbar_wait(bar(5 + (it & 1)), (it >> 1) & 1, abort, err, 27);
             ok = __all_sync(0xffffffffu, ok);
             tc_fence_after();
             uint32_t raw[64];
             float mx = -INFINITY;
             if (ok) {
-                tc_ld32_nowait(tmem_s + lane_addr + hf * 64, raw);
-                tc_ld32_nowait(tmem_s + lane_addr + hf * 64 + 32, raw + 32);
+                uint32_t sa = tmem_s + (it & 1) * AT_KEYS + lane_addr + hf * 64;
+                tc_ld32_nowait(sa, raw);
+                tc_ld32_nowait(sa + 32, raw + 32);
                 tc_ld_wait();
 #pragma unroll
                 for (int i = 0; i < 64; i++) {
@@ -579,16 +622,19 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
                     mx = fmaxf(mx, v);
                 }
             }
-            pair[hf * AT_ROWS + r] = mx;
+            swap[hf * AT_ROWS + r] = mx;
             named_barrier(1, 2 * AT_ROWS);
-            mx = fmaxf(mx, pair[(hf ^ 1) * AT_ROWS + r]);
+            mx = fmaxf(mx, swap[(hf ^ 1) * AT_ROWS + r]);
+            // the chunk before this one goes into the output with ITS factor
+            if (it > 0)
+                take_o(it - 1);
             float m_new = fmaxf(m_run, mx);
-            float alpha = m_run == -INFINITY ? 0.0f : exp2f(m_run - m_new);
+            alpha = m_run == -INFINITY ? 0.0f : exp2f(m_run - m_new);
             if (m_new == -INFINITY)
                 alpha = 1.0f;
             float l_chunk = 0.0f;
             if (ok) {
-                uint8_t *blk = p_s + hf * BLK_BYTES;
+                uint8_t *blk = p_s + (it & 1) * Cfg::P_BYTES + hf * BLK_BYTES;
 #pragma unroll
                 for (int q8 = 0; q8 < 8; q8++) {
                     uint32_t w[4];
@@ -607,28 +653,11 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
             }
             fence_async_smem();
             tc_fence_before();
-            mbar_arrive(bar(6));
+            mbar_arrive(bar(7 + (it & 1)));
             l_run = l_run * alpha + l_chunk;
             m_run = m_new;
-            // the pair buffer is read by the partner before the next chunk writes it:
-            // the partner passes the barrier above only after both have written, and
-            // writes again only after the barrier of the next chunk
-            ok = ok && mbar_wait(bar(7), it & 1, abort, err, 28);
-            ok = __all_sync(0xffffffffu, ok);
-            tc_fence_after();
-            if (ok) {
-#pragma unroll
-                for (int db = 0; db < HH / 32; db++) {
-                    float pv[32];
-                    tc_ld32(tmem_pv + lane_addr + hf * HH + db * 32, pv);
-#pragma unroll
-                    for (int i = 0; i < 32; i++)
-                        o[db * 32 + i] = o[db * 32 + i] * alpha + pv[i];
-                }
-            }
-            tc_fence_before();
-            mbar_arrive(bar(8));
         }
+        take_o(n_chunks - 1);
         // the row's sum: both threads' keys
         named_barrier(1, 2 * AT_ROWS);
         pair[hf * AT_ROWS + r] = l_run;
@@ -1079,12 +1108,12 @@ extern "C" int jb_attn_tc_prefill(const void *q, const void *k_cache, const void
         if (!attr_set) {                                                                       \
             if (cudaFuncSetAttribute(attn_tc_prefill_kernel<HDV>,                              \
                                      cudaFuncAttributeMaxDynamicSharedMemorySize,              \
-                                     AttnCfg<HDV>::SMEM_BYTES) != cudaSuccess)                 \
+                                     PrefillCfg<HDV>::SMEM_BYTES) != cudaSuccess)              \
                 return JB_ELAUNCH;                                                             \
             attr_set = true;                                                                   \
         }                                                                                      \
         launch(attn_tc_prefill_kernel<HDV>, dim3(n_blocks, nkv), PF_THREADS,                   \
-               AttnCfg<HDV>::SMEM_BYTES, st, mq, mk, mv, qblk, block_table, bt_stride,         \
+               PrefillCfg<HDV>::SMEM_BYTES, st, mq, mk, mv, qblk, block_table, bt_stride,      \
                (bf16 *)out, nh, nkv, G, R, window, scale);                                     \
     } while (0)
     if (hd == 128)
