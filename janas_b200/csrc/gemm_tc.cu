@@ -198,48 +198,92 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         ok = __all_sync(0xffffffffu, ok);   // the TMEM loads below are warp-wide
         tc_fence_after();
         uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16);
+        // The accumulator is read 32 columns (tokens) at a time; the read of the
+        // next 32 is in flight while the last 32 are stored.
         if (EPI == EPI_PARTIAL) {
             float *dst = out + (size_t)blockIdx.z * n * m;
-#pragma unroll 1
-            for (int t = 0; t < MT; t++) {
-                int ft = f + t * second_off;
-#pragma unroll 1
-                for (int c0 = 0; c0 < BN; c0 += 16) {
-                    float v[16];
-                    if (ok)
-                        tc_ld16(taddr + t * BN + c0, v);
-                    if (!ok) {
+            constexpr int COLS = MT * BN;           // tile t's tokens are columns [t BN, t BN + BN)
+            if constexpr (BN < 32) {
+                float v[16];
+                if (ok)
+                    tc_ld16(taddr, v);
+                if (ok && f < m) {
 #pragma unroll
-                        for (int j = 0; j < 16; j++)
-                            v[j] = 0.0f;
+                    for (int j = 0; j < 16; j++)
+                        if (n0 + j < n)
+                            dst[(size_t)(n0 + j) * m + f] = v[j];
+                }
+            } else {
+                uint32_t va[32], vb[32];
+                auto store32 = [&](const uint32_t *v, int c) {
+                    int t = c / BN, c0 = c - t * BN;
+                    int ft = f + t * second_off;
+                    if (ft >= m)
+                        return;
+                    float *p = dst + (size_t)(n0 + c0) * m + ft;
+                    if (n0 + c0 + 32 <= n) {        // the usual case: no token is cut off
+#pragma unroll
+                        for (int j = 0; j < 32; j++, p += m)
+                            *p = __uint_as_float(v[j]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; j++, p += m)
+                            if (n0 + c0 + j < n)
+                                *p = __uint_as_float(v[j]);
                     }
-                    if (ft < m) {
-#pragma unroll
-                        for (int j = 0; j < 16; j++) {
-                            int tok = n0 + c0 + j;
-                            if (tok < n)
-                                dst[(size_t)tok * m + ft] = v[j];
+                };
+                if (ok) {
+                    tc_ld32_nowait(taddr, va);
+#pragma unroll 1
+                    for (int c = 0; c < COLS; c += 64) {
+                        tc_ld_wait();
+                        if (c + 32 < COLS)
+                            tc_ld32_nowait(taddr + c + 32, vb);
+                        store32(va, c);
+                        if (c + 32 < COLS) {
+                            tc_ld_wait();
+                            if (c + 64 < COLS)
+                                tc_ld32_nowait(taddr + c + 64, va);
+                            store32(vb, c + 32);
                         }
                     }
                 }
             }
         } else {
             int ff = second_off;
-#pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 16) {
-                float g[16], u[16];
-                if (ok) {
-                    tc_ld16(taddr + c0, g);
-                    tc_ld16(taddr + BN + c0, u);
-                }
-                if (ok && f < ff) {
+            uint32_t ga[32], ua[32], gb[32], ub[32];
+            auto act32 = [&](const uint32_t *g, const uint32_t *u, int c0) {
+                if (f >= ff)
+                    return;
+                bf16 *p = out_act + (size_t)(n0 + c0) * ff + f;
+                bool whole = n0 + c0 + 32 <= n;
 #pragma unroll
-                    for (int j = 0; j < 16; j++) {
-                        int tok = n0 + c0 + j;
-                        if (tok < n) {
-                            float h = g[j] / (1.0f + expf(-g[j])) * u[j];
-                            out_act[(size_t)tok * ff + f] = __float2bfloat16_rn(h);
+                for (int j = 0; j < 32; j++, p += ff) {
+                    if (whole || n0 + c0 + j < n) {
+                        float gv = __uint_as_float(g[j]), uv = __uint_as_float(u[j]);
+                        float h = gv / (1.0f + __expf(-gv)) * uv;
+                        *p = __float2bfloat16_rn(h);
+                    }
+                }
+            };
+            if (ok) {
+                tc_ld32_nowait(taddr, ga);
+                tc_ld32_nowait(taddr + BN, ua);
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 64) {
+                    tc_ld_wait();
+                    if (c + 32 < BN) {
+                        tc_ld32_nowait(taddr + c + 32, gb);
+                        tc_ld32_nowait(taddr + BN + c + 32, ub);
+                    }
+                    act32(ga, ua, c);
+                    if (c + 32 < BN) {
+                        tc_ld_wait();
+                        if (c + 64 < BN) {
+                            tc_ld32_nowait(taddr + c + 64, ga);
+                            tc_ld32_nowait(taddr + BN + c + 64, ua);
                         }
+                        act32(gb, ub, c + 32);
                     }
                 }
             }
