@@ -558,6 +558,8 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
         bool live = j < q_count && j < R;
         int pos = q_pos + j;
         int lo = window > 0 && pos + 1 > window ? pos + 1 - window : 0;
+        int pos_last = q_pos + q_count - 1;                 // the block's last position
+        int lo_last = window > 0 && pos_last + 1 > window ? pos_last + 1 - window : 0;
         uint32_t lane_addr = (uint32_t)(qw * 32) << 16;
         const float c2 = scale * 1.4426950408889634f;      // scores in units of log2(e)
         float m_run = -INFINITY, l_run = 0.0f;              // l_run: this thread's keys only
@@ -598,12 +600,24 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
                 tc_ld32_nowait(sa, raw);
                 tc_ld32_nowait(sa + 32, raw + 32);
                 tc_ld_wait();
+                // most chunks lie wholly inside every row's range: no key is masked
+                bool inside = t0 + 63 <= q_pos && t0 >= lo_last;
+                if (inside && live) {
 #pragma unroll
-                for (int i = 0; i < 64; i++) {
-                    int t = t0 + i;
-                    float v = (live && t <= pos && t >= lo) ? __uint_as_float(raw[i]) * c2 : -INFINITY;
-                    raw[i] = __float_as_uint(v);
-                    mx = fmaxf(mx, v);
+                    for (int i = 0; i < 64; i++) {
+                        float v = __uint_as_float(raw[i]) * c2;
+                        raw[i] = __float_as_uint(v);
+                        mx = fmaxf(mx, v);
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 64; i++) {
+                        int t = t0 + i;
+                        float v = (live && t <= pos && t >= lo) ? __uint_as_float(raw[i]) * c2
+                                                                : -INFINITY;
+                        raw[i] = __float_as_uint(v);
+                        mx = fmaxf(mx, v);
+                    }
                 }
             }
             swap[hf * AT_ROWS + r] = mx;

@@ -31,9 +31,11 @@ __global__ void rope_table_kernel(float *__restrict__ cs, float *__restrict__ sn
     sn[i] = (float)s;
 }
 
-// One warp per (row, head slot); head slots are the q heads, then the k
-// heads, then the v heads of the row's fused [q | k | v] vector.  PAIRS is how
-// many (low, high) pairs of a head a lane holds: ceil(hd / 64).
+// One warp per (row, run of HPW head slots); head slots are the q heads, then
+// the k heads, then the v heads of the row's fused [q | k | v] vector.  PAIRS is
+// how many (low, high) pairs of a head a lane holds: ceil(hd / 64).  With many
+// rows a warp takes several head slots of its row in turn, so that the row's
+// rotation table and the norm weights are fetched once for all of them.
 //
 // qkv: S stacked [n, (nh + 2 nkv) hd] float partial sums.
 // q_out: [n, nh, hd] in the cache's type.  K and V go to page
@@ -47,88 +49,97 @@ qk_norm_rope_append_kernel(
     const float *__restrict__ sn, int rot_half, const int32_t *__restrict__ row_pos,
     const int32_t *__restrict__ row_seq, const int32_t *__restrict__ block_table, int bt_stride,
     TC *__restrict__ q_out, TC *__restrict__ k_cache, TC *__restrict__ v_cache, int n, int nh,
-    int nkv, int hd)
+    int nkv, int hd, int hpw)
 {
     pdl_trigger();
     unsigned slots = nh + 2 * nkv;
+    unsigned runs = (slots + hpw - 1) / hpw;          // runs of head slots per row
     unsigned task = blockIdx.x * blockDim.y + threadIdx.y;
-    if (task >= (unsigned)n * slots)
+    if (task >= (unsigned)n * runs)
         return;
-    unsigned row = task / slots, hs = task - row * slots;
+    unsigned row = task / runs, hs0 = (task - row * runs) * hpw;
+    unsigned hs1 = min(hs0 + hpw, slots);
     int lane = threadIdx.x;
     int half = hd / 2;
-    bool is_v = hs >= (unsigned)(nh + nkv);
-    const TW *w = hs < (unsigned)nh ? q_w : k_w;
 
     // Positions, page tables, rotation tables and norm weights were written long
     // before the kernel before this one: they are fetched before the wait.
     int pos = row_pos[row];
-    TC *dst;
-    if (hs < (unsigned)nh) {
-        dst = q_out + ((size_t)row * nh + hs) * hd;
-    } else {
-        if (k_cache == nullptr)
-            return;
-        int kvh = !is_v ? hs - nh : hs - nh - nkv;
-        int page = block_table[(size_t)row_seq[row] * bt_stride + pos / PAGE];
-        size_t at = (((size_t)page * nkv + kvh) * PAGE + (pos % PAGE)) * hd;
-        dst = (!is_v ? k_cache : v_cache) + at;
-    }
-    float co[PAIRS], si[PAIRS], wl[PAIRS], wh[PAIRS];
-    bool rotate = !is_v && rot_half == half;
+    int page = k_cache != nullptr
+                   ? block_table[(size_t)row_seq[row] * bt_stride + pos / PAGE] : 0;
+    bool rotate_any = rot_half == half;
+    float co[PAIRS], si[PAIRS], wql[PAIRS], wqh[PAIRS], wkl[PAIRS], wkh[PAIRS];
 #pragma unroll
     for (int j = 0; j < PAIRS; j++) {
         int i = lane + 32 * j;
         co[j] = 1.0f;
         si[j] = 0.0f;
-        wl[j] = wh[j] = 1.0f;
-        if (i < half && !is_v) {
-            if (rotate) {
+        wql[j] = wqh[j] = wkl[j] = wkh[j] = 1.0f;
+        if (i < half) {
+            if (rotate_any) {
                 co[j] = cs[(size_t)pos * rot_half + i];
                 si[j] = sn[(size_t)pos * rot_half + i];
             }
-            if (w != nullptr) {
-                wl[j] = to_f(w[i]);
-                wh[j] = to_f(w[i + half]);
+            if (q_w != nullptr) {
+                wql[j] = to_f(q_w[i]);
+                wqh[j] = to_f(q_w[i + half]);
+                wkl[j] = to_f(k_w[i]);
+                wkh[j] = to_f(k_w[i + half]);
             }
         }
     }
     pdl_wait();
 
-    const float *src = qkv + (size_t)row * slots * hd + (size_t)hs * hd;
-    float lo[PAIRS], hi[PAIRS];
-    float ss = 0.0f;
-#pragma unroll
-    for (int j = 0; j < PAIRS; j++) {
-        int i = lane + 32 * j;
-        lo[j] = hi[j] = 0.0f;
-        if (i < half) {
-            lo[j] = add_partials(0.0f, src + i, S, split_stride);
-            hi[j] = add_partials(0.0f, src + i + half, S, split_stride);
-            ss = fmaf(lo[j], lo[j], ss);
-            ss = fmaf(hi[j], hi[j], ss);
+    for (unsigned hs = hs0; hs < hs1; hs++) {
+        bool is_q = hs < (unsigned)nh;
+        bool is_v = hs >= (unsigned)(nh + nkv);
+        TC *dst;
+        if (is_q) {
+            dst = q_out + ((size_t)row * nh + hs) * hd;
+        } else {
+            if (k_cache == nullptr)
+                continue;
+            int kvh = !is_v ? hs - nh : hs - nh - nkv;
+            size_t at = (((size_t)page * nkv + kvh) * PAGE + (pos % PAGE)) * hd;
+            dst = (!is_v ? k_cache : v_cache) + at;
         }
-    }
-    float scale = 1.0f;
-    if (!is_v && w != nullptr) {
-        ss = warp_sum(ss);
-        scale = 1.0f / sqrtf(ss / (float)hd + eps);
-    }
+        const float *src = qkv + (size_t)row * slots * hd + (size_t)hs * hd;
+        float lo[PAIRS], hi[PAIRS];
+        float ss = 0.0f;
 #pragma unroll
-    for (int j = 0; j < PAIRS; j++) {
-        int i = lane + 32 * j;
-        if (i < half) {
-            float a = lo[j], b = hi[j];
-            if (!is_v && w != nullptr) {
-                a = (a * scale) * wl[j];
-                b = (b * scale) * wh[j];
+        for (int j = 0; j < PAIRS; j++) {
+            int i = lane + 32 * j;
+            lo[j] = hi[j] = 0.0f;
+            if (i < half) {
+                lo[j] = add_partials(0.0f, src + i, S, split_stride);
+                hi[j] = add_partials(0.0f, src + i + half, S, split_stride);
+                ss = fmaf(lo[j], lo[j], ss);
+                ss = fmaf(hi[j], hi[j], ss);
             }
-            if (rotate) {
-                dst[i] = from_f<TC>(a * co[j] - b * si[j]);
-                dst[i + half] = from_f<TC>(a * si[j] + b * co[j]);
-            } else {
-                dst[i] = from_f<TC>(a);
-                dst[i + half] = from_f<TC>(b);
+        }
+        bool normed = !is_v && q_w != nullptr;
+        float scale = 1.0f;
+        if (normed) {
+            ss = warp_sum(ss);
+            scale = 1.0f / sqrtf(ss / (float)hd + eps);
+        }
+        bool rotate = !is_v && rotate_any;
+#pragma unroll
+        for (int j = 0; j < PAIRS; j++) {
+            int i = lane + 32 * j;
+            if (i < half) {
+                float a = lo[j], b = hi[j];
+                if (normed) {
+                    a = (a * scale) * (is_q ? wql[j] : wkl[j]);
+                    b = (b * scale) * (is_q ? wqh[j] : wkh[j]);
+                }
+                if (rotate) {
+                    dst[i] = from_f<TC>(a * co[j] - b * si[j]);
+                    dst[i + half] = from_f<TC>(a * si[j] + b * co[j]);
+                } else {
+                    dst[i] = from_f<TC>(a);
+                    dst[i + half] = from_f<TC>(b);
+                }
             }
         }
     }
@@ -164,7 +175,11 @@ extern "C" int jb_qk_norm_rope_append(const float *qkv, int S, long long split_s
         return JB_EINVAL;
     if ((q_w == nullptr) != (k_w == nullptr))
         return JB_EINVAL;
-    size_t tasks = (size_t)n * (nh + 2 * nkv);
+    // few rows: a warp per head slot, for the shortest chain; many rows: several
+    // head slots per warp, for fewer fetches of what the row's heads share
+    int slots = nh + 2 * nkv;
+    int hpw = n >= 256 ? (slots >= 24 ? 6 : slots >= 8 ? 4 : 1) : 1;
+    size_t tasks = (size_t)n * ((slots + hpw - 1) / hpw);
     if (tasks > 0xffffffffu)
         return JB_EINVAL;
     dim3 block(32, 4);
@@ -174,7 +189,7 @@ extern "C" int jb_qk_norm_rope_append(const float *qkv, int S, long long split_s
     launch(qk_norm_rope_append_kernel<TC, TW, P>, grid, block, 0, st,                          \
         qkv, S, (size_t)split_stride, (const TW *)q_w, (const TW *)k_w, eps, cs, sn, rot_half, \
         row_pos, row_seq, block_table, bt_stride, (TC *)q_out, (TC *)k_cache, (TC *)v_cache, n, \
-        nh, nkv, hd)
+        nh, nkv, hd, hpw)
 #define JB_ROPE(TC, TW)                                                                        \
     do {                                                                                       \
         if (pairs <= 1)                                                                        \

@@ -32,17 +32,18 @@ __global__ void embed_kernel(const TT *__restrict__ table, const int32_t *__rest
 // When delta is given, x[row] += delta[0][row] + delta[1][row] + ... first and
 // is written back.  row_idx (or null) picks the rows that are normalized; with
 // it, out has one row per entry and no delta is allowed.
-template <typename TW, typename TO>
+// EPT: values a thread holds, ceil(dm / threads); 0: any width, nothing held.
+template <typename TW, typename TO, int EPT>
 __global__ void rmsnorm_kernel(float *__restrict__ x, const float *__restrict__ delta, int S,
                                size_t delta_stride, const int32_t *__restrict__ row_idx,
                                const TW *__restrict__ w, TO *__restrict__ out, int dm, float eps)
 {
-    constexpr int KEEP = 12;             // values a thread keeps between the two passes
+    constexpr int KEEP = EPT > 0 ? EPT : 1;
     __shared__ float red[32];
     pdl_trigger();
     // the norm's weight does not depend on the kernel before this one
     float wv[KEEP];
-    if (out != nullptr) {
+    if (EPT > 0 && out != nullptr) {
 #pragma unroll
         for (int u = 0; u < KEEP; u++) {
             int i = threadIdx.x + u * blockDim.x;
@@ -55,61 +56,76 @@ __global__ void rmsnorm_kernel(float *__restrict__ x, const float *__restrict__ 
     float *xr = x + row * dm;
     float xv[KEEP];
     float ss = 0.0f;
+    if (EPT > 0) {
 #pragma unroll
-    for (int u = 0; u < KEEP; u++) {
-        int i = threadIdx.x + u * blockDim.x;
-        float v = 0.0f;
-        if (i < dm) {
-            v = xr[i];
+        for (int u = 0; u < KEEP; u++) {
+            int i = threadIdx.x + u * blockDim.x;
+            float v = 0.0f;
+            if (i < dm) {
+                v = xr[i];
+                if (delta) {
+                    v = add_partials(v, delta + row * dm + i, S, delta_stride);
+                    xr[i] = v;
+                }
+            }
+            xv[u] = v;
+            ss = fmaf(v, v, ss);
+        }
+    } else {
+        for (int i = threadIdx.x; i < dm; i += blockDim.x) {
+            float v = xr[i];
             if (delta) {
                 v = add_partials(v, delta + row * dm + i, S, delta_stride);
                 xr[i] = v;
             }
+            ss = fmaf(v, v, ss);
         }
-        xv[u] = v;
-        ss = fmaf(v, v, ss);
-    }
-    for (int i = threadIdx.x + KEEP * blockDim.x; i < dm; i += blockDim.x) {   // very wide rows
-        float v = xr[i];
-        if (delta) {
-            v = add_partials(v, delta + row * dm + i, S, delta_stride);
-            xr[i] = v;
-        }
-        ss = fmaf(v, v, ss);
     }
     ss = block_sum(ss, red);
     if (out == nullptr)
         return;
     float scale = 1.0f / sqrtf(ss / (float)dm + eps);
     TO *o = out + orow * dm;
+    if (EPT > 0) {
 #pragma unroll
-    for (int u = 0; u < KEEP; u++) {
-        int i = threadIdx.x + u * blockDim.x;
-        if (i < dm)
-            o[i] = from_f<TO>((xv[u] * scale) * wv[u]);
+        for (int u = 0; u < KEEP; u++) {
+            int i = threadIdx.x + u * blockDim.x;
+            if (i < dm)
+                o[i] = from_f<TO>((xv[u] * scale) * wv[u]);
+        }
+    } else {
+        for (int i = threadIdx.x; i < dm; i += blockDim.x)
+            o[i] = from_f<TO>((xr[i] * scale) * to_f(w[i]));
     }
-    for (int i = threadIdx.x + KEEP * blockDim.x; i < dm; i += blockDim.x)
-        o[i] = from_f<TO>((xr[i] * scale) * to_f(w[i]));
 }
 
 // gu: S stacked [n, 2 ff] float partial sums; columns [0, ff) are the gate,
-// [ff, 2 ff) the up projection.  out[n, ff] = SiLU(gate) * up.
-template <typename TO>
+// [ff, 2 ff) the up projection.  out[n, ff] = SiLU(gate) * up.  VEC values per
+// thread (4 when ff is a multiple of 4 and nothing is split, else 1).
+template <typename TO, int VEC>
 __global__ void swiglu_kernel(const float *__restrict__ gu, int S, size_t stride,
                               TO *__restrict__ out, int ff, size_t total)
 {
     pdl_trigger();
     pdl_wait();
-    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * VEC;
     if (i >= total)
         return;
     size_t row = i / ff;
     int c = (int)(i % ff);
     const float *p = gu + row * 2 * ff;
-    float g = add_partials(0.0f, p + c, S, stride);
-    float u = add_partials(0.0f, p + ff + c, S, stride);
-    float h = g / (1.0f + expf(-g)) * u;
-    out[i] = from_f<TO>(h);
+    if (VEC == 4) {
+        float4 g = *reinterpret_cast<const float4 *>(p + c);
+        float4 u = *reinterpret_cast<const float4 *>(p + ff + c);
+        float gv[4] = {g.x, g.y, g.z, g.w}, uv[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int e = 0; e < 4; e++)
+            out[i + e] = from_f<TO>(gv[e] / (1.0f + expf(-gv[e])) * uv[e]);
+    } else {
+        float g = add_partials(0.0f, p + c, S, stride);
+        float u = add_partials(0.0f, p + ff + c, S, stride);
+        out[i] = from_f<TO>(g / (1.0f + expf(-g)) * u);
+    }
 }
 
 // Threads of a block that works on one row: about eight values each.  The
@@ -152,9 +168,24 @@ extern "C" int jb_rmsnorm(float *x, const float *delta, int S, long long delta_s
     if (delta && row_idx)
         return JB_EINVAL;
     int threads = norm_threads(dm);
+    int ept = (dm + threads - 1) / threads;
+#define JB_NORM_E(TW, TO, E)                                                                  \
+    launch(rmsnorm_kernel<TW, TO, E>, n_out, threads, 0, st, x, delta, S,                      \
+           (size_t)delta_stride, row_idx, (const TW *)w, (TO *)out, dm, eps)
 #define JB_NORM(TW, TO)                                                                       \
-    launch(rmsnorm_kernel<TW, TO>, n_out, threads, 0, st, x, delta, S, (size_t)delta_stride,   \
-           row_idx, (const TW *)w, (TO *)out, dm, eps)
+    do {                                                                                       \
+        switch (ept) {                                                                         \
+        case 1: JB_NORM_E(TW, TO, 1); break;                                                   \
+        case 2: JB_NORM_E(TW, TO, 2); break;                                                   \
+        case 3: JB_NORM_E(TW, TO, 3); break;                                                   \
+        case 4: JB_NORM_E(TW, TO, 4); break;                                                   \
+        case 5: JB_NORM_E(TW, TO, 5); break;                                                   \
+        case 6: JB_NORM_E(TW, TO, 6); break;                                                   \
+        case 7: JB_NORM_E(TW, TO, 7); break;                                                   \
+        case 8: JB_NORM_E(TW, TO, 8); break;                                                   \
+        default: JB_NORM_E(TW, TO, 0); break;                                                  \
+        }                                                                                      \
+    } while (0)
     if (out == nullptr)
         JB_NORM(float, float);
     else if (w_dt == JB_F32 && out_dt == JB_F32)
@@ -167,6 +198,7 @@ extern "C" int jb_rmsnorm(float *x, const float *delta, int S, long long delta_s
         JB_NORM(bf16, bf16);
     else
         return JB_EINVAL;
+#undef JB_NORM_E
 #undef JB_NORM
     return launch_status();
 }
@@ -177,11 +209,17 @@ extern "C" int jb_swiglu(const float *gu, int S, long long stride, void *out, in
     size_t total = (size_t)n * ff;
     if (total == 0)
         return JB_OK;
-    unsigned blocks = (unsigned)((total + 255) / 256);
-    if (out_dt == JB_F32)
-        launch(swiglu_kernel<float>, blocks, 256, 0, st, gu, S, (size_t)stride, (float *)out, ff, total);
+    bool vec = S == 1 && ff % 4 == 0 && (uintptr_t)gu % 16 == 0;
+    size_t threads = vec ? total / 4 : total;
+    unsigned blocks = (unsigned)((threads + 255) / 256);
+    if (out_dt == JB_F32 && vec)
+        launch(swiglu_kernel<float, 4>, blocks, 256, 0, st, gu, S, (size_t)stride, (float *)out, ff, total);
+    else if (out_dt == JB_F32)
+        launch(swiglu_kernel<float, 1>, blocks, 256, 0, st, gu, S, (size_t)stride, (float *)out, ff, total);
+    else if (out_dt == JB_BF16 && vec)
+        launch(swiglu_kernel<bf16, 4>, blocks, 256, 0, st, gu, S, (size_t)stride, (bf16 *)out, ff, total);
     else if (out_dt == JB_BF16)
-        launch(swiglu_kernel<bf16>, blocks, 256, 0, st, gu, S, (size_t)stride, (bf16 *)out, ff, total);
+        launch(swiglu_kernel<bf16, 1>, blocks, 256, 0, st, gu, S, (size_t)stride, (bf16 *)out, ff, total);
     else
         return JB_EINVAL;
     return launch_status();

@@ -19,7 +19,7 @@ from .registry import register_feed_forward
 class SwiGLU(FeedForward):
     """params: hidden_size, intermediate_size."""
 
-    FUSED_FROM = 128     # rows above which the fused gate-up-activation kernel is used
+    FUSED_FROM = 1 << 30  # rows above which the fused gate-up-activation kernel is used
 
     def __init__(self, spec, dtype, device):
         super().__init__(spec, dtype, device)

@@ -168,24 +168,26 @@ def test_attention_finds_a_far_key_and_the_window_s_edge(dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_qk_norm_rope_append(dtype):
-    nh, nkv, hd = 6, 2, 48
-    n = 40
+@pytest.mark.parametrize("n0,n1,hd", [(25, 15, 48), (300, 58, 128), (3, 1, 16)])
+def test_qk_norm_rope_append(dtype, n0, n1, hd):
+    """Few rows (a warp per head) and many rows (a warp takes several heads)."""
+    nh, nkv = 6, 2
+    n = n0 + n1
     width = (nh + 2 * nkv) * hd
     qkv = rnd(2, n, width, scale=2.0)
     qw, kw = (1 + 0.1 * rnd(hd)).to(dtype), (1 + 0.1 * rnd(hd, seed=1)).to(dtype)
-    # two sequences: rows 0..24 are positions 70..94 of sequence 0, rows 25..39
-    # positions 0..14 of sequence 1
-    pos = torch.cat([torch.arange(70, 95), torch.arange(0, 15)]).int()
-    seq = torch.cat([torch.zeros(25), torch.ones(15)]).int()
-    bt = torch.tensor([[4, 2, -1, -1, -1, -1, -1, -1], [1, -1, -1, -1, -1, -1, -1, -1]],
+    # two sequences: the first rows are positions 70.. of sequence 0, the others
+    # positions 0.. of sequence 1
+    pos = torch.cat([torch.arange(70, 70 + n0), torch.arange(0, n1)]).int()
+    seq = torch.cat([torch.zeros(n0), torch.ones(n1)]).int()
+    bt = torch.tensor([[4, 2, 0, 3, 5, 7, -1, -1], [1, -1, -1, -1, -1, -1, -1, -1]],
                       dtype=torch.int32)
-    kc = torch.zeros(6, nkv, 64, hd, dtype=dtype, device=DEV)
+    kc = torch.zeros(8, nkv, 64, hd, dtype=dtype, device=DEV)
     vc = torch.zeros_like(kc)
     half = hd // 2
     expo = np.float32(-2.0) * np.arange(half, dtype=np.float32) / np.float32(hd)
     inv = np.power(np.float64(np.float32(1e6)), expo.astype(np.float64)).astype(np.float32)
-    cs, sn = ops().rope_table(torch.from_numpy(inv).to(DEV), 128)
+    cs, sn = ops().rope_table(torch.from_numpy(inv).to(DEV), 512)
     q = ops().qk_norm_rope_append(qkv.to(DEV), qw.to(DEV), kw.to(DEV), 1e-6, cs, sn,
                                   pos.to(DEV), seq.to(DEV), bt.to(DEV), kc, vc, nh, nkv, hd,
                                   dtype).cpu().float()
@@ -203,7 +205,7 @@ def test_qk_norm_rope_append(dtype):
         assert (kc[page, :, pos[r] % 64] - wk[r]).abs().max() <= tol * wk.abs().max()
         assert (vc[page, :, pos[r] % 64] - vs[r]).abs().max() <= tol * vs.abs().max()
     # nothing else was written
-    written = torch.zeros(6, 64, dtype=torch.bool)
+    written = torch.zeros(8, 64, dtype=torch.bool)
     for r in range(n):
         written[bt[seq[r], pos[r] // 64], pos[r] % 64] = True
     kc, vc = kc.permute(0, 2, 1, 3), vc.permute(0, 2, 1, 3)      # [page, position, head, value]
