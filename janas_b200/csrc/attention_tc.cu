@@ -699,9 +699,12 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
 // head in scratch; attention.cu's merge kernel joins the CTAs' partials.
 constexpr int DQ_N = 16;                 // heads per MMA (N)
 constexpr int DQ_BLK = DQ_N * 128;       // a block of 16 rows of 128 bytes
-constexpr int DQ_STAGES = 3;
-constexpr int DQ_KV_STAGE = 4 * BLK_BYTES;   // K and V of one chunk, 128 values each
-constexpr int DQ_SMEM = 2 * DQ_BLK + 4 * DQ_BLK + DQ_STAGES * DQ_KV_STAGE + 1024 + 1024;
+// The ring holds units of 32 KB: the keys of a chunk, then its values, then the
+// next chunk's keys ...; three units, so that two CTAs fit an SM and one's waits
+// are filled by the other's work.
+constexpr int DQ_UNITS = 3;
+constexpr int DQ_UNIT = 2 * BLK_BYTES;       // K (or V) of one chunk, 128 values each
+constexpr int DQ_SMEM = 2 * DQ_BLK + 4 * DQ_BLK + DQ_UNITS * DQ_UNIT + 1024 + 1024;
 
 // GP: the group's heads rounded up to a power of two (the row threads' loops).
 template <int GP>
@@ -720,8 +723,8 @@ attn_tc_decode_kernel(const __grid_constant__ CUtensorMap map_q,
     uint8_t *q_s = smem;                       // 2 blocks of [16 heads][64 values]
     uint8_t *p_s = q_s + 2 * DQ_BLK;           // 2 buffers of 2 blocks of [16 heads][64 keys]
     uint8_t *kv_s = p_s + 4 * DQ_BLK;
-    uint64_t *bars = (uint64_t *)(kv_s + DQ_STAGES * DQ_KV_STAGE);
-    // bars: 0 q_full | 1..3 kv_full | 4..6 kv_empty | 7,8 s_full | 9,10 p_full | 11 o_full |
+    uint64_t *bars = (uint64_t *)(kv_s + DQ_UNITS * DQ_UNIT);
+    // bars: 0 q_full | 1..3 unit full | 4..6 unit free | 7,8 s_full | 9,10 p_full | 11 o_full |
     //       12 pv_free
     uint32_t *tmem_slot = (uint32_t *)(bars + 13);
     volatile int *abort = (volatile int *)(tmem_slot + 1);
@@ -748,7 +751,7 @@ attn_tc_decode_kernel(const __grid_constant__ CUtensorMap map_q,
     auto bar = [&](int i) { return bar0 + 8 * i; };
     if (threadIdx.x == 0) {
         mbar_init(bar(0), 1);
-        for (int s = 0; s < DQ_STAGES; s++) {
+        for (int s = 0; s < DQ_UNITS; s++) {
             mbar_init(bar(1 + s), 1);
             mbar_init(bar(4 + s), 1);
         }
@@ -783,15 +786,15 @@ attn_tc_decode_kernel(const __grid_constant__ CUtensorMap map_q,
         tma_load_3d(smem_u32(q_s + DQ_BLK), &map_q, bar(0), 64, kvh * G, q_row);
         const int32_t *bt = block_table + (size_t)seq * bt_stride;
         uint32_t armed = 0, last_parity = 0;
-        for (int it = 0; it < n_chunks; it++) {
-            int s = it % DQ_STAGES;
-            uint32_t ph = (it / DQ_STAGES) & 1;
+        for (int u = 0; u < 2 * n_chunks; u++) {        // unit u: K (even) or V (odd) of chunk u / 2
+            int s = u % DQ_UNITS;
+            uint32_t ph = (u / DQ_UNITS) & 1;
             if (!mbar_wait(bar(4 + s), ph ^ 1, abort, err, 11))
                 break;
-            mbar_expect_tx(bar(1 + s), DQ_KV_STAGE);
-            uint32_t k_dst = smem_u32(kv_s + s * DQ_KV_STAGE);
-            uint32_t v_dst = k_dst + 2 * BLK_BYTES;
-            int c = c_first + it;
+            mbar_expect_tx(bar(1 + s), DQ_UNIT);
+            uint32_t dst = smem_u32(kv_s + s * DQ_UNIT);
+            const CUtensorMap *map = (u & 1) ? &map_v : &map_k;
+            int c = c_first + u / 2;
 #pragma unroll
             for (int pg = 0; pg < 2; pg++) {
                 int idx = 2 * c + pg;
@@ -800,19 +803,15 @@ attn_tc_decode_kernel(const __grid_constant__ CUtensorMap map_q,
                     page = 0;          // not there: every position of it is masked
                 int y = (page * nkv + kvh) * PAGE;
 #pragma unroll
-                for (int b = 0; b < 2; b++) {
-                    tma_load_2d(k_dst + b * BLK_BYTES + pg * (PAGE * 128), &map_k, bar(1 + s),
-                                b * 64, y);
-                    tma_load_2d(v_dst + b * BLK_BYTES + pg * (PAGE * 128), &map_v, bar(1 + s),
-                                b * 64, y);
-                }
+                for (int b = 0; b < 2; b++)
+                    tma_load_2d(dst + b * BLK_BYTES + pg * (PAGE * 128), map, bar(1 + s), b * 64, y);
             }
             armed |= 1u << s;
             last_parity = (last_parity & ~(1u << s)) | (ph << s);
         }
         if (*abort) {
             volatile int never = 0;
-            for (int s = 0; s < DQ_STAGES; s++)
+            for (int s = 0; s < DQ_UNITS; s++)
                 if (armed & (1u << s))
                     mbar_wait(bar(1 + s), (last_parity >> s) & 1, &never, err, 14);
         }
@@ -823,11 +822,11 @@ attn_tc_decode_kernel(const __grid_constant__ CUtensorMap map_q,
         uint32_t q_a = smem_u32(q_s), p_a = smem_u32(p_s);
         // S^T of chunk `it` into S buffer it % 2
         auto issue_s = [&](int it) -> bool {
-            int s = it % DQ_STAGES;
-            if (!mbar_wait(bar(1 + s), (it / DQ_STAGES) & 1, abort, err, 13))
+            int u = 2 * it, s = u % DQ_UNITS;
+            if (!mbar_wait(bar(1 + s), (u / DQ_UNITS) & 1, abort, err, 13))
                 return false;
             tc_fence_after();
-            uint32_t k_a = smem_u32(kv_s + s * DQ_KV_STAGE);
+            uint32_t k_a = smem_u32(kv_s + s * DQ_UNIT);
 #pragma unroll
             for (int kk = 0; kk < HD / 16; kk++)
                 tc_mma(tmem_s + (it & 1) * DQ_N,
@@ -835,6 +834,7 @@ attn_tc_decode_kernel(const __grid_constant__ CUtensorMap map_q,
                        smem_desc_sw128(q_a + (kk / 4) * DQ_BLK + (kk % 4) * 32, 16, 1024),
                        idesc_s, kk != 0);
             tc_commit(bar(7 + (it & 1)));
+            tc_commit(bar(4 + s));              // the keys' unit is free once these are done
             return true;
         };
         bool ok = mbar_wait(bar(0), 0, abort, err, 12) && issue_s(0);
@@ -849,8 +849,12 @@ attn_tc_decode_kernel(const __grid_constant__ CUtensorMap map_q,
             if (!ok)
                 break;
             tc_fence_after();
-            int s = it % DQ_STAGES;
-            uint32_t v_a = smem_u32(kv_s + s * DQ_KV_STAGE) + 2 * BLK_BYTES;
+            int u = 2 * it + 1, s = u % DQ_UNITS;
+            ok = mbar_wait(bar(1 + s), (u / DQ_UNITS) & 1, abort, err, 19);   // the values are there
+            if (!ok)
+                break;
+            tc_fence_after();
+            uint32_t v_a = smem_u32(kv_s + s * DQ_UNIT);
             uint32_t pb = p_a + (it & 1) * 2 * DQ_BLK;
 #pragma unroll
             for (int kk = 0; kk < AT_KEYS / 16; kk++)

@@ -318,9 +318,9 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
     return out
 
 
-def _decode_parts(pairs: int, chunks: int, sms: int = 148) -> int:
+def _decode_parts(pairs: int, chunks: int, sms: int = 296) -> int:
     """Into how many CTAs the chunks of one (token, KV head) pair are cut.  A CTA
-    costs about three chunks' time to set up, and CTAs beyond one per SM come in
+    costs about three chunks' time to set up, and CTAs beyond two per SM come in
     waves: the cut that finishes first by that estimate."""
     best, best_t = 1, None
     for parts in range(1, chunks + 1):

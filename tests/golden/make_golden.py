@@ -86,7 +86,9 @@ int main(void)
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) != 2:
+        sys.exit(__doc__)
+    ref = sys.argv[1]
     here = os.path.dirname(os.path.abspath(__file__))
     with tempfile.TemporaryDirectory() as tmp:
         drv = os.path.join(tmp, "driver.c")
