@@ -9,7 +9,7 @@ from janas_b200.config import (ConfigError, ModelSpec, PartSpec, Qwen3Config, Ru
 from tiny import TINY
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E", "F"])
 def test_reads_every_key(name):
     d = TINY[name]
     c = config_from_dict(d)

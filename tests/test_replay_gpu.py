@@ -28,7 +28,7 @@ FP32_CUT_TOL = 0.0
 BF16_CUT_TOL = 1.5e-2
 
 LENGTHS = {"A": [7, 1, 13, 70, 127], "B": [1, 5, 17, 33, 130, 250], "C": [3, 40, 64, 65, 200, 430],
-           "D": [1, 31, 64, 129, 300, 500], "E": [2, 63, 128, 257, 600]}
+           "D": [1, 31, 64, 129, 300, 500], "E": [2, 63, 128, 257, 600], "F": [1, 9, 65, 190]}
 
 
 def requests(name):
@@ -61,7 +61,7 @@ def check_against_plain(name, dtype, got, reqs, ids):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E", "F"])
 def test_whole(name, dtype):
     reqs = requests(name)
     eng = engine(name, dtype)
@@ -72,7 +72,7 @@ def test_whole(name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E", "F"])
 def test_last_32_one_by_one(name, dtype):
     reqs = requests(name)
     eng = engine(name, dtype)
@@ -104,7 +104,7 @@ def batches_for(name):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E", "F"])
 def test_unequal_batches_with_slot_reuse(name, dtype):
     from janas_b200.engine import Engine
     batches = batches_for(name)

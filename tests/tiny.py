@@ -44,8 +44,16 @@ TINY_E = dict(
     use_sliding_window=True, sliding_window=150,
     layer_types=["sliding_attention", "full_attention", "full_attention"])
 
-TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E}
-SEEDS = {"A": 0, "B": 1, "C": 2, "D": 3, "E": 4}
+# sizes that are multiples of nothing: width 50 (rows of 100 bytes: the tensor-core
+# product refuses them and the plain one takes over), as many KV heads as heads
+TINY_F = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3",
+    num_hidden_layers=2, hidden_size=50, num_attention_heads=3, num_key_value_heads=3,
+    head_dim=16, intermediate_size=90, vocab_size=123, rope_theta=7777.0,
+    rms_norm_eps=1e-4, tie_word_embeddings=True, max_position_embeddings=200)
+
+TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E, "F": TINY_F}
+SEEDS = {"A": 0, "B": 1, "C": 2, "D": 3, "E": 4, "F": 5}
 
 
 def tokens(rng: np.random.Generator, n: int, vocab: int):
