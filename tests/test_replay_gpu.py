@@ -12,19 +12,24 @@ from tiny import TINY, tokens
 
 pytestmark = pytest.mark.gpu
 
-# Largest |difference| over largest |logit| of a request.
-# float32: sums in another order, another exp and sincos: a few 1e-6.
-FP32_TOL = 2e-5
+# Largest |difference| over largest |logit| of a request.  Measured on the six
+# tiny configurations: float32 up to 1e-6 against the plain model; bfloat16 up to
+# 6e-3 against the plain model and 5e-3 against the plain model that rounds at the
+# same places; the limits below leave a factor of three to five.
+# float32: sums in another order, another exp and sincos.
+FP32_TOL = 5e-6
 # bfloat16 against the plain implementation that rounds at the same places: what
 # is left is an occasional value that rounds the other way (2^-9 of one
-# activation) carried through the layers.
+# activation) carried through the layers, and the softmax weights, which the
+# tensor-core attention rounds to bfloat16 before they meet the values.
 BF16_SAME_ROUNDING_TOL = 1.5e-2
 # bfloat16 against exact float32: the rounding itself (2^-9 per stored value).
-BF16_TOL = 4e-2
+BF16_TOL = 2e-2
 # float32 engine against itself under another cut: every kernel adds in an order
-# that does not depend on the cut.
+# that does not depend on the cut, so the logits are the same bits.
 FP32_CUT_TOL = 0.0
-# bfloat16 engine against itself under another cut
+# bfloat16 engine against itself under another cut: a prompt's rows go through
+# other tile shapes of the tensor-core kernels than a single decoded token.
 BF16_CUT_TOL = 1.5e-2
 
 LENGTHS = {"A": [7, 1, 13, 70, 127], "B": [1, 5, 17, 33, 130, 250], "C": [3, 40, 64, 65, 200, 430],
