@@ -600,25 +600,24 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
                 tc_ld32_nowait(sa, raw);
                 tc_ld32_nowait(sa + 32, raw + 32);
                 tc_ld_wait();
-                // most chunks lie wholly inside every row's range: no key is masked
+                // most chunks lie wholly inside every row's range: no key is masked.
+                // The maximum is taken over the raw scores (the scale is positive)
+                // and scaled once; the scale itself goes into the exponent's FMA.
                 bool inside = t0 + 63 <= q_pos && t0 >= lo_last;
                 if (inside && live) {
 #pragma unroll
-                    for (int i = 0; i < 64; i++) {
-                        float v = __uint_as_float(raw[i]) * c2;
-                        raw[i] = __float_as_uint(v);
-                        mx = fmaxf(mx, v);
-                    }
+                    for (int i = 0; i < 64; i++)
+                        mx = fmaxf(mx, __uint_as_float(raw[i]));
                 } else {
 #pragma unroll
                     for (int i = 0; i < 64; i++) {
                         int t = t0 + i;
-                        float v = (live && t <= pos && t >= lo) ? __uint_as_float(raw[i]) * c2
-                                                                : -INFINITY;
+                        float v = (live && t <= pos && t >= lo) ? __uint_as_float(raw[i]) : -INFINITY;
                         raw[i] = __float_as_uint(v);
                         mx = fmaxf(mx, v);
                     }
                 }
+                mx *= c2;
             }
             swap[hf * AT_ROWS + r] = mx;
             named_barrier(1, 2 * AT_ROWS);
@@ -631,6 +630,9 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
             if (m_new == -INFINITY)
                 alpha = 1.0f;
             float l_chunk = 0.0f;
+            // with nothing visible yet the maximum is -inf: subtract 0 instead, every
+            // score is -inf and every weight 0
+            float m_use = m_new == -INFINITY ? 0.0f : m_new;
             if (ok) {
                 uint8_t *blk = p_s + (it & 1) * Cfg::P_BYTES + hf * BLK_BYTES;
 #pragma unroll
@@ -638,10 +640,12 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
                     uint32_t w[4];
 #pragma unroll
                     for (int e = 0; e < 4; e++) {
+                        // a masked score is -inf and m_new is finite here or the row
+                        // is not live: 2^(-inf) = 0
                         float s0 = __uint_as_float(raw[8 * q8 + 2 * e]);
                         float s1 = __uint_as_float(raw[8 * q8 + 2 * e + 1]);
-                        float p0 = s0 == -INFINITY ? 0.0f : exp2f(s0 - m_new);
-                        float p1 = s1 == -INFINITY ? 0.0f : exp2f(s1 - m_new);
+                        float p0 = fast_exp2(fmaf(s0, c2, -m_use));
+                        float p1 = fast_exp2(fmaf(s1, c2, -m_use));
                         l_chunk += p0 + p1;
                         __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
                         w[e] = *reinterpret_cast<uint32_t *>(&pk);

@@ -201,6 +201,14 @@ __host__ __device__ constexpr uint32_t instr_desc_bf16(int m, int n, bool b_mn_m
            ((uint32_t)(m >> 4) << 24);
 }
 
+// 2^x in one instruction (ex2.approx.ftz: relative error about 2^-22; -inf gives 0).
+__device__ __forceinline__ float fast_exp2(float x)
+{
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 // A barrier among `count` threads of the CTA (count a multiple of 32), by number.
 __device__ __forceinline__ void named_barrier(int id, int count)
 {
