@@ -41,7 +41,7 @@ __global__ void rope_table_kernel(float *__restrict__ cs, float *__restrict__ sn
 // q_out: [n, nh, hd] in the cache's type.  K and V go to page
 // block_table[seq][pos / PAGE] of k_cache / v_cache, which are laid out
 // [page][kv head][PAGE][hd].
-template <typename TC, typename TW, int PAIRS>
+template <typename TC, typename TW, int PAIRS, int HPW>
 __global__ void __launch_bounds__(128)
 qk_norm_rope_append_kernel(
     const float *__restrict__ qkv, int S, size_t split_stride, const TW *__restrict__ q_w,
@@ -49,8 +49,9 @@ qk_norm_rope_append_kernel(
     const float *__restrict__ sn, int rot_half, const int32_t *__restrict__ row_pos,
     const int32_t *__restrict__ row_seq, const int32_t *__restrict__ block_table, int bt_stride,
     TC *__restrict__ q_out, TC *__restrict__ k_cache, TC *__restrict__ v_cache, int n, int nh,
-    int nkv, int hd, int hpw)
+    int nkv, int hd)
 {
+    constexpr int hpw = HPW;
     pdl_trigger();
     unsigned slots = nh + 2 * nkv;
     unsigned runs = (slots + hpw - 1) / hpw;          // runs of head slots per row
@@ -90,7 +91,27 @@ qk_norm_rope_append_kernel(
     }
     pdl_wait();
 
-    for (unsigned hs = hs0; hs < hs1; hs++) {
+    // every head of this warp is fetched before the first is worked on
+    float lo[HPW][PAIRS], hi[HPW][PAIRS];
+#pragma unroll
+    for (int k = 0; k < HPW; k++) {
+        unsigned hs = hs0 + k;
+        const float *src = qkv + (size_t)row * slots * hd + (size_t)hs * hd;
+#pragma unroll
+        for (int j = 0; j < PAIRS; j++) {
+            int i = lane + 32 * j;
+            lo[k][j] = hi[k][j] = 0.0f;
+            if (hs < hs1 && i < half) {
+                lo[k][j] = add_partials(0.0f, src + i, S, split_stride);
+                hi[k][j] = add_partials(0.0f, src + i + half, S, split_stride);
+            }
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < HPW; k++) {
+        unsigned hs = hs0 + k;
+        if (hs >= hs1)
+            break;
         bool is_q = hs < (unsigned)nh;
         bool is_v = hs >= (unsigned)(nh + nkv);
         TC *dst;
@@ -103,19 +124,11 @@ qk_norm_rope_append_kernel(
             size_t at = (((size_t)page * nkv + kvh) * PAGE + (pos % PAGE)) * hd;
             dst = (!is_v ? k_cache : v_cache) + at;
         }
-        const float *src = qkv + (size_t)row * slots * hd + (size_t)hs * hd;
-        float lo[PAIRS], hi[PAIRS];
         float ss = 0.0f;
 #pragma unroll
         for (int j = 0; j < PAIRS; j++) {
-            int i = lane + 32 * j;
-            lo[j] = hi[j] = 0.0f;
-            if (i < half) {
-                lo[j] = add_partials(0.0f, src + i, S, split_stride);
-                hi[j] = add_partials(0.0f, src + i + half, S, split_stride);
-                ss = fmaf(lo[j], lo[j], ss);
-                ss = fmaf(hi[j], hi[j], ss);
-            }
+            ss = fmaf(lo[k][j], lo[k][j], ss);
+            ss = fmaf(hi[k][j], hi[k][j], ss);
         }
         bool normed = !is_v && q_w != nullptr;
         float scale = 1.0f;
@@ -128,7 +141,7 @@ qk_norm_rope_append_kernel(
         for (int j = 0; j < PAIRS; j++) {
             int i = lane + 32 * j;
             if (i < half) {
-                float a = lo[j], b = hi[j];
+                float a = lo[k][j], b = hi[k][j];
                 if (normed) {
                     a = (a * scale) * (is_q ? wql[j] : wkl[j]);
                     b = (b * scale) * (is_q ? wqh[j] : wkh[j]);
@@ -178,18 +191,25 @@ extern "C" int jb_qk_norm_rope_append(const float *qkv, int S, long long split_s
     // few rows: a warp per head slot, for the shortest chain; many rows: several
     // head slots per warp, for fewer fetches of what the row's heads share
     int slots = nh + 2 * nkv;
-    int hpw = n >= 256 ? (slots >= 24 ? 6 : slots >= 8 ? 4 : 1) : 1;
+    int hpw = n >= 256 && slots >= 8 ? 4 : 1;
     size_t tasks = (size_t)n * ((slots + hpw - 1) / hpw);
     if (tasks > 0xffffffffu)
         return JB_EINVAL;
     dim3 block(32, 4);
     unsigned grid = (unsigned)((tasks + 3) / 4);
     int pairs = (hd / 2 + 31) / 32;
-#define JB_ROPE_P(TC, TW, P)                                                                   \
-    launch(qk_norm_rope_append_kernel<TC, TW, P>, grid, block, 0, st,                          \
+#define JB_ROPE_PH(TC, TW, P, H)                                                               \
+    launch(qk_norm_rope_append_kernel<TC, TW, P, H>, grid, block, 0, st,                       \
         qkv, S, (size_t)split_stride, (const TW *)q_w, (const TW *)k_w, eps, cs, sn, rot_half, \
         row_pos, row_seq, block_table, bt_stride, (TC *)q_out, (TC *)k_cache, (TC *)v_cache, n, \
-        nh, nkv, hd, hpw)
+        nh, nkv, hd)
+#define JB_ROPE_P(TC, TW, P)                                                                   \
+    do {                                                                                       \
+        if (hpw == 1)                                                                          \
+            JB_ROPE_PH(TC, TW, P, 1);                                                          \
+        else                                                                                   \
+            JB_ROPE_PH(TC, TW, P, 4);                                                          \
+    } while (0)
 #define JB_ROPE(TC, TW)                                                                        \
     do {                                                                                       \
         if (pairs <= 1)                                                                        \
@@ -212,6 +232,7 @@ extern "C" int jb_qk_norm_rope_append(const float *qkv, int S, long long split_s
     else
         return JB_EINVAL;
 #undef JB_ROPE_P
+#undef JB_ROPE_PH
 #undef JB_ROPE
     return launch_status();
 }

@@ -99,6 +99,58 @@ __global__ void rmsnorm_kernel(float *__restrict__ x, const float *__restrict__ 
     }
 }
 
+// The same for many rows at once, bfloat16 output: a warp per row, eight rows a
+// block, four values per lane and load.  Its sums run in another order than
+// rmsnorm_kernel's, so it serves the bfloat16 path only (the 32-bit path keeps one
+// order for every batch); dm must be a multiple of 4.
+template <typename TW>
+__global__ void __launch_bounds__(256)
+rmsnorm_rows_kernel(float *__restrict__ x, const float *__restrict__ delta, int S,
+                    size_t delta_stride, const TW *__restrict__ w, bf16 *__restrict__ out,
+                    int n, int dm, float eps)
+{
+    pdl_trigger();
+    pdl_wait();
+    int lane = threadIdx.x & 31;
+    size_t row = (size_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (row >= (size_t)n)
+        return;
+    float4 *xr = reinterpret_cast<float4 *>(x + row * dm);
+    int nv = dm / 4;
+    float ss = 0.0f;
+    for (int i = lane; i < nv; i += 32) {
+        float4 v = xr[i];
+        if (delta) {
+            const float *d = delta + row * dm + 4 * i;
+            if (S == 1) {
+                float4 a = *reinterpret_cast<const float4 *>(d);
+                v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+            } else {
+                v.x = add_partials(v.x, d, S, delta_stride);
+                v.y = add_partials(v.y, d + 1, S, delta_stride);
+                v.z = add_partials(v.z, d + 2, S, delta_stride);
+                v.w = add_partials(v.w, d + 3, S, delta_stride);
+            }
+            xr[i] = v;
+        }
+        ss = fmaf(v.x, v.x, ss);
+        ss = fmaf(v.y, v.y, ss);
+        ss = fmaf(v.z, v.z, ss);
+        ss = fmaf(v.w, v.w, ss);
+    }
+    ss = warp_sum(ss);
+    float scale = 1.0f / sqrtf(ss / (float)dm + eps);
+    uint2 *o = reinterpret_cast<uint2 *>(out + row * dm);
+    for (int i = lane; i < nv; i += 32) {
+        float4 v = xr[i];                       // this lane wrote it: a cache hit
+        float w0 = to_f(w[4 * i]), w1 = to_f(w[4 * i + 1]), w2 = to_f(w[4 * i + 2]),
+              w3 = to_f(w[4 * i + 3]);
+        __nv_bfloat162 lo = __floats2bfloat162_rn((v.x * scale) * w0, (v.y * scale) * w1);
+        __nv_bfloat162 hi = __floats2bfloat162_rn((v.z * scale) * w2, (v.w * scale) * w3);
+        o[i] = make_uint2(*reinterpret_cast<uint32_t *>(&lo), *reinterpret_cast<uint32_t *>(&hi));
+    }
+}
+
 // gu: S stacked [n, 2 ff] float partial sums; columns [0, ff) are the gate,
 // [ff, 2 ff) the up projection.  out[n, ff] = SiLU(gate) * up.  VEC values per
 // thread (4 when ff is a multiple of 4 and nothing is split, else 1).
@@ -167,6 +219,21 @@ extern "C" int jb_rmsnorm(float *x, const float *delta, int S, long long delta_s
         return JB_OK;
     if (delta && row_idx)
         return JB_EINVAL;
+    // many rows of the bfloat16 path: the kernel that takes eight rows a block
+    if (out != nullptr && out_dt == JB_BF16 && row_idx == nullptr && n_out >= 256 && dm % 4 == 0 &&
+        (uintptr_t)x % 16 == 0 && (uintptr_t)delta % 16 == 0 && (uintptr_t)out % 8 == 0 &&
+        (delta == nullptr || delta_stride % 4 == 0)) {
+        unsigned blocks = (unsigned)((n_out + 7) / 8);
+        if (w_dt == JB_F32)
+            launch(rmsnorm_rows_kernel<float>, blocks, 256, 0, st, x, delta, S,
+                   (size_t)delta_stride, (const float *)w, (bf16 *)out, n_out, dm, eps);
+        else if (w_dt == JB_BF16)
+            launch(rmsnorm_rows_kernel<bf16>, blocks, 256, 0, st, x, delta, S,
+                   (size_t)delta_stride, (const bf16 *)w, (bf16 *)out, n_out, dm, eps);
+        else
+            return JB_EINVAL;
+        return launch_status();
+    }
     int threads = norm_threads(dm);
     int ept = (dm + threads - 1) / threads;
 #define JB_NORM_E(TW, TO, E)                                                                  \

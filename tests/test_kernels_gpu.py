@@ -35,7 +35,7 @@ def test_embed(dtype, dm):
 
 @pytest.mark.parametrize("wdt", DTYPES)
 @pytest.mark.parametrize("odt", DTYPES)
-@pytest.mark.parametrize("n,dm", [(1, 40), (5, 2560), (33, 1000)])
+@pytest.mark.parametrize("n,dm", [(1, 40), (5, 2560), (33, 1000), (300, 1000), (257, 2560)])
 def test_rmsnorm(wdt, odt, n, dm):
     x = rnd(n, dm, scale=3.0)
     w = (1 + 0.1 * rnd(dm)).to(wdt)
