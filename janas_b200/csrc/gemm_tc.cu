@@ -415,6 +415,41 @@ extern "C" int jb_gemm_tc_splits(int n, int m, int k)
     return best;
 }
 
+// Tokens per tile (256 features x this many tokens) for a product over many
+// tokens.  One CTA fits an SM, so tiles run in rounds of as many as there are
+// SMs; a narrower tile can turn a mostly empty last round into none.  A tile's
+// time is a fixed part plus, per 64-wide block of k, the larger of its MMA time
+// and the time to bring its operands in (measured: about 116 GB/s per SM), which
+// is why narrower tiles are not proportionally faster.
+static int many_tokens_tile(int n, int m, int k)
+{
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+            sms <= 0)
+            sms = 148;
+    }
+    const int choices[5] = {256, 224, 192, 160, 128};
+    int kb = (k + BK - 1) / BK;
+    long m_tiles = (m + 2 * TILE_M - 1) / (2 * TILE_M);
+    int best = 256;
+    double best_t = 1e30;
+    for (int c = 0; c < 5; c++) {
+        int bn = choices[c];
+        long tiles = m_tiles * ((n + bn - 1) / bn);
+        long rounds = (tiles + sms - 1) / sms;
+        double mma = 0.55 * bn / 256.0, load = (32768.0 + bn * 128.0) / 116000.0;
+        double t = rounds * (8.0 + kb * (mma > load ? mma : load));
+        if (t < best_t * 0.98) {
+            best_t = t;
+            best = bn;
+        }
+    }
+    return best;
+}
+
 // out: [splits, n, m] float partial sums of A[n, k] . W[m, k]^T.
 extern "C" int jb_gemm_tc(const void *A, const void *W, float *out, int n, int m, int k, int splits,
                           cudaStream_t st)
@@ -424,7 +459,13 @@ extern "C" int jb_gemm_tc(const void *A, const void *W, float *out, int n, int m
     if (n > 128) {
         if (splits != 1)
             return JB_EINVAL;
-        return launch_tc<256, 2, EPI_PARTIAL>(A, W, out, nullptr, n, m, k, m, TILE_M, 1, st);
+        switch (many_tokens_tile(n, m, k)) {
+        case 128: return launch_tc<128, 2, EPI_PARTIAL>(A, W, out, nullptr, n, m, k, m, TILE_M, 1, st);
+        case 160: return launch_tc<160, 2, EPI_PARTIAL>(A, W, out, nullptr, n, m, k, m, TILE_M, 1, st);
+        case 192: return launch_tc<192, 2, EPI_PARTIAL>(A, W, out, nullptr, n, m, k, m, TILE_M, 1, st);
+        case 224: return launch_tc<224, 2, EPI_PARTIAL>(A, W, out, nullptr, n, m, k, m, TILE_M, 1, st);
+        default: return launch_tc<256, 2, EPI_PARTIAL>(A, W, out, nullptr, n, m, k, m, TILE_M, 1, st);
+        }
     }
     if (n <= 16)
         return launch_tc<16, 1, EPI_PARTIAL>(A, W, out, nullptr, n, m, k, m, TILE_M, splits, st);
