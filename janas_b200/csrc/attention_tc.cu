@@ -1,27 +1,32 @@
 // Causal grouped-query attention over the paged cache on the tensor cores
-// (tcgen05), for bfloat16 heads of 64 or 128 values.
+// (tcgen05), for bfloat16 heads of 64 or 128 values.  Keys and values come in
+// chunks of 128 positions, two cache pages, straight from the pages into shared
+// memory by TMA; V is read as an MN-major operand as it lies in the page
+// ([position][value]).  Three kernels:
 //
-// A CTA works for one KV head on a block of 128 rows: the G query heads of the
-// group for R = 128 / G consecutive positions of one sequence (prefill), or the
-// G heads of one decoded token (decode; the other rows of the block are idle).
-// Keys and values come in chunks of 128 positions, two cache pages, straight
-// from the pages into shared memory by TMA.  Per chunk:
+// attn_tc_prefill_kernel   A CTA works for one KV head on a block of 128 rows:
+//     the G query heads of the group for R = 128 / G consecutive positions of
+//     one sequence.  Per chunk S = Q K^T, softmax by two threads per row (scale,
+//     causal and window mask, running maximum, exp, sum; P to shared memory in
+//     bfloat16), PV = P V; the running (m, l, o) stays in registers; chunks are
+//     software-pipelined through a second S and a second P buffer.
 //
-//   S = Q K^T          tcgen05.mma, Q and K K-major, S in tensor memory
-//   softmax            one thread per row: scale, causal and window mask, running
-//                      maximum, exp, sum; P written to shared memory in bfloat16
-//   PV = P V           tcgen05.mma, V read as an MN-major operand as it lies in
-//                      the page ([position][value]), PV in tensor memory
+// attn_tc_decode_kernel    One decoded token, heads of 128 values, up to 16
+//     heads per KV head: the keys are the M operand (S^T = K Q^T, O^T = V^T P),
+//     one thread per key; a CTA runs over its chunks and leaves one partial
+//     (m, l, O) per head, which attention.cu's merge kernel joins.  That spreads
+//     one token's long context over many SMs.
 //
-// Prefill rows keep the running (m, l, o) in registers over all their chunks and
-// write o / l.  Decode rows write one partial (m, l, PV) per chunk to scratch,
-// in the layout of attention.cu, whose merge kernel then joins them in chunk
-// order; that spreads one token's long context over many SMs.
+// attn_tc_rows_kernel      One decoded token for the sizes the kernel above does
+//     not take (heads of 64 values, more than 16 heads per KV head): the block
+//     of 128 rows holds the group's heads, one chunk per CTA, one partial per
+//     chunk.
 //
 // Warp 0 issues the TMA loads, warp 1 owns the tensor memory and issues the
-// MMAs, warps 2..5 are the 128 row threads.  Every mbarrier wait has a time
-// limit (see tc_common.cuh); a wait that runs out is recorded in an error word
-// (jb_attn_tc_error) and the CTA winds down.  No load uses cluster multicast.
+// MMAs, the other warps are the row (or key) threads.  Every mbarrier wait has a
+// time limit (see tc_common.cuh); a wait that runs out is recorded in an error
+// word (jb_attn_tc_error) and the CTA winds down.  No load uses cluster
+// multicast.
 //
 // Formulas as in attention.cu (reference: src/llm/attention.c:107-118,574-588,
 // 734-739,870-910).
@@ -57,15 +62,16 @@ __device__ __forceinline__ uint32_t swz(int row, int j)
     return (uint32_t)(row * 128 + ((j ^ (row & 7)) << 4));
 }
 
-template <int HD, bool DECODE>
+template <int HD>
 __global__ void __launch_bounds__(192)
-attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+attn_tc_rows_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                const __grid_constant__ CUtensorMap map_v, const int32_t *__restrict__ qblk,
                const int32_t *__restrict__ row_pos, const int32_t *__restrict__ row_seq,
                const int32_t *__restrict__ block_table, int bt_stride, bf16 *__restrict__ out,
                float *__restrict__ part, int nh, int nkv, int G, int R, int window, float scale,
                int max_chunks, int chunks_per_cta, int row0)
 {
+    constexpr bool DECODE = true;      // this kernel serves decoded tokens only
     using Cfg = AttnCfg<HD>;
     constexpr int NB = Cfg::NB;
     extern __shared__ uint8_t smem_raw[];
@@ -1036,8 +1042,8 @@ static bool attn_tensor_map(const void *ptr, long long d0, long long d1, long lo
     return true;
 }
 
-template <int HD, bool DECODE>
-static int launch_attn_tc(const void *q, const void *k_cache, const void *v_cache,
+template <int HD>
+static int launch_attn_rows(const void *q, const void *k_cache, const void *v_cache,
                           long long n_pages, const int32_t *qblk, int n_blocks,
                           const int32_t *row_pos, const int32_t *row_seq,
                           const int32_t *block_table, int bt_stride, void *out, float *part, int n,
@@ -1047,11 +1053,11 @@ static int launch_attn_tc(const void *q, const void *k_cache, const void *v_cach
     using Cfg = AttnCfg<HD>;
     int G = nh / nkv;
     CUtensorMap mq, mk, mv;
-    if (!attn_tensor_map(q, HD, nh, n, G, DECODE ? 1 : R, &mq) ||
+    if (!attn_tensor_map(q, HD, nh, n, G, 1, &mq) ||
         !attn_tensor_map(k_cache, HD, n_pages * nkv * PAGE, 0, PAGE, 0, &mk) ||
         !attn_tensor_map(v_cache, HD, n_pages * nkv * PAGE, 0, PAGE, 0, &mv))
         return JB_EINVAL;
-    auto kern = attn_tc_kernel<HD, DECODE>;
+    auto kern = attn_tc_rows_kernel<HD>;
     static bool attr_set = false;
     if (!attr_set) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -1059,8 +1065,7 @@ static int launch_attn_tc(const void *q, const void *k_cache, const void *v_cach
             return JB_ELAUNCH;
         attr_set = true;
     }
-    unsigned gx = DECODE ? (unsigned)n_rows * ((max_chunks + chunks_per_cta - 1) / chunks_per_cta)
-                         : (unsigned)n_blocks;
+    unsigned gx = (unsigned)n_rows * ((max_chunks + chunks_per_cta - 1) / chunks_per_cta);
     if (gx == 0)
         return JB_OK;
     launch(kern, dim3(gx, nkv), 192, Cfg::SMEM_BYTES, st, mq, mk, mv, qblk, row_pos, row_seq,
@@ -1176,11 +1181,11 @@ extern "C" int jb_attn_tc_decode(const void *q, const void *k_cache, const void 
         return launch_status();
     }
     if (hd == 128)
-        return launch_attn_tc<128, true>(q, k_cache, v_cache, n_pages, nullptr, 0, row_pos, row_seq,
+        return launch_attn_rows<128>(q, k_cache, v_cache, n_pages, nullptr, 0, row_pos, row_seq,
                                          block_table, bt_stride, nullptr, part, n, nh, nkv, 0,
                                          window, scale, max_chunks, chunks_per_cta, row0, n_rows,
                                          st);
-    return launch_attn_tc<64, true>(q, k_cache, v_cache, n_pages, nullptr, 0, row_pos, row_seq,
+    return launch_attn_rows<64>(q, k_cache, v_cache, n_pages, nullptr, 0, row_pos, row_seq,
                                     block_table, bt_stride, nullptr, part, n, nh, nkv, 0, window,
                                     scale, max_chunks, chunks_per_cta, row0, n_rows, st);
 }
