@@ -785,20 +785,31 @@ attn_tc_decode_kernel(const __grid_constant__ CUtensorMap map_q,
     uint32_t tmem = *tmem_slot;
     uint32_t tmem_s = tmem, tmem_pv = tmem + 2 * DQ_N;    // S: two buffers of 16 columns
     int *err = &g_attn_tc_error;
-    // q, the keys and the values were written by the kernel before this one
+    // q and the keys and values of position q_pos were written by the kernel before
+    // this one; every chunk before q_pos's holds what earlier steps left, so the
+    // thread that loads fetches those without waiting for that kernel
     pdl_trigger();
-    pdl_wait();
+    bool loader = warp == 0 && lane == 0;
+    if (!loader)
+        pdl_wait();
 
-    if (warp == 0 && lane == 0) {
+    if (loader) {
         // ---------------------------------------------------------- TMA loads
-        mbar_expect_tx(bar(0), (uint32_t)(G * HD * 2));
-        tma_load_3d(smem_u32(q_s), &map_q, bar(0), 0, kvh * G, q_row);
-        tma_load_3d(smem_u32(q_s + DQ_BLK), &map_q, bar(0), 64, kvh * G, q_row);
+        bool waited = false;
+        auto wait_and_load_q = [&]() {
+            pdl_wait();
+            mbar_expect_tx(bar(0), (uint32_t)(G * HD * 2));
+            tma_load_3d(smem_u32(q_s), &map_q, bar(0), 0, kvh * G, q_row);
+            tma_load_3d(smem_u32(q_s + DQ_BLK), &map_q, bar(0), 64, kvh * G, q_row);
+            waited = true;
+        };
         const int32_t *bt = block_table + (size_t)seq * bt_stride;
         uint32_t armed = 0, last_parity = 0;
         for (int u = 0; u < 2 * n_chunks; u++) {        // unit u: K (even) or V (odd) of chunk u / 2
             int s = u % DQ_UNITS;
             uint32_t ph = (u / DQ_UNITS) & 1;
+            if (!waited && (u >= DQ_UNITS || c_first + u / 2 >= q_pos / AT_KEYS))
+                wait_and_load_q();
             if (!mbar_wait(bar(4 + s), ph ^ 1, abort, err, 11))
                 break;
             mbar_expect_tx(bar(1 + s), DQ_UNIT);
@@ -819,6 +830,8 @@ attn_tc_decode_kernel(const __grid_constant__ CUtensorMap map_q,
             armed |= 1u << s;
             last_parity = (last_parity & ~(1u << s)) | (ph << s);
         }
+        if (!waited)
+            wait_and_load_q();
         if (*abort) {
             volatile int never = 0;
             for (int s = 0; s < DQ_UNITS; s++)

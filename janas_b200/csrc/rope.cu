@@ -31,17 +31,16 @@ __global__ void rope_table_kernel(float *__restrict__ cs, float *__restrict__ sn
     sn[i] = (float)s;
 }
 
-// One warp per (row, run of HPW head slots); head slots are the q heads, then
-// the k heads, then the v heads of the row's fused [q | k | v] vector.  PAIRS is
-// how many (low, high) pairs of a head a lane holds: ceil(hd / 64).  With many
-// rows a warp takes several head slots of its row in turn, so that the row's
-// rotation table and the norm weights are fetched once for all of them.
+// One warp per (row, head slot); head slots are the q heads, then the k heads,
+// then the v heads of the row's fused [q | k | v] vector.  PAIRS is how many
+// (low, high) pairs of a head a lane holds: ceil(hd / 64).  This kernel takes
+// every even head size up to 512; the usual sizes go to the kernel below.
 //
 // qkv: S stacked [n, (nh + 2 nkv) hd] float partial sums.
 // q_out: [n, nh, hd] in the cache's type.  K and V go to page
 // block_table[seq][pos / PAGE] of k_cache / v_cache, which are laid out
 // [page][kv head][PAGE][hd].
-template <typename TC, typename TW, int PAIRS, int HPW>
+template <typename TC, typename TW, int PAIRS>
 __global__ void __launch_bounds__(128)
 qk_norm_rope_append_kernel(
     const float *__restrict__ qkv, int S, size_t split_stride, const TW *__restrict__ q_w,
@@ -51,111 +50,198 @@ qk_norm_rope_append_kernel(
     TC *__restrict__ q_out, TC *__restrict__ k_cache, TC *__restrict__ v_cache, int n, int nh,
     int nkv, int hd)
 {
-    constexpr int hpw = HPW;
     pdl_trigger();
     unsigned slots = nh + 2 * nkv;
-    unsigned runs = (slots + hpw - 1) / hpw;          // runs of head slots per row
     unsigned task = blockIdx.x * blockDim.y + threadIdx.y;
-    if (task >= (unsigned)n * runs)
+    if (task >= (unsigned)n * slots)
         return;
-    unsigned row = task / runs, hs0 = (task - row * runs) * hpw;
-    unsigned hs1 = min(hs0 + hpw, slots);
+    unsigned row = task / slots, hs = task - row * slots;
     int lane = threadIdx.x;
     int half = hd / 2;
+    bool is_q = hs < (unsigned)nh;
+    bool is_v = hs >= (unsigned)(nh + nkv);
 
     // Positions, page tables, rotation tables and norm weights were written long
     // before the kernel before this one: they are fetched before the wait.
     int pos = row_pos[row];
     int page = k_cache != nullptr
                    ? block_table[(size_t)row_seq[row] * bt_stride + pos / PAGE] : 0;
-    bool rotate_any = rot_half == half;
-    float co[PAIRS], si[PAIRS], wql[PAIRS], wqh[PAIRS], wkl[PAIRS], wkh[PAIRS];
+    bool normed = !is_v && q_w != nullptr;
+    bool rotate = !is_v && rot_half == half;
+    const TW *w = is_q ? q_w : k_w;
+    float co[PAIRS], si[PAIRS], wl[PAIRS], wh[PAIRS];
 #pragma unroll
     for (int j = 0; j < PAIRS; j++) {
         int i = lane + 32 * j;
         co[j] = 1.0f;
         si[j] = 0.0f;
-        wql[j] = wqh[j] = wkl[j] = wkh[j] = 1.0f;
+        wl[j] = wh[j] = 1.0f;
         if (i < half) {
-            if (rotate_any) {
+            if (rotate) {
                 co[j] = cs[(size_t)pos * rot_half + i];
                 si[j] = sn[(size_t)pos * rot_half + i];
             }
-            if (q_w != nullptr) {
-                wql[j] = to_f(q_w[i]);
-                wqh[j] = to_f(q_w[i + half]);
-                wkl[j] = to_f(k_w[i]);
-                wkh[j] = to_f(k_w[i + half]);
+            if (normed) {
+                wl[j] = to_f(w[i]);
+                wh[j] = to_f(w[i + half]);
             }
         }
     }
     pdl_wait();
 
-    // every head of this warp is fetched before the first is worked on
-    float lo[HPW][PAIRS], hi[HPW][PAIRS];
+    TC *dst;
+    if (is_q) {
+        dst = q_out + ((size_t)row * nh + hs) * hd;
+    } else {
+        if (k_cache == nullptr)
+            return;
+        int kvh = !is_v ? hs - nh : hs - nh - nkv;
+        size_t at = (((size_t)page * nkv + kvh) * PAGE + (pos % PAGE)) * hd;
+        dst = (!is_v ? k_cache : v_cache) + at;
+    }
+    const float *src = qkv + (size_t)row * slots * hd + (size_t)hs * hd;
+    float lo[PAIRS], hi[PAIRS];
+    float ss = 0.0f;
 #pragma unroll
-    for (int k = 0; k < HPW; k++) {
-        unsigned hs = hs0 + k;
-        const float *src = qkv + (size_t)row * slots * hd + (size_t)hs * hd;
+    for (int j = 0; j < PAIRS; j++) {
+        int i = lane + 32 * j;
+        lo[j] = hi[j] = 0.0f;
+        if (i < half) {
+            lo[j] = add_partials(0.0f, src + i, S, split_stride);
+            hi[j] = add_partials(0.0f, src + i + half, S, split_stride);
+        }
+        ss = fmaf(lo[j], lo[j], ss);
+        ss = fmaf(hi[j], hi[j], ss);
+    }
+    float scale = 1.0f;
+    if (normed) {
+        ss = warp_sum(ss);
+        scale = 1.0f / sqrtf(ss / (float)hd + eps);
+    }
 #pragma unroll
-        for (int j = 0; j < PAIRS; j++) {
-            int i = lane + 32 * j;
-            lo[k][j] = hi[k][j] = 0.0f;
-            if (hs < hs1 && i < half) {
-                lo[k][j] = add_partials(0.0f, src + i, S, split_stride);
-                hi[k][j] = add_partials(0.0f, src + i + half, S, split_stride);
+    for (int j = 0; j < PAIRS; j++) {
+        int i = lane + 32 * j;
+        if (i < half) {
+            float a = lo[j], b = hi[j];
+            if (normed) {
+                a = (a * scale) * wl[j];
+                b = (b * scale) * wh[j];
+            }
+            if (rotate) {
+                dst[i] = from_f<TC>(a * co[j] - b * si[j]);
+                dst[i + half] = from_f<TC>(a * si[j] + b * co[j]);
+            } else {
+                dst[i] = from_f<TC>(a);
+                dst[i + half] = from_f<TC>(b);
             }
         }
     }
+}
+
+// The same for head sizes 32, 64, 128 and 256: LPH = hd / 8 lanes share a head
+// slot, each with four consecutive values of the low half and the four that
+// pair with them in the high half, so that a warp works on 32 / LPH head slots
+// of its row at once with 16-byte loads.  Everything must lie on 16-byte
+// boundaries (the launcher checks).  The sums of squares are added in another
+// order than in the kernel above; which of the two runs depends on the head
+// size and the addresses only, never on the number of rows.
+template <typename TC, typename TW, int LPH>
+__global__ void __launch_bounds__(128)
+qk_norm_rope_append_vec_kernel(
+    const float *__restrict__ qkv, int S, size_t split_stride, const TW *__restrict__ q_w,
+    const TW *__restrict__ k_w, float eps, const float *__restrict__ cs,
+    const float *__restrict__ sn, int rot_half, const int32_t *__restrict__ row_pos,
+    const int32_t *__restrict__ row_seq, const int32_t *__restrict__ block_table, int bt_stride,
+    TC *__restrict__ q_out, TC *__restrict__ k_cache, TC *__restrict__ v_cache, int n, int nh,
+    int nkv)
+{
+    constexpr int SLOTS_PER_WARP = 32 / LPH;
+    constexpr int half = 4 * LPH, hd = 2 * half;
+    pdl_trigger();
+    unsigned slots = nh + 2 * nkv;
+    unsigned groups = (slots + SLOTS_PER_WARP - 1) / SLOTS_PER_WARP;
+    unsigned task = blockIdx.x * blockDim.y + threadIdx.y;
+    if (task >= (unsigned)n * groups)
+        return;
+    unsigned row = task / groups;
+    unsigned hs = (task - row * groups) * SLOTS_PER_WARP + threadIdx.x / LPH;
+    int at4 = 4 * (threadIdx.x % LPH);          // this lane's values: at4 .. at4 + 3 of each half
+    bool live = hs < slots;
+    bool is_q = hs < (unsigned)nh;
+    bool is_v = hs >= (unsigned)(nh + nkv);
+
+    int pos = row_pos[row];
+    int page = k_cache != nullptr
+                   ? block_table[(size_t)row_seq[row] * bt_stride + pos / PAGE] : 0;
+    bool normed = live && !is_v && q_w != nullptr;
+    bool rotate = live && !is_v && rot_half == half;
+    float4 co = make_float4(1.0f, 1.0f, 1.0f, 1.0f), si = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    float4 wl = co, wh = co;
+    if (rotate) {
+        co = load4(cs + (size_t)pos * half + at4);
+        si = load4(sn + (size_t)pos * half + at4);
+    }
+    if (normed) {
+        const TW *w = is_q ? q_w : k_w;
+        wl = load4(w + at4);
+        wh = load4(w + half + at4);
+    }
+    pdl_wait();
+
+    float4 lo = make_float4(0.0f, 0.0f, 0.0f, 0.0f), hi = lo;
+    if (live) {
+        const float *src = qkv + (size_t)row * slots * hd + (size_t)hs * hd + at4;
+        for (int s0 = 0; s0 < S; s0 += 4) {
+            float4 a[4], b[4];
 #pragma unroll
-    for (int k = 0; k < HPW; k++) {
-        unsigned hs = hs0 + k;
-        if (hs >= hs1)
-            break;
-        bool is_q = hs < (unsigned)nh;
-        bool is_v = hs >= (unsigned)(nh + nkv);
-        TC *dst;
-        if (is_q) {
-            dst = q_out + ((size_t)row * nh + hs) * hd;
-        } else {
-            if (k_cache == nullptr)
-                continue;
-            int kvh = !is_v ? hs - nh : hs - nh - nkv;
-            size_t at = (((size_t)page * nkv + kvh) * PAGE + (pos % PAGE)) * hd;
-            dst = (!is_v ? k_cache : v_cache) + at;
-        }
-        float ss = 0.0f;
-#pragma unroll
-        for (int j = 0; j < PAIRS; j++) {
-            ss = fmaf(lo[k][j], lo[k][j], ss);
-            ss = fmaf(hi[k][j], hi[k][j], ss);
-        }
-        bool normed = !is_v && q_w != nullptr;
-        float scale = 1.0f;
-        if (normed) {
-            ss = warp_sum(ss);
-            scale = 1.0f / sqrtf(ss / (float)hd + eps);
-        }
-        bool rotate = !is_v && rotate_any;
-#pragma unroll
-        for (int j = 0; j < PAIRS; j++) {
-            int i = lane + 32 * j;
-            if (i < half) {
-                float a = lo[k][j], b = hi[k][j];
-                if (normed) {
-                    a = (a * scale) * (is_q ? wql[j] : wkl[j]);
-                    b = (b * scale) * (is_q ? wqh[j] : wkh[j]);
+            for (int u = 0; u < 4; u++)
+                if (s0 + u < S) {
+                    a[u] = load4(src + (size_t)(s0 + u) * split_stride);
+                    b[u] = load4(src + (size_t)(s0 + u) * split_stride + half);
                 }
-                if (rotate) {
-                    dst[i] = from_f<TC>(a * co[j] - b * si[j]);
-                    dst[i + half] = from_f<TC>(a * si[j] + b * co[j]);
-                } else {
-                    dst[i] = from_f<TC>(a);
-                    dst[i + half] = from_f<TC>(b);
+#pragma unroll
+            for (int u = 0; u < 4; u++)
+                if (s0 + u < S) {
+                    lo.x += a[u].x; lo.y += a[u].y; lo.z += a[u].z; lo.w += a[u].w;
+                    hi.x += b[u].x; hi.y += b[u].y; hi.z += b[u].z; hi.w += b[u].w;
                 }
-            }
         }
     }
+    float ss = lo.x * lo.x;
+    ss = fmaf(lo.y, lo.y, ss); ss = fmaf(lo.z, lo.z, ss); ss = fmaf(lo.w, lo.w, ss);
+    ss = fmaf(hi.x, hi.x, ss); ss = fmaf(hi.y, hi.y, ss);
+    ss = fmaf(hi.z, hi.z, ss); ss = fmaf(hi.w, hi.w, ss);
+#pragma unroll
+    for (int o = LPH / 2; o > 0; o >>= 1)
+        ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (!live)
+        return;
+    TC *dst;
+    if (is_q) {
+        dst = q_out + ((size_t)row * nh + hs) * hd;
+    } else {
+        if (k_cache == nullptr)
+            return;
+        int kvh = !is_v ? hs - nh : hs - nh - nkv;
+        size_t at = (((size_t)page * nkv + kvh) * PAGE + (pos % PAGE)) * hd;
+        dst = (!is_v ? k_cache : v_cache) + at;
+    }
+    if (normed) {
+        float scale = 1.0f / sqrtf(ss / (float)hd + eps);
+        lo.x = (lo.x * scale) * wl.x; lo.y = (lo.y * scale) * wl.y;
+        lo.z = (lo.z * scale) * wl.z; lo.w = (lo.w * scale) * wl.w;
+        hi.x = (hi.x * scale) * wh.x; hi.y = (hi.y * scale) * wh.y;
+        hi.z = (hi.z * scale) * wh.z; hi.w = (hi.w * scale) * wh.w;
+    }
+    if (rotate) {
+        float4 a = lo, b = hi;
+        lo = make_float4(a.x * co.x - b.x * si.x, a.y * co.y - b.y * si.y,
+                         a.z * co.z - b.z * si.z, a.w * co.w - b.w * si.w);
+        hi = make_float4(a.x * si.x + b.x * co.x, a.y * si.y + b.y * co.y,
+                         a.z * si.z + b.z * co.z, a.w * si.w + b.w * co.w);
+    }
+    store4(dst + at4, lo);
+    store4(dst + half + at4, hi);
 }
 
 }  // namespace jb
@@ -188,28 +274,60 @@ extern "C" int jb_qk_norm_rope_append(const float *qkv, int S, long long split_s
         return JB_EINVAL;
     if ((q_w == nullptr) != (k_w == nullptr))
         return JB_EINVAL;
-    // few rows: a warp per head slot, for the shortest chain; many rows: several
-    // head slots per warp, for fewer fetches of what the row's heads share
     int slots = nh + 2 * nkv;
-    int hpw = n >= 256 && slots >= 8 ? 4 : 1;
-    size_t tasks = (size_t)n * ((slots + hpw - 1) / hpw);
+    dim3 block(32, 4);
+    auto aligned = [](const void *p, size_t to) { return (uintptr_t)p % to == 0; };
+    size_t w_to = w_dt == JB_F32 ? 16 : 8, c_to = cache_dt == JB_F32 ? 16 : 8;
+    bool vec = (hd == 32 || hd == 64 || hd == 128 || hd == 256) && split_stride % 4 == 0 &&
+               aligned(qkv, 16) && aligned(cs, 16) && aligned(sn, 16) && aligned(q_w, w_to) &&
+               aligned(k_w, w_to) && aligned(q_out, c_to) && aligned(k_cache, c_to) &&
+               aligned(v_cache, c_to);
+    if (vec) {
+        int per_warp = 32 / (hd / 8);
+        size_t tasks = (size_t)n * ((slots + per_warp - 1) / per_warp);
+        if (tasks > 0xffffffffu)
+            return JB_EINVAL;
+        unsigned grid = (unsigned)((tasks + 3) / 4);
+#define JB_ROPE_V(TC, TW, L)                                                                   \
+    launch(qk_norm_rope_append_vec_kernel<TC, TW, L>, grid, block, 0, st,                      \
+        qkv, S, (size_t)split_stride, (const TW *)q_w, (const TW *)k_w, eps, cs, sn, rot_half, \
+        row_pos, row_seq, block_table, bt_stride, (TC *)q_out, (TC *)k_cache, (TC *)v_cache, n, \
+        nh, nkv)
+#define JB_ROPE_VL(TC, TW)                                                                     \
+    do {                                                                                       \
+        if (hd == 32)                                                                          \
+            JB_ROPE_V(TC, TW, 4);                                                              \
+        else if (hd == 64)                                                                     \
+            JB_ROPE_V(TC, TW, 8);                                                              \
+        else if (hd == 128)                                                                    \
+            JB_ROPE_V(TC, TW, 16);                                                             \
+        else                                                                                   \
+            JB_ROPE_V(TC, TW, 32);                                                             \
+    } while (0)
+        if (cache_dt == JB_F32 && w_dt == JB_F32)
+            JB_ROPE_VL(float, float);
+        else if (cache_dt == JB_F32 && w_dt == JB_BF16)
+            JB_ROPE_VL(float, bf16);
+        else if (cache_dt == JB_BF16 && w_dt == JB_F32)
+            JB_ROPE_VL(bf16, float);
+        else if (cache_dt == JB_BF16 && w_dt == JB_BF16)
+            JB_ROPE_VL(bf16, bf16);
+        else
+            return JB_EINVAL;
+#undef JB_ROPE_V
+#undef JB_ROPE_VL
+        return launch_status();
+    }
+    size_t tasks = (size_t)n * slots;
     if (tasks > 0xffffffffu)
         return JB_EINVAL;
-    dim3 block(32, 4);
     unsigned grid = (unsigned)((tasks + 3) / 4);
     int pairs = (hd / 2 + 31) / 32;
-#define JB_ROPE_PH(TC, TW, P, H)                                                               \
-    launch(qk_norm_rope_append_kernel<TC, TW, P, H>, grid, block, 0, st,                       \
+#define JB_ROPE_P(TC, TW, P)                                                                   \
+    launch(qk_norm_rope_append_kernel<TC, TW, P>, grid, block, 0, st,                          \
         qkv, S, (size_t)split_stride, (const TW *)q_w, (const TW *)k_w, eps, cs, sn, rot_half, \
         row_pos, row_seq, block_table, bt_stride, (TC *)q_out, (TC *)k_cache, (TC *)v_cache, n, \
         nh, nkv, hd)
-#define JB_ROPE_P(TC, TW, P)                                                                   \
-    do {                                                                                       \
-        if (hpw == 1)                                                                          \
-            JB_ROPE_PH(TC, TW, P, 1);                                                          \
-        else                                                                                   \
-            JB_ROPE_PH(TC, TW, P, 4);                                                          \
-    } while (0)
 #define JB_ROPE(TC, TW)                                                                        \
     do {                                                                                       \
         if (pairs <= 1)                                                                        \
@@ -232,7 +350,6 @@ extern "C" int jb_qk_norm_rope_append(const float *qkv, int S, long long split_s
     else
         return JB_EINVAL;
 #undef JB_ROPE_P
-#undef JB_ROPE_PH
 #undef JB_ROPE
     return launch_status();
 }

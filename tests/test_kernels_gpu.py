@@ -58,6 +58,30 @@ def test_rmsnorm(wdt, odt, n, dm):
     assert (got - want).abs().max() <= tol * want.abs().max()
 
 
+@pytest.mark.parametrize("wdt", DTYPES)
+@pytest.mark.parametrize("n,dm,S", [(1, 1024, 1), (8, 2560, 14), (3, 1027, 17), (5, 9000, 2),
+                                    (2, 17000, 3)])
+def test_rmsnorm_few_rows(wdt, n, dm, S):
+    """Few rows with bfloat16 output: a row shared out among the CTAs of a cluster.
+    One value of each row is large, so that a CTA's missing share would show."""
+    x = rnd(n, dm, scale=3.0)
+    x[:, dm - 3] = 200.0
+    w = (1 + 0.1 * rnd(dm)).to(wdt)
+    delta = rnd(S, n, dm, seed=1)
+    xd = x.to(DEV).clone()
+    got = ops().rmsnorm(xd, w.to(DEV), 1e-5, torch.bfloat16, delta=delta.to(DEV)).cpu().float()
+    x2 = x.clone()
+    for s in range(S):
+        x2 = x2 + delta[s]
+    assert torch.equal(xd.cpu(), x2)
+    want = plain.rms_norm(x2, w.float(), 1e-5)
+    assert (got - want).abs().max() <= 2 ** -8 * want.abs().max()
+    rows = torch.tensor([n - 1, 0], dtype=torch.int32)
+    got = ops().rmsnorm(x.to(DEV), w.to(DEV), 1e-5, torch.bfloat16, rows=rows.to(DEV)).cpu().float()
+    want = plain.rms_norm(x[rows.long()], w.float(), 1e-5)
+    assert (got - want).abs().max() <= 2 ** -8 * want.abs().max()
+
+
 @pytest.mark.parametrize("odt", DTYPES)
 def test_swiglu(odt):
     n, ff = 7, 300
@@ -168,10 +192,12 @@ def test_attention_finds_a_far_key_and_the_window_s_edge(dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("n0,n1,hd", [(25, 15, 48), (300, 58, 128), (3, 1, 16)])
-def test_qk_norm_rope_append(dtype, n0, n1, hd):
-    """Few rows (a warp per head) and many rows (a warp takes several heads)."""
-    nh, nkv = 6, 2
+@pytest.mark.parametrize("n0,n1,hd,nh,nkv", [(25, 15, 48, 6, 2), (300, 58, 128, 6, 2), (3, 1, 16, 6, 2),
+                                             (40, 9, 32, 5, 1), (17, 30, 64, 9, 3),
+                                             (9, 11, 256, 3, 3), (6, 3, 80, 4, 2)])
+def test_qk_norm_rope_append(dtype, n0, n1, hd, nh, nkv):
+    """The kernel for any even head size (48, 16, 80) and the 16-byte one for head
+    sizes 32, 64, 128 and 256, with head counts that leave a warp partly empty."""
     n = n0 + n1
     width = (nh + 2 * nkv) * hd
     qkv = rnd(2, n, width, scale=2.0)
