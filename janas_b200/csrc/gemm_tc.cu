@@ -13,8 +13,8 @@
 // A CTA computes one tile: 128 * MT features by BN tokens over one part of k
 // (grid.z parts; each part writes its own float partial sum, added by whoever
 // reads the product next, in a fixed order).  Warp 0 issues the TMA loads,
-// warp 1 owns the tensor memory and issues the MMAs, warps 2..5 read the
-// accumulator back (one thread per feature) and store.  With EPI_SWIGLU the two
+// warp 1 owns the tensor memory and issues the MMAs, warps 2..9 read the
+// accumulator back (a thread per feature and half of the tokens) and store.  With EPI_SWIGLU the two
 // weight tiles are the gate rows and the up rows of the same features and the
 // epilogue writes SiLU(gate) * up in bfloat16.
 //
@@ -39,6 +39,10 @@ constexpr int TILE_M = 128;         // features per MMA
 constexpr int W_TILE_BYTES = TILE_M * BK * 2;
 constexpr int EPI_PARTIAL = 0;      // store float partial sums
 constexpr int EPI_SWIGLU = 1;       // two tiles: gate and up; store SiLU(gate) * up as bfloat16
+// warp 0 loads, warp 1 issues the MMAs, warps 2..9 read the accumulator back: a
+// warp may read the 32 TMEM lanes of its index modulo 4, so two warps share each
+// quarter of the features and take the 32-column groups in turn
+constexpr int GEMM_THREADS = 320;
 
 __device__ int g_gemm_tc_error;     // 0, or the code of the first wait that ran out
 
@@ -76,7 +80,7 @@ template <int BN, int MT> struct TileCfg {
 };
 
 template <int BN, int MT, int EPI>
-__global__ void __launch_bounds__(192)
+__global__ void __launch_bounds__(GEMM_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
                float *__restrict__ out, bf16 *__restrict__ out_act, int n, int m, int k,
                int second_off, int kb_per_split)
@@ -200,14 +204,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16);
         // The accumulator is read 32 columns (tokens) at a time; the read of the
         // next 32 is in flight while the last 32 are stored.
+        int hgrp = (warp - 2) >> 2;             // which of the two warps of this quarter
         if (EPI == EPI_PARTIAL) {
             float *dst = out + (size_t)blockIdx.z * n * m;
             constexpr int COLS = MT * BN;           // tile t's tokens are columns [t BN, t BN + BN)
             if constexpr (BN < 32) {
                 float v[16];
-                if (ok)
+                if (ok && hgrp == 0)
                     tc_ld16(taddr, v);
-                if (ok && f < m) {
+                if (ok && hgrp == 0 && f < m) {
 #pragma unroll
                     for (int j = 0; j < 16; j++)
                         if (n0 + j < n)
@@ -232,19 +237,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                                 *p = __uint_as_float(v[j]);
                     }
                 };
-                if (ok) {
-                    tc_ld32_nowait(taddr, va);
+                // this warp's groups of 32 columns: hgrp, hgrp + 2, ...; the read of the
+                // next group is in flight while the last one is stored
+                int c = 32 * hgrp;
+                if (ok && c < COLS) {
+                    tc_ld32_nowait(taddr + c, va);
 #pragma unroll 1
-                    for (int c = 0; c < COLS; c += 64) {
+                    for (; c < COLS; c += 128) {
                         tc_ld_wait();
-                        if (c + 32 < COLS)
-                            tc_ld32_nowait(taddr + c + 32, vb);
+                        if (c + 64 < COLS)
+                            tc_ld32_nowait(taddr + c + 64, vb);
                         store32(va, c);
-                        if (c + 32 < COLS) {
+                        if (c + 64 < COLS) {
                             tc_ld_wait();
-                            if (c + 64 < COLS)
-                                tc_ld32_nowait(taddr + c + 64, va);
-                            store32(vb, c + 32);
+                            if (c + 128 < COLS)
+                                tc_ld32_nowait(taddr + c + 128, va);
+                            store32(vb, c + 64);
                         }
                     }
                 }
@@ -252,6 +260,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         } else {
             int ff = second_off;
             uint32_t ga[32], ua[32], gb[32], ub[32];
+            // SiLU(g) u = g u / (1 + 2^(-g log2 e)), with the approximate exponential
+            // and reciprocal (a few units in the last place of a float; the result is
+            // rounded to bfloat16)
             auto act32 = [&](const uint32_t *g, const uint32_t *u, int c0) {
                 if (f >= ff)
                     return;
@@ -261,29 +272,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 for (int j = 0; j < 32; j++, p += ff) {
                     if (whole || n0 + c0 + j < n) {
                         float gv = __uint_as_float(g[j]), uv = __uint_as_float(u[j]);
-                        float h = gv / (1.0f + __expf(-gv)) * uv;
-                        *p = __float2bfloat16_rn(h);
+                        float e = fast_exp2(gv * -1.4426950408889634f);
+                        *p = __float2bfloat16_rn(__fdividef(gv * uv, 1.0f + e));
                     }
                 }
             };
-            if (ok) {
-                tc_ld32_nowait(taddr, ga);
-                tc_ld32_nowait(taddr + BN, ua);
+            int c = 32 * hgrp;
+            if (ok && c < BN) {
+                tc_ld32_nowait(taddr + c, ga);
+                tc_ld32_nowait(taddr + BN + c, ua);
 #pragma unroll 1
-                for (int c = 0; c < BN; c += 64) {
+                for (; c < BN; c += 128) {
                     tc_ld_wait();
-                    if (c + 32 < BN) {
-                        tc_ld32_nowait(taddr + c + 32, gb);
-                        tc_ld32_nowait(taddr + BN + c + 32, ub);
+                    if (c + 64 < BN) {
+                        tc_ld32_nowait(taddr + c + 64, gb);
+                        tc_ld32_nowait(taddr + BN + c + 64, ub);
                     }
                     act32(ga, ua, c);
-                    if (c + 32 < BN) {
+                    if (c + 64 < BN) {
                         tc_ld_wait();
-                        if (c + 64 < BN) {
-                            tc_ld32_nowait(taddr + c + 64, ga);
-                            tc_ld32_nowait(taddr + BN + c + 64, ua);
+                        if (c + 128 < BN) {
+                            tc_ld32_nowait(taddr + c + 128, ga);
+                            tc_ld32_nowait(taddr + BN + c + 128, ua);
                         }
-                        act32(gb, ub, c + 32);
+                        act32(gb, ub, c + 64);
                     }
                 }
             }
@@ -371,7 +383,7 @@ static int launch_tc(const void *A, const void *W, float *out, bf16 *out_act, in
     dim3 grid((n + BN - 1) / BN, (feats + tile_feats - 1) / tile_feats, splits);
     if (grid.y > 65535 || grid.z > 65535)
         return JB_EINVAL;
-    launch(kern, grid, 192, Cfg::SMEM_BYTES, st, map_w, map_a, out, out_act, n, m, k, second_off,
+    launch(kern, grid, GEMM_THREADS, Cfg::SMEM_BYTES, st, map_w, map_a, out, out_act, n, m, k, second_off,
            kbps);
     return launch_status();
 }
@@ -483,9 +495,18 @@ extern "C" int jb_gemm_tc_swiglu(const void *A, const void *W, void *out_act, in
 {
     if (!jb_gemm_tc_ok(A, W, n, 2 * ff, k))
         return JB_EINVAL;
-    if (n > 128)
-        return launch_tc<256, 2, EPI_SWIGLU>(A, W, nullptr, (bf16 *)out_act, n, 2 * ff, k, 2 * ff,
-                                             ff, 1, st);
+    if (n > 128) {
+#define JB_SWIGLU(B)                                                                           \
+    launch_tc<B, 2, EPI_SWIGLU>(A, W, nullptr, (bf16 *)out_act, n, 2 * ff, k, 2 * ff, ff, 1, st)
+        switch (many_tokens_tile(n, 2 * ff, k)) {
+        case 128: return JB_SWIGLU(128);
+        case 160: return JB_SWIGLU(160);
+        case 192: return JB_SWIGLU(192);
+        case 224: return JB_SWIGLU(224);
+        default: return JB_SWIGLU(256);
+        }
+#undef JB_SWIGLU
+    }
     return launch_tc<128, 2, EPI_SWIGLU>(A, W, nullptr, (bf16 *)out_act, n, 2 * ff, k, 2 * ff, ff,
                                          1, st);
 }

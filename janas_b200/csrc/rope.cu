@@ -10,6 +10,8 @@
 // (src/llm/model_attn.c:31-39); K after norm and rotation and V as it is go to
 // the cache at the row's position (src/llm/model_attn.c:103-145; the
 // reference's eight-bit cache is not reproduced).
+#include <algorithm>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -160,88 +162,97 @@ qk_norm_rope_append_vec_kernel(
     pdl_trigger();
     unsigned slots = nh + 2 * nkv;
     unsigned groups = (slots + SLOTS_PER_WARP - 1) / SLOTS_PER_WARP;
-    unsigned task = blockIdx.x * blockDim.y + threadIdx.y;
-    if (task >= (unsigned)n * groups)
-        return;
-    unsigned row = task / groups;
-    unsigned hs = (task - row * groups) * SLOTS_PER_WARP + threadIdx.x / LPH;
+    unsigned total = (unsigned)n * groups;
     int at4 = 4 * (threadIdx.x % LPH);          // this lane's values: at4 .. at4 + 3 of each half
-    bool live = hs < slots;
-    bool is_q = hs < (unsigned)nh;
-    bool is_v = hs >= (unsigned)(nh + nkv);
+    bool waited = false;
+    // with many rows a warp takes several tasks in turn: blocks that live for one
+    // task only are started more slowly than they finish
+    for (unsigned task = blockIdx.x * blockDim.y + threadIdx.y; task < total;
+         task += gridDim.x * blockDim.y) {
+        unsigned row = task / groups;
+        unsigned hs = (task - row * groups) * SLOTS_PER_WARP + threadIdx.x / LPH;
+        bool live = hs < slots;
+        bool is_q = hs < (unsigned)nh;
+        bool is_v = hs >= (unsigned)(nh + nkv);
 
-    int pos = row_pos[row];
-    int page = k_cache != nullptr
-                   ? block_table[(size_t)row_seq[row] * bt_stride + pos / PAGE] : 0;
-    bool normed = live && !is_v && q_w != nullptr;
-    bool rotate = live && !is_v && rot_half == half;
-    float4 co = make_float4(1.0f, 1.0f, 1.0f, 1.0f), si = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    float4 wl = co, wh = co;
-    if (rotate) {
-        co = load4(cs + (size_t)pos * half + at4);
-        si = load4(sn + (size_t)pos * half + at4);
-    }
-    if (normed) {
-        const TW *w = is_q ? q_w : k_w;
-        wl = load4(w + at4);
-        wh = load4(w + half + at4);
-    }
-    pdl_wait();
-
-    float4 lo = make_float4(0.0f, 0.0f, 0.0f, 0.0f), hi = lo;
-    if (live) {
-        const float *src = qkv + (size_t)row * slots * hd + (size_t)hs * hd + at4;
-        for (int s0 = 0; s0 < S; s0 += 4) {
-            float4 a[4], b[4];
-#pragma unroll
-            for (int u = 0; u < 4; u++)
-                if (s0 + u < S) {
-                    a[u] = load4(src + (size_t)(s0 + u) * split_stride);
-                    b[u] = load4(src + (size_t)(s0 + u) * split_stride + half);
-                }
-#pragma unroll
-            for (int u = 0; u < 4; u++)
-                if (s0 + u < S) {
-                    lo.x += a[u].x; lo.y += a[u].y; lo.z += a[u].z; lo.w += a[u].w;
-                    hi.x += b[u].x; hi.y += b[u].y; hi.z += b[u].z; hi.w += b[u].w;
-                }
+        // positions, page tables, rotation tables and norm weights were written long
+        // before the kernel before this one: they are fetched before the wait
+        int pos = row_pos[row];
+        int page = k_cache != nullptr
+                       ? block_table[(size_t)row_seq[row] * bt_stride + pos / PAGE] : 0;
+        bool normed = live && !is_v && q_w != nullptr;
+        bool rotate = live && !is_v && rot_half == half;
+        float4 co = make_float4(1.0f, 1.0f, 1.0f, 1.0f), si = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        float4 wl = co, wh = co;
+        if (rotate) {
+            co = load4(cs + (size_t)pos * half + at4);
+            si = load4(sn + (size_t)pos * half + at4);
         }
-    }
-    float ss = lo.x * lo.x;
-    ss = fmaf(lo.y, lo.y, ss); ss = fmaf(lo.z, lo.z, ss); ss = fmaf(lo.w, lo.w, ss);
-    ss = fmaf(hi.x, hi.x, ss); ss = fmaf(hi.y, hi.y, ss);
-    ss = fmaf(hi.z, hi.z, ss); ss = fmaf(hi.w, hi.w, ss);
+        if (normed) {
+            const TW *w = is_q ? q_w : k_w;
+            wl = load4(w + at4);
+            wh = load4(w + half + at4);
+        }
+        if (!waited) {
+            pdl_wait();
+            waited = true;
+        }
+
+        float4 lo = make_float4(0.0f, 0.0f, 0.0f, 0.0f), hi = lo;
+        if (live) {
+            const float *src = qkv + (size_t)row * slots * hd + (size_t)hs * hd + at4;
+            for (int s0 = 0; s0 < S; s0 += 4) {
+                float4 a[4], b[4];
 #pragma unroll
-    for (int o = LPH / 2; o > 0; o >>= 1)
-        ss += __shfl_xor_sync(0xffffffffu, ss, o);
-    if (!live)
-        return;
-    TC *dst;
-    if (is_q) {
-        dst = q_out + ((size_t)row * nh + hs) * hd;
-    } else {
-        if (k_cache == nullptr)
-            return;
-        int kvh = !is_v ? hs - nh : hs - nh - nkv;
-        size_t at = (((size_t)page * nkv + kvh) * PAGE + (pos % PAGE)) * hd;
-        dst = (!is_v ? k_cache : v_cache) + at;
+                for (int u = 0; u < 4; u++)
+                    if (s0 + u < S) {
+                        a[u] = load4(src + (size_t)(s0 + u) * split_stride);
+                        b[u] = load4(src + (size_t)(s0 + u) * split_stride + half);
+                    }
+#pragma unroll
+                for (int u = 0; u < 4; u++)
+                    if (s0 + u < S) {
+                        lo.x += a[u].x; lo.y += a[u].y; lo.z += a[u].z; lo.w += a[u].w;
+                        hi.x += b[u].x; hi.y += b[u].y; hi.z += b[u].z; hi.w += b[u].w;
+                    }
+            }
+        }
+        float ss = lo.x * lo.x;
+        ss = fmaf(lo.y, lo.y, ss); ss = fmaf(lo.z, lo.z, ss); ss = fmaf(lo.w, lo.w, ss);
+        ss = fmaf(hi.x, hi.x, ss); ss = fmaf(hi.y, hi.y, ss);
+        ss = fmaf(hi.z, hi.z, ss); ss = fmaf(hi.w, hi.w, ss);
+#pragma unroll
+        for (int o = LPH / 2; o > 0; o >>= 1)
+            ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (!live)
+            continue;
+        TC *dst;
+        if (is_q) {
+            dst = q_out + ((size_t)row * nh + hs) * hd;
+        } else {
+            if (k_cache == nullptr)
+                continue;
+            int kvh = !is_v ? hs - nh : hs - nh - nkv;
+            size_t at = (((size_t)page * nkv + kvh) * PAGE + (pos % PAGE)) * hd;
+            dst = (!is_v ? k_cache : v_cache) + at;
+        }
+        if (normed) {
+            float scale = 1.0f / sqrtf(ss / (float)hd + eps);
+            lo.x = (lo.x * scale) * wl.x; lo.y = (lo.y * scale) * wl.y;
+            lo.z = (lo.z * scale) * wl.z; lo.w = (lo.w * scale) * wl.w;
+            hi.x = (hi.x * scale) * wh.x; hi.y = (hi.y * scale) * wh.y;
+            hi.z = (hi.z * scale) * wh.z; hi.w = (hi.w * scale) * wh.w;
+        }
+        if (rotate) {
+            float4 a = lo, b = hi;
+            lo = make_float4(a.x * co.x - b.x * si.x, a.y * co.y - b.y * si.y,
+                             a.z * co.z - b.z * si.z, a.w * co.w - b.w * si.w);
+            hi = make_float4(a.x * si.x + b.x * co.x, a.y * si.y + b.y * co.y,
+                             a.z * si.z + b.z * co.z, a.w * si.w + b.w * co.w);
+        }
+        store4(dst + at4, lo);
+        store4(dst + half + at4, hi);
     }
-    if (normed) {
-        float scale = 1.0f / sqrtf(ss / (float)hd + eps);
-        lo.x = (lo.x * scale) * wl.x; lo.y = (lo.y * scale) * wl.y;
-        lo.z = (lo.z * scale) * wl.z; lo.w = (lo.w * scale) * wl.w;
-        hi.x = (hi.x * scale) * wh.x; hi.y = (hi.y * scale) * wh.y;
-        hi.z = (hi.z * scale) * wh.z; hi.w = (hi.w * scale) * wh.w;
-    }
-    if (rotate) {
-        float4 a = lo, b = hi;
-        lo = make_float4(a.x * co.x - b.x * si.x, a.y * co.y - b.y * si.y,
-                         a.z * co.z - b.z * si.z, a.w * co.w - b.w * si.w);
-        hi = make_float4(a.x * si.x + b.x * co.x, a.y * si.y + b.y * co.y,
-                         a.z * si.z + b.z * co.z, a.w * si.w + b.w * co.w);
-    }
-    store4(dst + at4, lo);
-    store4(dst + half + at4, hi);
 }
 
 }  // namespace jb
@@ -287,7 +298,7 @@ extern "C" int jb_qk_norm_rope_append(const float *qkv, int S, long long split_s
         size_t tasks = (size_t)n * ((slots + per_warp - 1) / per_warp);
         if (tasks > 0xffffffffu)
             return JB_EINVAL;
-        unsigned grid = (unsigned)((tasks + 3) / 4);
+        unsigned grid = (unsigned)std::min<size_t>((tasks + 3) / 4, 148 * 16);
 #define JB_ROPE_V(TC, TW, L)                                                                   \
     launch(qk_norm_rope_append_vec_kernel<TC, TW, L>, grid, block, 0, st,                      \
         qkv, S, (size_t)split_stride, (const TW *)q_w, (const TW *)k_w, eps, cs, sn, rot_half, \

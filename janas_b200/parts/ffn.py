@@ -19,11 +19,11 @@ from .registry import register_feed_forward
 class SwiGLU(FeedForward):
     """params: hidden_size, intermediate_size."""
 
-    # Rows above which gate, up and the activation run as one kernel.  That kernel
-    # (ops.linear_swiglu) exists and is tested, but on B200 its epilogue costs more
-    # than the separate activation kernel saves (276 against 149 + 39 microseconds at
-    # 2,048 rows of Qwen3-4B), so it is not used.
-    FUSED_FROM = 1 << 30
+    # Rows from which gate, up and the activation run as one kernel
+    # (ops.linear_swiglu).  Measured on B200 at Qwen3-4B sizes: 167 against 165 + 37
+    # microseconds at 2,048 rows, 103 against 109 at 1,024, even at 512; with few rows
+    # the one kernel cannot cut k into parts and loses (29 against 20 at 8 rows).
+    FUSED_FROM = 512
 
     def __init__(self, spec, dtype, device):
         super().__init__(spec, dtype, device)
@@ -48,7 +48,7 @@ class SwiGLU(FeedForward):
 
     def forward(self, ctx: StepContext, h: torch.Tensor) -> torch.Tensor:
         act = None
-        if ctx.n_rows > self.FUSED_FROM and ctx.dtype == torch.bfloat16:
+        if ctx.n_rows >= self.FUSED_FROM and ctx.dtype == torch.bfloat16:
             # enough rows to fill the SMs without cutting k: gate, up and the
             # activation in one kernel
             act = ops.linear_swiglu(h, self.w_gate_up)

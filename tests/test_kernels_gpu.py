@@ -332,13 +332,15 @@ def test_gemm_tensor_core_finds_one_large_product():
 def test_gemm_tensor_core_swiglu(n, ff, k):
     a = rnd(n, k, dtype=torch.bfloat16)
     w = rnd(2 * ff, k, dtype=torch.bfloat16, seed=5, scale=0.3)
+    a[1] *= 60.0                          # gates of a few hundred, of both signs
     got = ops().linear_swiglu(a.to(DEV), w.to(DEV))
     assert ops().gemm_tc_error() == 0
     gu = a.double() @ w.double().T
     g, u = gu[:, :ff], gu[:, ff:]
     want = (g / (1 + torch.exp(-g)) * u).float()
     assert got.dtype == torch.bfloat16 and got.shape == (n, ff)
-    assert (got.float().cpu() - want).abs().max() <= 2 ** -8 * want.abs().max()
+    err = (got.float().cpu() - want).abs().max(dim=1).values      # row by row: row 1 is large
+    assert bool((err <= 2 ** -8 * want.abs().max(dim=1).values).all())
 
 
 def test_products_that_the_tensor_core_kernel_refuses_go_the_plain_way():
