@@ -194,6 +194,38 @@ attn_partial_kernel(const T *__restrict__ q, const T *__restrict__ k_cache,
     }
 }
 
+// N partials of one (row, head), fetched together, join the running (m, l, o):
+// their largest maximum first, then each weighted by e^(its maximum - that), so
+// that the weights do not wait for one another.  The sums run in chunk order.
+template <int N>
+__device__ __forceinline__ void merge_partials(const float *__restrict__ base, size_t stride,
+                                               int c0, int n_chunks, int d, int hd, float &m,
+                                               float &l, float &o)
+{
+    float mc[N], lc[N], oc[N];
+#pragma unroll
+    for (int u = 0; u < N; u++) {
+        const float *p = base + (size_t)min(c0 + u, n_chunks - 1) * stride;
+        mc[u] = p[0];
+        lc[u] = p[1];
+        oc[u] = d < hd ? p[2 + d] : 0.0f;
+    }
+    float mn = m;
+#pragma unroll
+    for (int u = 0; u < N; u++)
+        mn = fmaxf(mn, mc[u]);
+    float a = m == -INFINITY ? 0.0f : expf(m - mn);
+    l *= a;
+    o *= a;
+#pragma unroll
+    for (int u = 0; u < N; u++) {
+        float w = c0 + u < n_chunks ? expf(mc[u] - mn) : 0.0f;
+        l = fmaf(lc[u], w, l);
+        o = fmaf(oc[u], w, o);
+    }
+    m = mn;
+}
+
 // One block per (row, head); thread d owns one value of the head.
 template <typename T>
 __global__ void attn_merge_kernel(const float *__restrict__ part,
@@ -209,28 +241,16 @@ __global__ void attn_merge_kernel(const float *__restrict__ part,
     int lo = window > 0 && pos + 1 > window ? pos + 1 - window : 0;
     // a partial covers chunks_per_part chunks; max_chunks is the partials' stride
     int n_chunks = (pos / ATT_CHUNK - lo / ATT_CHUNK + chunks_per_part) / chunks_per_part;
+    const float *base = part + part_at((size_t)lrow, nh, h, max_chunks, 0, hd);
+    size_t stride = part_at(0, nh, 0, max_chunks, 1, hd);
     float m = -INFINITY, l = 0.0f, o = 0.0f;
-    // eight partials are fetched together and then joined in chunk order
-    for (int c0 = 0; c0 < n_chunks; c0 += 8) {
-        float mc[8], lc[8], oc[8];
-#pragma unroll
-        for (int u = 0; u < 8; u++) {
-            int ci = min(c0 + u, n_chunks - 1);
-            const float *p = part + part_at((size_t)lrow, nh, h, max_chunks, ci, hd);
-            mc[u] = p[0];
-            lc[u] = p[1];
-            oc[u] = d < hd ? p[2 + d] : 0.0f;
-        }
-#pragma unroll
-        for (int u = 0; u < 8; u++) {
-            if (c0 + u >= n_chunks)
-                break;
-            float mn = fmaxf(m, mc[u]);
-            float a = expf(m - mn), b = expf(mc[u] - mn);
-            l = l * a + lc[u] * b;
-            o = o * a + oc[u] * b;
-            m = mn;
-        }
+    // a row with few partials fetches four at a time, one with many sixteen: most
+    // rows need one trip to memory
+    if (n_chunks <= 4) {
+        merge_partials<4>(base, stride, 0, n_chunks, d, hd, m, l, o);
+    } else {
+        for (int c0 = 0; c0 < n_chunks; c0 += 16)
+            merge_partials<16>(base, stride, c0, n_chunks, d, hd, m, l, o);
     }
     if (d < hd)
         out[((size_t)row * nh + h) * hd + d] = from_f<T>(o / l);
