@@ -429,6 +429,11 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
     float *pair = (float *)(tmem_slot + 4);    // [2 chunks][2 halves][128 rows]
 
     int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        prefetch_tensor_map(&map_q);
+        prefetch_tensor_map(&map_k);
+        prefetch_tensor_map(&map_v);
+    }
     int kvh = blockIdx.y;
     const int32_t *b = qblk + 4 * (gridDim.x - 1 - blockIdx.x);   // long blocks first
     int q_row = b[0], q_count = b[1], q_pos = b[2], seq = b[3];
@@ -742,6 +747,11 @@ attn_tc_decode_kernel(const __grid_constant__ CUtensorMap map_q,
     float *red_l = red_m + 4 * DQ_N;
 
     int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        prefetch_tensor_map(&map_k);
+        prefetch_tensor_map(&map_v);
+        prefetch_tensor_map(&map_q);
+    }
     int kvh = blockIdx.y;
     int parts = (max_chunks + chunks_per_cta - 1) / chunks_per_cta;
     int max_parts = parts;             // partials per (row, head) in scratch
@@ -790,7 +800,9 @@ attn_tc_decode_kernel(const __grid_constant__ CUtensorMap map_q,
     // thread that loads fetches those without waiting for that kernel
     pdl_trigger();
     bool loader = warp == 0 && lane == 0;
-    if (!loader)
+    // The other lanes of the loader's warp do not wait either (they touch no memory):
+    // a wait in one branch of a warp holds the whole warp, the loader with it.
+    if (warp != 0)
         pdl_wait();
 
     if (loader) {

@@ -95,6 +95,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     volatile int *abort = (volatile int *)(tmem_slot + 1);
 
     int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        prefetch_tensor_map(&map_w);
+        prefetch_tensor_map(&map_a);
+    }
     // token tiles vary fastest: the CTAs that run at the same time share weight
     // tiles, which then come from memory once, and the (small) activations come
     // from the L2

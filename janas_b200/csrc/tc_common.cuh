@@ -65,6 +65,13 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
 }
 
+// Brings a tensor map (a kernel parameter) into the descriptor cache ahead of its
+// first use.
+__device__ __forceinline__ void prefetch_tensor_map(const CUtensorMap *map)
+{
+    asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar,
                                             int x, int y)
 {
