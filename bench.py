@@ -4,6 +4,7 @@
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--batch B]
                     [--context C] [--dtype bfloat16|float32] [--no-points]
     python bench.py --impl reference ...     (prints why it is unavailable)
+    python bench.py --only decode|prefill|timeline ...   (one part, for profiling)
 
 The default run has the layer sizes of Qwen3-4B (36 layers, hidden 2560, 32
 heads, 8 KV heads, head size 128, feed-forward 9728, vocabulary 151936, tied
@@ -167,6 +168,34 @@ def decode_device_timed(eng, slots, tokens, steps, warmup):
     return a.elapsed_time(b) / steps, ops.COUNTERS["launches"] - l0, tokens
 
 
+def decode_timeline(eng, slots, tokens, warmup):
+    """Prints, for the last of three decode steps recorded with torch.profiler
+    (CUPTI activity records; the step is the replayed CUDA graph), when each kernel
+    started and ended and how long after the kernel before it ended.  Kernels start
+    before their predecessors end (programmatic dependent launch), so a kernel's
+    cost on the step's critical path is the last column, not its duration."""
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+    for _ in range(warmup + 2):
+        tokens = eng.decode(slots, tokens).tolist()
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(3):
+            tokens = eng.decode(slots, tokens).tolist()
+        torch.cuda.synchronize()
+    evs = [e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA]
+    evs.sort(key=lambda e: e.time_range.start)
+    last = evs[-(len(evs) // 3):]
+    t0 = last[0].time_range.start
+    prev_end = t0
+    print("start us   duration   end us   after the one before   kernel")
+    for e in last:
+        s, en = e.time_range.start - t0, e.time_range.end - t0
+        print(f"{s:8.1f} {en - s:10.1f} {en:8.1f} {en - (prev_end - t0):10.1f}   {e.name[:64]}")
+        prev_end = max(prev_end, e.time_range.end)
+    print(f"step: {prev_end - t0:.1f} us")
+
+
 def step_bytes(eng, batch, context):
     """Bytes a decode step has to read: every weight once, and the keys and
     values of the live sequences."""
@@ -200,8 +229,9 @@ def main():
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--no-points", action="store_true", help="skip decoding at batch 1 and 64")
-    ap.add_argument("--only", default="", choices=["", "decode", "prefill"],
-                    help="run one part only and print its time (for profiling; no JSON line)")
+    ap.add_argument("--only", default="", choices=["", "decode", "prefill", "timeline"],
+                    help="run one part only and print its time (for profiling; no JSON line); "
+                         "timeline: when each kernel of one replayed decode step ends")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -228,6 +258,11 @@ def main():
     big_batch = 64 if not args.no_points else args.batch
     eng = build_engine(args, args.layers, room * max(big_batch, args.batch), max(big_batch, args.batch))
     cfg = dict(QWEN3_4B)
+
+    if args.only == "timeline":
+        slots, toks = fill(eng, args.batch, args.context, rng)
+        decode_timeline(eng, slots, toks, args.warmup)
+        return 0
 
     if args.only == "decode":
         slots, toks = fill(eng, args.batch, args.context, rng)
