@@ -383,31 +383,41 @@ attn_tc_rows_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 }
 
 // --------------------------------------------------------------- prefill rows
-// The block of 128 rows with two threads per row: warps 2..5 take keys 0..63 of
-// a chunk and the first half of the head's values, warps 6..9 keys 64..127 and
-// the second half.  A row's two threads agree on the chunk's maximum through
-// shared memory; each keeps the sum of its own weights, joined at the end.  The
-// scores of a chunk stay in registers between the maximum and the weights, so
-// tensor memory is read once.
-constexpr int PF_THREADS = 320;
+// A CTA works for one KV head on two blocks of 128 rows, A and B: the G query
+// heads of the group for 2 R consecutive positions of one sequence (R = 128 / G
+// each).  Both blocks use the same keys and values, so a chunk is loaded once for
+// 256 rows, and they take turns: while one block's row threads turn scores into
+// weights, the tensor core works on the other block.  One thread per row: no
+// exchange between threads.
+//
+//   per chunk and block:  S = Q K^T  ->  row thread: S from tensor memory, mask,
+//   maximum, p = 2^(s - m), sum, P to shared memory in bfloat16  ->  O += P V
+//
+// O stays in tensor memory and P V accumulates onto it.  A row's exponent
+// reference m is therefore not moved with every chunk but only when the chunk's
+// maximum exceeds it by more than 8 (weights up to 2^8, far inside bfloat16 and
+// float range); then the row thread scales its row of O and its sum by
+// 2^(m_old - m_new) before it hands P over.  After the first chunks that is rare.
+//
+// Tensor memory: S_A [0, 128), S_B [128, 256), O_A [256, 256 + HD), O_B after it.
+// Shared memory: Q_A, Q_B, P_A, P_B, and a ring of three units that hold in turn
+// the keys of a chunk, its values, the next chunk's keys ...
+constexpr int PF_THREADS = 320;     // warp 0 loads, warp 1 issues MMAs, 2..5 rows of A, 6..9 of B
+constexpr int PF_UNITS = 3;
+constexpr float PF_LAZY = 8.0f;     // how far (in powers of two) a maximum may run ahead of m
 
 template <int HD> struct PrefillCfg {
     static constexpr int NB = HD / 64;
-    static constexpr int Q_BYTES = NB * BLK_BYTES;
-    static constexpr int P_BYTES = 2 * BLK_BYTES;          // 128 rows x 128 keys, two of them
-    static constexpr int KV_STAGE = 2 * NB * BLK_BYTES;
-    static constexpr int TAIL = 3072;                      // barriers, what rows' threads swap
-    static constexpr int SMEM_BYTES = Q_BYTES + 2 * P_BYTES + AT_STAGES * KV_STAGE + TAIL;
-    static constexpr int TMEM_COLS = 512;                  // S twice (2 x 128), PV (HD)
+    static constexpr int Q_TILE = NB * BLK_BYTES;          // 128 rows x HD
+    static constexpr int P_TILE = 2 * BLK_BYTES;           // 128 rows x 128 keys
+    static constexpr int UNIT = NB * BLK_BYTES;            // 128 positions x HD
+    static constexpr int TAIL = 3072;                      // barriers and the like
+    static constexpr int SMEM_BYTES = 2 * Q_TILE + 2 * P_TILE + PF_UNITS * UNIT + TAIL;
+    static constexpr int TMEM_COLS = 512;
 };
 
-// The chunks are software-pipelined: while the row threads turn the scores of
-// chunk i into weights, the tensor core computes the scores of chunk i + 1 (a
-// second S buffer) and P V of chunk i - 1 (a second P buffer); P V of chunk i - 1
-// is added to the running output, scaled by that chunk's factor, after the
-// maximum of chunk i is known.
 template <int HD>
-__global__ void __launch_bounds__(PF_THREADS)
+__global__ void __launch_bounds__(PF_THREADS, 1)
 attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
                        const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, const int32_t *__restrict__ qblk,
@@ -417,16 +427,15 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
 {
     using Cfg = PrefillCfg<HD>;
     constexpr int NB = Cfg::NB;
-    constexpr int HH = HD / 2;                 // values a row thread owns
     extern __shared__ __align__(1024) uint8_t smem[];
-    uint8_t *q_s = smem;
-    uint8_t *p_s = q_s + Cfg::Q_BYTES;         // two buffers of P_BYTES
-    uint8_t *kv_s = p_s + 2 * Cfg::P_BYTES;
-    uint64_t *bars = (uint64_t *)(kv_s + AT_STAGES * Cfg::KV_STAGE);
-    // bars: 0 q_full | 1,2 kv_full | 3,4 kv_empty | 5,6 s_full | 7,8 p_full | 9 o_full | 10 pv_free
-    uint32_t *tmem_slot = (uint32_t *)(bars + 11);
+    uint8_t *q_s = smem;                           // two tiles
+    uint8_t *p_s = q_s + 2 * Cfg::Q_TILE;          // two tiles
+    uint8_t *kv_s = p_s + 2 * Cfg::P_TILE;
+    uint64_t *bars = (uint64_t *)(kv_s + PF_UNITS * Cfg::UNIT);
+    // bars: 0 q_full | 1..3 unit full | 4..6 unit free | 7,8 s_full A,B | 9,10 p_full A,B |
+    //       11,12 pv_done A,B
+    uint32_t *tmem_slot = (uint32_t *)(bars + 13);
     volatile int *abort = (volatile int *)(tmem_slot + 1);
-    float *pair = (float *)(tmem_slot + 4);    // [2 chunks][2 halves][128 rows]
 
     int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
@@ -437,6 +446,7 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
     int kvh = blockIdx.y;
     const int32_t *b = qblk + 4 * (gridDim.x - 1 - blockIdx.x);   // long blocks first
     int q_row = b[0], q_count = b[1], q_pos = b[2], seq = b[3];
+    bool has_b = q_count > R;                                    // the second block has rows
     int lo0 = window > 0 && q_pos + 1 > window ? q_pos + 1 - window : 0;
     int c_first = lo0 / AT_KEYS;
     int c_last = (q_pos + q_count - 1) / AT_KEYS;
@@ -448,14 +458,15 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
     auto bar = [&](int i) { return bar0 + 8 * i; };
     if (threadIdx.x == 0) {
         mbar_init(bar(0), 1);
-        for (int s = 0; s < 2; s++) {
+        for (int s = 0; s < PF_UNITS; s++) {
             mbar_init(bar(1 + s), 1);
-            mbar_init(bar(3 + s), 1);
-            mbar_init(bar(5 + s), 1);
-            mbar_init(bar(7 + s), 2 * AT_ROWS);
+            mbar_init(bar(4 + s), 1);
         }
-        mbar_init(bar(9), 1);
-        mbar_init(bar(10), 2 * AT_ROWS);
+        for (int t = 0; t < 2; t++) {
+            mbar_init(bar(7 + t), 1);
+            mbar_init(bar(9 + t), AT_ROWS);
+            mbar_init(bar(11 + t), 1);
+        }
         *abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -468,7 +479,6 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
     __syncthreads();
     tc_fence_after();
     uint32_t tmem = *tmem_slot;
-    uint32_t tmem_s = tmem, tmem_pv = tmem + 2 * AT_KEYS;
     int *err = &g_attn_tc_error;
     // q, the keys and the values were written by the kernel before this one
     pdl_trigger();
@@ -476,21 +486,23 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
 
     if (warp == 0 && lane == 0) {
         // ---------------------------------------------------------- TMA loads
-        mbar_expect_tx(bar(0), (uint32_t)(R * G * HD * 2));
+        mbar_expect_tx(bar(0), (uint32_t)((has_b ? 2 : 1) * R * G * HD * 2));
+        for (int t = 0; t < (has_b ? 2 : 1); t++)
 #pragma unroll
-        for (int bb = 0; bb < NB; bb++)
-            tma_load_3d(smem_u32(q_s + bb * BLK_BYTES), &map_q, bar(0), bb * 64, kvh * G, q_row);
+            for (int bb = 0; bb < NB; bb++)
+                tma_load_3d(smem_u32(q_s + t * Cfg::Q_TILE + bb * BLK_BYTES), &map_q, bar(0),
+                            bb * 64, kvh * G, q_row + t * R);
         const int32_t *bt = block_table + (size_t)seq * bt_stride;
         uint32_t armed = 0, last_parity = 0;
-        for (int it = 0; it < n_chunks; it++) {
-            int s = it % AT_STAGES;
-            uint32_t ph = (it / AT_STAGES) & 1;
-            if (!mbar_wait(bar(3 + s), ph ^ 1, abort, err, 21))
+        for (int u = 0; u < 2 * n_chunks; u++) {       // unit u: K (even) or V (odd) of chunk u / 2
+            int s = u % PF_UNITS;
+            uint32_t ph = (u / PF_UNITS) & 1;
+            if (!mbar_wait(bar(4 + s), ph ^ 1, abort, err, 21))
                 break;
-            mbar_expect_tx(bar(1 + s), Cfg::KV_STAGE);
-            uint32_t k_dst = smem_u32(kv_s + s * Cfg::KV_STAGE);
-            uint32_t v_dst = k_dst + NB * BLK_BYTES;
-            int c = c_first + it;
+            mbar_expect_tx(bar(1 + s), Cfg::UNIT);
+            uint32_t dst = smem_u32(kv_s + s * Cfg::UNIT);
+            const CUtensorMap *map = (u & 1) ? &map_v : &map_k;
+            int c = c_first + u / 2;
 #pragma unroll
             for (int pg = 0; pg < 2; pg++) {
                 int idx = 2 * c + pg;
@@ -499,19 +511,15 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
                     page = 0;          // not there: every position of it is masked
                 int y = (page * nkv + kvh) * PAGE;
 #pragma unroll
-                for (int bb = 0; bb < NB; bb++) {
-                    tma_load_2d(k_dst + bb * BLK_BYTES + pg * (PAGE * 128), &map_k, bar(1 + s),
-                                bb * 64, y);
-                    tma_load_2d(v_dst + bb * BLK_BYTES + pg * (PAGE * 128), &map_v, bar(1 + s),
-                                bb * 64, y);
-                }
+                for (int bb = 0; bb < NB; bb++)
+                    tma_load_2d(dst + bb * BLK_BYTES + pg * (PAGE * 128), map, bar(1 + s), bb * 64, y);
             }
             armed |= 1u << s;
             last_parity = (last_parity & ~(1u << s)) | (ph << s);
         }
         if (*abort) {
             volatile int never = 0;
-            for (int s = 0; s < AT_STAGES; s++)
+            for (int s = 0; s < PF_UNITS; s++)
                 if (armed & (1u << s))
                     mbar_wait(bar(1 + s), (last_parity >> s) & 1, &never, err, 24);
         }
@@ -519,176 +527,206 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
         // --------------------------------------------------------------- MMAs
         constexpr uint32_t idesc_s = instr_desc_bf16(AT_ROWS, AT_KEYS, false);
         constexpr uint32_t idesc_pv = instr_desc_bf16(AT_ROWS, HD, true);
-        uint32_t q_a = smem_u32(q_s), p_a = smem_u32(p_s);
-        // the scores of chunk `it` into S buffer it % 2
-        auto issue_s = [&](int it) -> bool {
-            int s = it % AT_STAGES;
-            if (!mbar_wait(bar(1 + s), (it / AT_STAGES) & 1, abort, err, 23))
-                return false;
-            tc_fence_after();
-            uint32_t k_a = smem_u32(kv_s + s * Cfg::KV_STAGE);
+        int tiles = has_b ? 2 : 1;
+        bool ok = mbar_wait(bar(0), 0, abort, err, 22);
+        // the scores of chunk `it` of block t; the chunk's keys are in unit 2 it
+        auto issue_s = [&](int it, int t) {
+            uint32_t q_a = smem_u32(q_s + t * Cfg::Q_TILE);
+            uint32_t k_a = smem_u32(kv_s + ((2 * it) % PF_UNITS) * Cfg::UNIT);
 #pragma unroll
             for (int kk = 0; kk < HD / 16; kk++) {
                 uint32_t off = (kk / 4) * BLK_BYTES + (kk % 4) * 32;
-                tc_mma(tmem_s + (it & 1) * AT_KEYS, smem_desc_sw128(q_a + off, 16, 1024),
+                tc_mma(tmem + t * AT_KEYS, smem_desc_sw128(q_a + off, 16, 1024),
                        smem_desc_sw128(k_a + off, 16, 1024), idesc_s, kk != 0);
             }
-            tc_commit(bar(5 + (it & 1)));
-            return true;
+            tc_commit(bar(7 + t));
         };
-        bool ok = mbar_wait(bar(0), 0, abort, err, 22) && issue_s(0);
-        for (int it = 0; it < n_chunks && ok; it++) {
-            // this chunk's K and V stay in their stage until its P V is done, so the
-            // next chunk's scores need the other stage: two stages suffice
-            if (it + 1 < n_chunks)
-                ok = issue_s(it + 1);
-            ok = ok && mbar_wait(bar(7 + (it & 1)), (it >> 1) & 1, abort, err, 25);   // P is there
-            if (ok && it > 0)
-                ok = mbar_wait(bar(10), (it - 1) & 1, abort, err, 26);   // the last PV was read
-            if (!ok)
-                break;
+        auto keys_there = [&](int it) {
+            int u = 2 * it;
+            bool there = mbar_wait(bar(1 + u % PF_UNITS), (u / PF_UNITS) & 1, abort, err, 23);
             tc_fence_after();
-            int s = it % AT_STAGES;
-            uint32_t v_a = smem_u32(kv_s + s * Cfg::KV_STAGE) + NB * BLK_BYTES;
-            uint32_t pb = p_a + (it & 1) * Cfg::P_BYTES;
+            return there;
+        };
+        if (ok && (ok = keys_there(0))) {
+            for (int t = 0; t < tiles; t++)
+                issue_s(0, t);
+            tc_commit(bar(4 + 0));                 // the keys' unit is free once these are done
+        }
+        for (int it = 0; it < n_chunks && ok; it++) {
+            int uv = 2 * it + 1, sv = uv % PF_UNITS;
+            bool more = it + 1 < n_chunks;
+            for (int t = 0; t < tiles && ok; t++) {
+                ok = mbar_wait(bar(9 + t), it & 1, abort, err, 25);               // P is there
+                if (ok && t == 0)
+                    ok = mbar_wait(bar(1 + sv), (uv / PF_UNITS) & 1, abort, err, 26);   // the values
+                if (!ok)
+                    break;
+                tc_fence_after();
+                uint32_t v_a = smem_u32(kv_s + sv * Cfg::UNIT);
+                uint32_t pb = smem_u32(p_s + t * Cfg::P_TILE);
 #pragma unroll
-            for (int kk = 0; kk < AT_KEYS / 16; kk++) {
-                uint32_t p_off = (kk / 4) * BLK_BYTES + (kk % 4) * 32;
-                tc_mma(tmem_pv, smem_desc_sw128(pb + p_off, 16, 1024),
-                       smem_desc_sw128(v_a + kk * 16 * 128, BLK_BYTES, 1024), idesc_pv, kk != 0);
+                for (int kk = 0; kk < AT_KEYS / 16; kk++) {
+                    uint32_t p_off = (kk / 4) * BLK_BYTES + (kk % 4) * 32;
+                    tc_mma(tmem + 2 * AT_KEYS + t * HD, smem_desc_sw128(pb + p_off, 16, 1024),
+                           smem_desc_sw128(v_a + kk * 16 * 128, BLK_BYTES, 1024), idesc_pv,
+                           (it | kk) != 0);
+                }
+                tc_commit(bar(11 + t));
+                if (t == tiles - 1)
+                    tc_commit(bar(4 + sv));        // the values' unit is free
+                // this block's next scores, while its row threads are still idle
+                if (more) {
+                    if (t == 0)
+                        ok = keys_there(it + 1);
+                    if (!ok)
+                        break;
+                    issue_s(it + 1, t);
+                    if (t == tiles - 1)
+                        tc_commit(bar(4 + (2 * (it + 1)) % PF_UNITS));
+                }
             }
-            tc_commit(bar(9));
-            tc_commit(bar(3 + s));
         }
     } else if (warp >= 2) {
         // ------------------------------------------------------------ row threads
+        int t = (warp - 2) >> 2;                // block A or B
         int qw = warp & 3;                      // the TMEM lanes this warp may read
-        int hf = (warp - 2) >> 2;               // which half of the keys and of the values
         int r = qw * 32 + lane;                 // this thread's row of the block
         int j = r / G, g = r - j * G;           // position within the block, head of the group
-        bool live = j < q_count && j < R;
-        int pos = q_pos + j;
+        int jq = t * R + j;                     // position within the CTA's run
+        bool live = j < R && jq < q_count;
+        bool tile_live = t == 0 || has_b;
+        int pos = q_pos + jq;
         int lo = window > 0 && pos + 1 > window ? pos + 1 - window : 0;
-        int pos_last = q_pos + q_count - 1;                 // the block's last position
+        // the block's first and last position: chunks between them need no mask
+        int pos_first = q_pos + t * R;
+        int pos_last = min(q_pos + q_count, pos_first + R) - 1;
         int lo_last = window > 0 && pos_last + 1 > window ? pos_last + 1 - window : 0;
         uint32_t lane_addr = (uint32_t)(qw * 32) << 16;
+        uint32_t tmem_s = tmem + t * AT_KEYS + lane_addr;
+        uint32_t tmem_o = tmem + 2 * AT_KEYS + t * HD + lane_addr;
         const float c2 = scale * 1.4426950408889634f;      // scores in units of log2(e)
-        float m_run = -INFINITY, l_run = 0.0f;              // l_run: this thread's keys only
-        float alpha = 0.0f;                                 // of the chunk whose P V is pending
-        float o[HH];
-#pragma unroll
-        for (int i = 0; i < HH; i++)
-            o[i] = 0.0f;
+        float m_ref = -INFINITY, l_run = 0.0f;
         bool ok = true;
-        // P V of chunk `it` joins the running output, scaled by that chunk's factor
-        auto take_o = [&](int it) {
-            ok = ok && mbar_wait(bar(9), it & 1, abort, err, 28);
+        for (int it = 0; it < n_chunks && tile_live; it++) {
+            int t0 = (c_first + it) * AT_KEYS;              // the chunk's first key
+            ok = ok && mbar_wait(bar(7 + t), it & 1, abort, err, 27);
             ok = __all_sync(0xffffffffu, ok);
             tc_fence_after();
-            if (ok) {
-#pragma unroll
-                for (int db = 0; db < HH / 32; db++) {
-                    float pv[32];
-                    tc_ld32(tmem_pv + lane_addr + hf * HH + db * 32, pv);
-#pragma unroll
-                    for (int i = 0; i < 32; i++)
-                        o[db * 32 + i] = o[db * 32 + i] * alpha + pv[i];
-                }
-            }
-            tc_fence_before();
-            mbar_arrive(bar(10));
-        };
-        for (int it = 0; it < n_chunks; it++) {
-            int t0 = (c_first + it) * AT_KEYS + hf * 64;    // this thread's first key
-            float *swap = pair + (it & 1) * 2 * AT_ROWS;
-            ok = ok && mbar_wait(bar(5 + (it & 1)), (it >> 1) & 1, abort, err, 27);
-            ok = __all_sync(0xffffffffu, ok);
-            tc_fence_after();
-            uint32_t raw[64];
+            uint32_t raw[AT_KEYS];
             float mx = -INFINITY;
             if (ok) {
-                uint32_t sa = tmem_s + (it & 1) * AT_KEYS + lane_addr + hf * 64;
-                tc_ld32_nowait(sa, raw);
-                tc_ld32_nowait(sa + 32, raw + 32);
+#pragma unroll
+                for (int cb = 0; cb < AT_KEYS / 32; cb++)
+                    tc_ld32_nowait(tmem_s + cb * 32, raw + cb * 32);
                 tc_ld_wait();
                 // most chunks lie wholly inside every row's range: no key is masked.
                 // The maximum is taken over the raw scores (the scale is positive)
                 // and scaled once; the scale itself goes into the exponent's FMA.
-                bool inside = t0 + 63 <= q_pos && t0 >= lo_last;
+                bool inside = t0 + AT_KEYS - 1 <= pos_first && t0 >= lo_last;
+                float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
                 if (inside && live) {
 #pragma unroll
-                    for (int i = 0; i < 64; i++)
-                        mx = fmaxf(mx, __uint_as_float(raw[i]));
+                    for (int i = 0; i < AT_KEYS; i += 4)
+#pragma unroll
+                        for (int e = 0; e < 4; e++)
+                            m4[e] = fmaxf(m4[e], __uint_as_float(raw[i + e]));
                 } else {
 #pragma unroll
-                    for (int i = 0; i < 64; i++) {
-                        int t = t0 + i;
-                        float v = (live && t <= pos && t >= lo) ? __uint_as_float(raw[i]) : -INFINITY;
-                        raw[i] = __float_as_uint(v);
-                        mx = fmaxf(mx, v);
-                    }
-                }
-                mx *= c2;
-            }
-            swap[hf * AT_ROWS + r] = mx;
-            named_barrier(1, 2 * AT_ROWS);
-            mx = fmaxf(mx, swap[(hf ^ 1) * AT_ROWS + r]);
-            // the chunk before this one goes into the output with ITS factor
-            if (it > 0)
-                take_o(it - 1);
-            float m_new = fmaxf(m_run, mx);
-            alpha = m_run == -INFINITY ? 0.0f : exp2f(m_run - m_new);
-            if (m_new == -INFINITY)
-                alpha = 1.0f;
-            float l_chunk = 0.0f;
-            // with nothing visible yet the maximum is -inf: subtract 0 instead, every
-            // score is -inf and every weight 0
-            float m_use = m_new == -INFINITY ? 0.0f : m_new;
-            if (ok) {
-                uint8_t *blk = p_s + (it & 1) * Cfg::P_BYTES + hf * BLK_BYTES;
+                    for (int i = 0; i < AT_KEYS; i += 4)
 #pragma unroll
-                for (int q8 = 0; q8 < 8; q8++) {
+                        for (int e = 0; e < 4; e++) {
+                            int key = t0 + i + e;
+                            float v = (live && key <= pos && key >= lo)
+                                          ? __uint_as_float(raw[i + e]) : -INFINITY;
+                            raw[i + e] = __float_as_uint(v);
+                            m4[e] = fmaxf(m4[e], v);
+                        }
+                }
+                mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * c2;
+            }
+            // P of the chunk before has been read, and O is whole, once that chunk's
+            // P V is done
+            if (it > 0) {
+                ok = ok && mbar_wait(bar(11 + t), (it - 1) & 1, abort, err, 28);
+                ok = __all_sync(0xffffffffu, ok);
+                tc_fence_after();
+            }
+            // move the row's reference only when the maximum has run far ahead of it
+            bool move = mx > m_ref + PF_LAZY || (m_ref == -INFINITY && mx > -INFINITY);
+            float alpha = 1.0f;
+            if (move) {
+                alpha = m_ref == -INFINITY ? 0.0f : exp2f(m_ref - mx);
+                m_ref = mx;
+                l_run *= alpha;
+            }
+            if (ok && it > 0 && __any_sync(0xffffffffu, move)) {
+                // the warp's rows of O, 32 values at a time; rows that stay keep factor 1
+#pragma unroll 1
+                for (int db = 0; db < HD / 32; db++) {
+                    uint32_t ov[32];
+                    tc_ld32_nowait(tmem_o + db * 32, ov);
+                    tc_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; i++)
+                        ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
+                    tc_st32(tmem_o + db * 32, ov);
+                }
+                tc_st_wait();
+            }
+            // with nothing visible yet the reference is -inf: subtract 0 instead, every
+            // score is -inf and every weight 0
+            float m_use = m_ref == -INFINITY ? 0.0f : m_ref;
+            float l4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            if (ok) {
+                uint8_t *tile = p_s + t * Cfg::P_TILE;
+#pragma unroll
+                for (int q8 = 0; q8 < AT_KEYS / 8; q8++) {
                     uint32_t w[4];
 #pragma unroll
                     for (int e = 0; e < 4; e++) {
-                        // a masked score is -inf and m_new is finite here or the row
-                        // is not live: 2^(-inf) = 0
                         float s0 = __uint_as_float(raw[8 * q8 + 2 * e]);
                         float s1 = __uint_as_float(raw[8 * q8 + 2 * e + 1]);
                         float p0 = fast_exp2(fmaf(s0, c2, -m_use));
                         float p1 = fast_exp2(fmaf(s1, c2, -m_use));
-                        l_chunk += p0 + p1;
+                        l4[e] += p0 + p1;
                         __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
                         w[e] = *reinterpret_cast<uint32_t *>(&pk);
                     }
-                    *reinterpret_cast<uint4 *>(blk + swz(r, q8)) = make_uint4(w[0], w[1], w[2], w[3]);
+                    // keys 8 q8 .. 8 q8 + 7: block q8 / 8, 16-byte chunk q8 % 8 of the row
+                    *reinterpret_cast<uint4 *>(tile + (q8 / 8) * BLK_BYTES + swz(r, q8 % 8)) =
+                        make_uint4(w[0], w[1], w[2], w[3]);
                 }
             }
             fence_async_smem();
             tc_fence_before();
-            mbar_arrive(bar(7 + (it & 1)));
-            l_run = l_run * alpha + l_chunk;
-            m_run = m_new;
+            mbar_arrive(bar(9 + t));
+            l_run += (l4[0] + l4[1]) + (l4[2] + l4[3]);
         }
-        take_o(n_chunks - 1);
-        // the row's sum: both threads' keys
-        named_barrier(1, 2 * AT_ROWS);
-        pair[hf * AT_ROWS + r] = l_run;
-        named_barrier(1, 2 * AT_ROWS);
-        float l_all = l_run + pair[(hf ^ 1) * AT_ROWS + r];
-        if (ok && live) {
-            float inv = 1.0f / l_all;
-            bf16 *dst = out + ((size_t)(q_row + j) * nh + kvh * G + g) * HD + hf * HH;
+        if (tile_live) {
+            ok = ok && mbar_wait(bar(11 + t), (n_chunks - 1) & 1, abort, err, 29);
+            ok = __all_sync(0xffffffffu, ok);
+            tc_fence_after();
+            float inv = 1.0f / l_run;
+            bf16 *dst = out + ((size_t)(q_row + jq) * nh + kvh * G + g) * HD;
+#pragma unroll 1
+            for (int db = 0; db < HD / 32; db++) {
+                float ov[32];
+                if (ok)
+                    tc_ld32(tmem_o + db * 32, ov);
+                if (ok && live) {
 #pragma unroll
-            for (int i = 0; i < HH; i += 8) {
-                uint32_t w[4];
+                    for (int i = 0; i < 32; i += 8) {
+                        uint32_t w[4];
 #pragma unroll
-                for (int e = 0; e < 4; e++) {
-                    __nv_bfloat162 pk =
-                        __floats2bfloat162_rn(o[i + 2 * e] * inv, o[i + 2 * e + 1] * inv);
-                    w[e] = *reinterpret_cast<uint32_t *>(&pk);
+                        for (int e = 0; e < 4; e++) {
+                            __nv_bfloat162 pk = __floats2bfloat162_rn(ov[i + 2 * e] * inv,
+                                                                      ov[i + 2 * e + 1] * inv);
+                            w[e] = *reinterpret_cast<uint32_t *>(&pk);
+                        }
+                        *reinterpret_cast<uint4 *>(dst + db * 32 + i) =
+                            make_uint4(w[0], w[1], w[2], w[3]);
+                    }
                 }
-                *reinterpret_cast<uint4 *>(dst + i) = make_uint4(w[0], w[1], w[2], w[3]);
             }
         }
     }
@@ -1111,12 +1149,11 @@ extern "C" int jb_attn_tc_ok(int nh, int nkv, int hd)
            nkv <= 65535;
 }
 
-// Positions of one sequence that a prefill block holds: 128 rows / heads per group.
+// Positions of one sequence that a CTA of the prefill kernel holds (an entry of qblk).
 extern "C" int jb_attn_tc_block_positions(int nh, int nkv)
 {
     int G = nh / nkv;
-    int R = AT_ROWS / G;
-    return R > 256 ? 256 : R;
+    return 2 * (AT_ROWS / G);      // a CTA of the prefill kernel holds two blocks of 128 rows
 }
 
 // Prefill rows.  q, out: [n, nh, hd] bfloat16; caches [n_pages, nkv, PAGE, hd].
@@ -1129,8 +1166,8 @@ extern "C" int jb_attn_tc_prefill(const void *q, const void *k_cache, const void
 {
     if (!jb_attn_tc_ok(nh, nkv, hd) || n <= 0)
         return JB_EINVAL;
-    int R = jb_attn_tc_block_positions(nh, nkv);
     int G = nh / nkv;
+    int R = AT_ROWS / G;               // positions of one block; qblk's runs hold up to 2 R
     CUtensorMap mq, mk, mv;
     if (!attn_tensor_map(q, hd, nh, n, G, R, &mq) ||
         !attn_tensor_map(k_cache, hd, n_pages * nkv * PAGE, 0, PAGE, 0, &mk) ||

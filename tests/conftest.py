@@ -12,6 +12,13 @@ sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (a B200)")
+    # The plain implementation is the tests' yardstick, so its float32 results must
+    # not depend on how a library splits work over host threads.  Seen with 16
+    # threads: the first attention product of a process was off by 3e-5 in a block of
+    # rows about once in six processes (and right when computed again); never with one
+    # thread.  The tiny models need no more.
+    import torch
+    torch.set_num_threads(1)
 
 
 def pytest_collection_modifyitems(config, items):
