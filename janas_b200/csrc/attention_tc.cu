@@ -433,8 +433,8 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
     uint8_t *kv_s = p_s + 2 * Cfg::P_TILE;
     uint64_t *bars = (uint64_t *)(kv_s + PF_UNITS * Cfg::UNIT);
     // bars: 0 q_full | 1..3 unit full | 4..6 unit free | 7,8 s_full A,B | 9,10 p_full A,B |
-    //       11,12 pv_done A,B
-    uint32_t *tmem_slot = (uint32_t *)(bars + 13);
+    //       11,12 pv_done A,B | 13,14 s_free A,B
+    uint32_t *tmem_slot = (uint32_t *)(bars + 15);
     volatile int *abort = (volatile int *)(tmem_slot + 1);
 
     int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -443,8 +443,10 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
         prefetch_tensor_map(&map_k);
         prefetch_tensor_map(&map_v);
     }
-    int kvh = blockIdx.y;
-    const int32_t *b = qblk + 4 * (gridDim.x - 1 - blockIdx.x);   // long blocks first
+    // qblk lists the longest runs first; all KV heads of a run are neighbours in the
+    // grid, so that CTAs start in the order of their length
+    int kvh = blockIdx.x % nkv;
+    const int32_t *b = qblk + 4 * (blockIdx.x / nkv);
     int q_row = b[0], q_count = b[1], q_pos = b[2], seq = b[3];
     bool has_b = q_count > R;                                    // the second block has rows
     int lo0 = window > 0 && q_pos + 1 > window ? q_pos + 1 - window : 0;
@@ -466,6 +468,7 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
             mbar_init(bar(7 + t), 1);
             mbar_init(bar(9 + t), AT_ROWS);
             mbar_init(bar(11 + t), 1);
+            mbar_init(bar(13 + t), AT_ROWS);
         }
         *abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -553,8 +556,22 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
             tc_commit(bar(4 + 0));                 // the keys' unit is free once these are done
         }
         for (int it = 0; it < n_chunks && ok; it++) {
+            // the next chunk's scores as soon as the row threads hold this chunk's in
+            // registers: they are there when the row threads come back for them
+            if (it + 1 < n_chunks) {
+                ok = keys_there(it + 1);
+                for (int t = 0; t < tiles && ok; t++) {
+                    ok = mbar_wait(bar(13 + t), it & 1, abort, err, 30);
+                    if (!ok)
+                        break;
+                    tc_fence_after();
+                    issue_s(it + 1, t);
+                }
+                if (!ok)
+                    break;
+                tc_commit(bar(4 + (2 * (it + 1)) % PF_UNITS));
+            }
             int uv = 2 * it + 1, sv = uv % PF_UNITS;
-            bool more = it + 1 < n_chunks;
             for (int t = 0; t < tiles && ok; t++) {
                 ok = mbar_wait(bar(9 + t), it & 1, abort, err, 25);               // P is there
                 if (ok && t == 0)
@@ -574,16 +591,6 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
                 tc_commit(bar(11 + t));
                 if (t == tiles - 1)
                     tc_commit(bar(4 + sv));        // the values' unit is free
-                // this block's next scores, while its row threads are still idle
-                if (more) {
-                    if (t == 0)
-                        ok = keys_there(it + 1);
-                    if (!ok)
-                        break;
-                    issue_s(it + 1, t);
-                    if (t == tiles - 1)
-                        tc_commit(bar(4 + (2 * (it + 1)) % PF_UNITS));
-                }
             }
         }
     } else if (warp >= 2) {
@@ -619,6 +626,9 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
                 for (int cb = 0; cb < AT_KEYS / 32; cb++)
                     tc_ld32_nowait(tmem_s + cb * 32, raw + cb * 32);
                 tc_ld_wait();
+                // the scores are in registers: the tensor core may write the next chunk's
+                tc_fence_before();
+                mbar_arrive(bar(13 + t));
                 // most chunks lie wholly inside every row's range: no key is masked.
                 // The maximum is taken over the raw scores (the scale is positive)
                 // and scaled once; the scale itself goes into the exponent's FMA.
@@ -1158,7 +1168,8 @@ extern "C" int jb_attn_tc_block_positions(int nh, int nkv)
 
 // Prefill rows.  q, out: [n, nh, hd] bfloat16; caches [n_pages, nkv, PAGE, hd].
 // qblk: int32 [n_blocks][4] = first row, positions (<= block positions), the
-// first row's position, the sequence's index in block_table.
+// first row's position, the sequence's index in block_table; CTAs start in this
+// order, so the runs that see the most keys should come first.
 extern "C" int jb_attn_tc_prefill(const void *q, const void *k_cache, const void *v_cache,
                                   long long n_pages, const int32_t *qblk, int n_blocks,
                                   const int32_t *block_table, int bt_stride, void *out, int n,
@@ -1185,7 +1196,7 @@ extern "C" int jb_attn_tc_prefill(const void *q, const void *k_cache, const void
                 return JB_ELAUNCH;                                                             \
             attr_set = true;                                                                   \
         }                                                                                      \
-        launch(attn_tc_prefill_kernel<HDV>, dim3(n_blocks, nkv), PF_THREADS,                   \
+        launch(attn_tc_prefill_kernel<HDV>, dim3((unsigned)n_blocks * nkv), PF_THREADS,        \
                PrefillCfg<HDV>::SMEM_BYTES, st, mq, mk, mv, qblk, block_table, bt_stride,      \
                (bf16 *)out, nh, nkv, G, R, window, scale);                                     \
     } while (0)

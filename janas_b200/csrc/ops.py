@@ -245,6 +245,8 @@ def attention_blocks(seq_row0, seq_pos0, seq_len, positions_per_block: int,
     for i, (r0, p0, n) in enumerate(zip(seq_row0, seq_pos0, seq_len)):
         for a in range(0, int(n), positions_per_block):
             rows.append((int(r0) + a, min(positions_per_block, int(n) - a), int(p0) + a, i))
+    # the runs that end latest see the most keys and take longest: they start first
+    rows.sort(key=lambda b: -(b[2] + b[1]))
     return torch.from_numpy(np.asarray(rows, dtype=np.int32).reshape(-1, 4)).to(device)
 
 
