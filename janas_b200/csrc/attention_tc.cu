@@ -400,8 +400,8 @@ attn_tc_rows_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 // 2^(m_old - m_new) before it hands P over.  After the first chunks that is rare.
 //
 // Tensor memory: S_A [0, 128), S_B [128, 256), O_A [256, 256 + HD), O_B after it.
-// Shared memory: Q_A, Q_B, P_A, P_B, and a ring of three units that hold in turn
-// the keys of a chunk, its values, the next chunk's keys ...
+// Shared memory: Q_A, Q_B, P_A, P_B, and a ring of three units that hold keys and
+// values in the order of their use: K0 K1 V0 K2 V1 K3 ...
 constexpr int PF_THREADS = 320;     // warp 0 loads, warp 1 issues MMAs, 2..5 rows of A, 6..9 of B
 constexpr int PF_UNITS = 3;
 constexpr float PF_LAZY = 8.0f;     // how far (in powers of two) a maximum may run ahead of m
@@ -497,15 +497,18 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
                             bb * 64, kvh * G, q_row + t * R);
         const int32_t *bt = block_table + (size_t)seq * bt_stride;
         uint32_t armed = 0, last_parity = 0;
-        for (int u = 0; u < 2 * n_chunks; u++) {       // unit u: K (even) or V (odd) of chunk u / 2
+        for (int u = 0; u < 2 * n_chunks; u++) {       // units in the order they are used
             int s = u % PF_UNITS;
             uint32_t ph = (u / PF_UNITS) & 1;
             if (!mbar_wait(bar(4 + s), ph ^ 1, abort, err, 21))
                 break;
             mbar_expect_tx(bar(1 + s), Cfg::UNIT);
             uint32_t dst = smem_u32(kv_s + s * Cfg::UNIT);
-            const CUtensorMap *map = (u & 1) ? &map_v : &map_k;
-            int c = c_first + u / 2;
+            bool is_v = u == 2 * n_chunks - 1 || (u > 0 && (u & 1) == 0);
+            int chunk = u == 0 ? 0 : u == 2 * n_chunks - 1 ? n_chunks - 1 : is_v ? (u - 2) / 2
+                                                                            : (u + 1) / 2;
+            const CUtensorMap *map = is_v ? &map_v : &map_k;
+            int c = c_first + chunk;
 #pragma unroll
             for (int pg = 0; pg < 2; pg++) {
                 int idx = 2 * c + pg;
@@ -531,11 +534,16 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
         constexpr uint32_t idesc_s = instr_desc_bf16(AT_ROWS, AT_KEYS, false);
         constexpr uint32_t idesc_pv = instr_desc_bf16(AT_ROWS, HD, true);
         int tiles = has_b ? 2 : 1;
+        // The ring's units in the order of their use: K0, then for every chunk the next
+        // chunk's keys before this chunk's values (K1 V0 K2 V1 ...), so that a unit is
+        // asked for a whole chunk before it is needed.
+        auto unit_k = [&](int j) { return j == 0 ? 0 : 2 * j - 1; };
+        auto unit_v = [&](int j) { return j == n_chunks - 1 ? 2 * n_chunks - 1 : 2 * j + 2; };
         bool ok = mbar_wait(bar(0), 0, abort, err, 22);
         // the scores of chunk `it` of block t; the chunk's keys are in unit 2 it
         auto issue_s = [&](int it, int t) {
             uint32_t q_a = smem_u32(q_s + t * Cfg::Q_TILE);
-            uint32_t k_a = smem_u32(kv_s + ((2 * it) % PF_UNITS) * Cfg::UNIT);
+            uint32_t k_a = smem_u32(kv_s + (unit_k(it) % PF_UNITS) * Cfg::UNIT);
 #pragma unroll
             for (int kk = 0; kk < HD / 16; kk++) {
                 uint32_t off = (kk / 4) * BLK_BYTES + (kk % 4) * 32;
@@ -545,7 +553,7 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
             tc_commit(bar(7 + t));
         };
         auto keys_there = [&](int it) {
-            int u = 2 * it;
+            int u = unit_k(it);
             bool there = mbar_wait(bar(1 + u % PF_UNITS), (u / PF_UNITS) & 1, abort, err, 23);
             tc_fence_after();
             return there;
@@ -569,9 +577,9 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
                 }
                 if (!ok)
                     break;
-                tc_commit(bar(4 + (2 * (it + 1)) % PF_UNITS));
+                tc_commit(bar(4 + unit_k(it + 1) % PF_UNITS));
             }
-            int uv = 2 * it + 1, sv = uv % PF_UNITS;
+            int uv = unit_v(it), sv = uv % PF_UNITS;
             for (int t = 0; t < tiles && ok; t++) {
                 ok = mbar_wait(bar(9 + t), it & 1, abort, err, 25);               // P is there
                 if (ok && t == 0)
@@ -654,13 +662,6 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
                 }
                 mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * c2;
             }
-            // P of the chunk before has been read, and O is whole, once that chunk's
-            // P V is done
-            if (it > 0) {
-                ok = ok && mbar_wait(bar(11 + t), (it - 1) & 1, abort, err, 28);
-                ok = __all_sync(0xffffffffu, ok);
-                tc_fence_after();
-            }
             // move the row's reference only when the maximum has run far ahead of it
             bool move = mx > m_ref + PF_LAZY || (m_ref == -INFINITY && mx > -INFINITY);
             float alpha = 1.0f;
@@ -668,6 +669,29 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
                 alpha = m_ref == -INFINITY ? 0.0f : exp2f(m_ref - mx);
                 m_ref = mx;
                 l_run *= alpha;
+            }
+            // with nothing visible yet the reference is -inf: subtract 0 instead, every
+            // score is -inf and every weight 0
+            float m_use = m_ref == -INFINITY ? 0.0f : m_ref;
+            // the weights, two bfloat16 to a register, in place of the scores
+            float l4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+            for (int i = 0; i < AT_KEYS / 2; i += 4) {
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    float p0 = fast_exp2(fmaf(__uint_as_float(raw[2 * (i + e)]), c2, -m_use));
+                    float p1 = fast_exp2(fmaf(__uint_as_float(raw[2 * (i + e) + 1]), c2, -m_use));
+                    l4[e] += p0 + p1;
+                    __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
+                    raw[i + e] = *reinterpret_cast<uint32_t *>(&pk);
+                }
+            }
+            // P of the chunk before has been read, and O is whole, once that chunk's
+            // P V is done: only now is that needed
+            if (it > 0) {
+                ok = ok && mbar_wait(bar(11 + t), (it - 1) & 1, abort, err, 28);
+                ok = __all_sync(0xffffffffu, ok);
+                tc_fence_after();
             }
             if (ok && it > 0 && __any_sync(0xffffffffu, move)) {
                 // the warp's rows of O, 32 values at a time; rows that stay keep factor 1
@@ -683,29 +707,13 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
                 }
                 tc_st_wait();
             }
-            // with nothing visible yet the reference is -inf: subtract 0 instead, every
-            // score is -inf and every weight 0
-            float m_use = m_ref == -INFINITY ? 0.0f : m_ref;
-            float l4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
             if (ok) {
                 uint8_t *tile = p_s + t * Cfg::P_TILE;
+                // keys 8 q8 .. 8 q8 + 7: block q8 / 8, 16-byte chunk q8 % 8 of the row
 #pragma unroll
-                for (int q8 = 0; q8 < AT_KEYS / 8; q8++) {
-                    uint32_t w[4];
-#pragma unroll
-                    for (int e = 0; e < 4; e++) {
-                        float s0 = __uint_as_float(raw[8 * q8 + 2 * e]);
-                        float s1 = __uint_as_float(raw[8 * q8 + 2 * e + 1]);
-                        float p0 = fast_exp2(fmaf(s0, c2, -m_use));
-                        float p1 = fast_exp2(fmaf(s1, c2, -m_use));
-                        l4[e] += p0 + p1;
-                        __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
-                        w[e] = *reinterpret_cast<uint32_t *>(&pk);
-                    }
-                    // keys 8 q8 .. 8 q8 + 7: block q8 / 8, 16-byte chunk q8 % 8 of the row
+                for (int q8 = 0; q8 < AT_KEYS / 8; q8++)
                     *reinterpret_cast<uint4 *>(tile + (q8 / 8) * BLK_BYTES + swz(r, q8 % 8)) =
-                        make_uint4(w[0], w[1], w[2], w[3]);
-                }
+                        make_uint4(raw[4 * q8], raw[4 * q8 + 1], raw[4 * q8 + 2], raw[4 * q8 + 3]);
             }
             fence_async_smem();
             tc_fence_before();
