@@ -542,13 +542,15 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
         bool ok = mbar_wait(bar(0), 0, abort, err, 22);
         // the scores of chunk `it` of block t; the chunk's keys are in unit 2 it
         auto issue_s = [&](int it, int t) {
-            uint32_t q_a = smem_u32(q_s + t * Cfg::Q_TILE);
-            uint32_t k_a = smem_u32(kv_s + (unit_k(it) % PF_UNITS) * Cfg::UNIT);
+            // one descriptor per operand; the steps along k are added to its address
+            // field (16-byte units), so that the one issuing thread has little to compute
+            uint64_t dq = smem_desc_sw128(smem_u32(q_s + t * Cfg::Q_TILE), 16, 1024);
+            uint64_t dk = smem_desc_sw128(
+                smem_u32(kv_s + (unit_k(it) % PF_UNITS) * Cfg::UNIT), 16, 1024);
 #pragma unroll
             for (int kk = 0; kk < HD / 16; kk++) {
-                uint32_t off = (kk / 4) * BLK_BYTES + (kk % 4) * 32;
-                tc_mma(tmem + t * AT_KEYS, smem_desc_sw128(q_a + off, 16, 1024),
-                       smem_desc_sw128(k_a + off, 16, 1024), idesc_s, kk != 0);
+                uint64_t off = (uint64_t)(((kk / 4) * BLK_BYTES + (kk % 4) * 32) >> 4);
+                tc_mma(tmem + t * AT_KEYS, dq + off, dk + off, idesc_s, kk != 0);
             }
             tc_commit(bar(7 + t));
         };
@@ -587,14 +589,13 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
                 if (!ok)
                     break;
                 tc_fence_after();
-                uint32_t v_a = smem_u32(kv_s + sv * Cfg::UNIT);
-                uint32_t pb = smem_u32(p_s + t * Cfg::P_TILE);
+                uint64_t dv = smem_desc_sw128(smem_u32(kv_s + sv * Cfg::UNIT), BLK_BYTES, 1024);
+                uint64_t dp = smem_desc_sw128(smem_u32(p_s + t * Cfg::P_TILE), 16, 1024);
 #pragma unroll
                 for (int kk = 0; kk < AT_KEYS / 16; kk++) {
-                    uint32_t p_off = (kk / 4) * BLK_BYTES + (kk % 4) * 32;
-                    tc_mma(tmem + 2 * AT_KEYS + t * HD, smem_desc_sw128(pb + p_off, 16, 1024),
-                           smem_desc_sw128(v_a + kk * 16 * 128, BLK_BYTES, 1024), idesc_pv,
-                           (it | kk) != 0);
+                    uint64_t p_off = (uint64_t)(((kk / 4) * BLK_BYTES + (kk % 4) * 32) >> 4);
+                    tc_mma(tmem + 2 * AT_KEYS + t * HD, dp + p_off, dv + (uint64_t)(kk * 128),
+                           idesc_pv, (it | kk) != 0);
                 }
                 tc_commit(bar(11 + t));
                 if (t == tiles - 1)
