@@ -4,12 +4,12 @@
 // memory by TMA; V is read as an MN-major operand as it lies in the page
 // ([position][value]).  Three kernels:
 //
-// attn_tc_prefill_kernel   A CTA works for one KV head on a block of 128 rows:
-//     the G query heads of the group for R = 128 / G consecutive positions of
-//     one sequence.  Per chunk S = Q K^T, softmax by two threads per row (scale,
-//     causal and window mask, running maximum, exp, sum; P to shared memory in
-//     bfloat16), PV = P V; the running (m, l, o) stays in registers; chunks are
-//     software-pipelined through a second S and a second P buffer.
+// attn_tc_prefill_kernel   A CTA works for one KV head on two blocks of 128 rows:
+//     the G query heads of the group for 2 R consecutive positions of one
+//     sequence (R = 128 / G a block).  Per chunk and block S = Q K^T, softmax by
+//     one thread per row (scale, causal and window mask, exp, sum; P to shared
+//     memory in bfloat16), O += P V with O in tensor memory; the blocks take
+//     turns on the tensor core and share the chunk's keys and values.
 //
 // attn_tc_decode_kernel    One decoded token, heads of 128 values, up to 16
 //     heads per KV head: the keys are the M operand (S^T = K Q^T, O^T = V^T P),

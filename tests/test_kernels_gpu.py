@@ -431,6 +431,43 @@ def test_attention_tensor_core_decode(nh, nkv, hd, window):
         assert err <= 2 ** -7, (mc, err)
 
 
+def test_attention_tensor_core_prefill_moves_its_reference():
+    """The prefill kernel keeps a row's exponent reference until a chunk's maximum
+    runs more than 2^8 ahead, then scales the row's output, which lies in tensor
+    memory.  Here the keys of the first chunk score 0, those of the second 2^9.5
+    above them and one key of the third another 2^9.5: the 128 keys of an earlier
+    chunk together still weigh a good part of what follows, so a wrong factor would
+    show."""
+    o = ops()
+    n, nh, nkv, hd = 400, 8, 2, 128
+    q = torch.zeros(n, nh, hd)
+    k = torch.zeros(n, nkv, hd)
+    v = rnd(n, nkv, hd).to(torch.bfloat16).float()
+    q[:, :, 3] = 8.0
+    step = 9.5 * math.sqrt(hd) / (8.0 * 1.4426950408889634)
+    k[128:256, :, 3] = step
+    k[260, :, 3] = 2 * step
+    k = k.bfloat16().float()
+    want = plain.attention(q.double(), k.double(), v.double(), 0).float()
+    kc, vc, bt = _paged_many([k.bfloat16()], [v.bfloat16()], 9, seed=2)
+    pos = torch.arange(n, dtype=torch.int32)
+    seq = torch.zeros(n, dtype=torch.int32)
+    per = o.attention_block_positions(nh, nkv)
+    blocks = o.attention_blocks([0], [0], [n], per, torch.device(DEV))
+    mc = (n - 1) // o.attention_chunk() + 1
+    got = o.attention(q.bfloat16().to(DEV), kc.to(DEV), vc.to(DEV), pos.to(DEV), seq.to(DEV),
+                      bt.to(DEV), 0, 1 / math.sqrt(hd), mc, blocks=blocks).cpu().float()
+    assert o.attn_tc_error() == 0
+    for rows in (slice(0, 128), slice(128, 260), slice(260, n)):     # 0, 1, 2 moves
+        err = (got[rows] - want[rows]).abs().max() / want[rows].abs().max()
+        assert err <= 2 ** -7, (rows, float(err))
+    # the earlier chunks do weigh: without them the answers are others
+    alone = v[260].repeat_interleave(nh // nkv, 0)
+    assert (want[300] - alone).abs().max() > 10 * 2 ** -7 * want[300].abs().max()
+    alone = v[128:131].mean(0).repeat_interleave(nh // nkv, 0)
+    assert (want[130] - alone).abs().max() > 3 * 2 ** -7 * want[130].abs().max()
+
+
 def test_attention_tensor_core_finds_a_far_key():
     """As for the plain kernel: one key among 700 stands out, with and without a
     window, for prefill rows and for a decoded token."""
