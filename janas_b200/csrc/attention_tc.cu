@@ -64,14 +64,14 @@ __device__ __forceinline__ uint32_t swz(int row, int j)
 
 template <int HD>
 __global__ void __launch_bounds__(192)
-attn_tc_rows_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-               const __grid_constant__ CUtensorMap map_v, const int32_t *__restrict__ qblk,
-               const int32_t *__restrict__ row_pos, const int32_t *__restrict__ row_seq,
-               const int32_t *__restrict__ block_table, int bt_stride, bf16 *__restrict__ out,
-               float *__restrict__ part, int nh, int nkv, int G, int R, int window, float scale,
-               int max_chunks, int chunks_per_cta, int row0)
+attn_tc_rows_kernel(const __grid_constant__ CUtensorMap map_q,
+                    const __grid_constant__ CUtensorMap map_k,
+                    const __grid_constant__ CUtensorMap map_v,
+                    const int32_t *__restrict__ row_pos, const int32_t *__restrict__ row_seq,
+                    const int32_t *__restrict__ block_table, int bt_stride,
+                    float *__restrict__ part, int nh, int nkv, int G, int window, float scale,
+                    int max_chunks, int chunks_per_cta, int row0)
 {
-    constexpr bool DECODE = true;      // this kernel serves decoded tokens only
     using Cfg = AttnCfg<HD>;
     constexpr int NB = Cfg::NB;
     extern __shared__ uint8_t smem_raw[];
@@ -87,36 +87,19 @@ attn_tc_rows_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     int kvh = blockIdx.y;
 
-    // ---- what this CTA works on
-    int q_row, q_count, q_pos, seq, c_first, c_last, lrow = 0;
-    if (DECODE) {
-        lrow = blockIdx.x / ((max_chunks + chunks_per_cta - 1) / chunks_per_cta);
-        int part_i = blockIdx.x % ((max_chunks + chunks_per_cta - 1) / chunks_per_cta);
-        q_row = row0 + lrow;
-        q_count = 1;
-        q_pos = row_pos[q_row];
-        seq = row_seq[q_row];
-        int lo = window > 0 && q_pos + 1 > window ? q_pos + 1 - window : 0;
-        c_first = lo / AT_KEYS + part_i * chunks_per_cta;
-        c_last = min(q_pos / AT_KEYS, c_first + chunks_per_cta - 1);
-    } else {
-        const int32_t *b = qblk + 4 * (gridDim.x - 1 - blockIdx.x);   // long blocks first
-        q_row = b[0];
-        q_count = b[1];
-        q_pos = b[2];
-        seq = b[3];
-        int lo = window > 0 && q_pos + 1 > window ? q_pos + 1 - window : 0;
-        c_first = lo / AT_KEYS;
-        c_last = (q_pos + q_count - 1) / AT_KEYS;
-    }
+    // ---- what this CTA works on: a run of chunks of one decoded token
+    int parts = (max_chunks + chunks_per_cta - 1) / chunks_per_cta;
+    int lrow = blockIdx.x / parts, part_i = blockIdx.x % parts;
+    int q_row = row0 + lrow;
+    int q_pos = row_pos[q_row];
+    int seq = row_seq[q_row];
+    int lo = window > 0 && q_pos + 1 > window ? q_pos + 1 - window : 0;
+    int c_base = lo / AT_KEYS;         // the row's first chunk (index 0 of its partials)
+    int c_first = c_base + part_i * chunks_per_cta;
+    int c_last = min(q_pos / AT_KEYS, c_first + chunks_per_cta - 1);
     int n_chunks = c_last - c_first + 1;
     if (n_chunks <= 0)
         return;                        // nothing to do: before any barrier or tensor memory
-    int c_base = 0;                    // decode: the row's first chunk (index 0 of its partials)
-    if (DECODE) {
-        int lo = window > 0 && q_pos + 1 > window ? q_pos + 1 - window : 0;
-        c_base = lo / AT_KEYS;
-    }
 
     uint32_t bar0 = smem_u32(bars);
     auto bar = [&](int i) { return bar0 + 8 * i; };
@@ -150,8 +133,7 @@ attn_tc_rows_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 
     if (warp == 0 && lane == 0) {
         // ---------------------------------------------------------- TMA loads
-        int rbox = DECODE ? 1 : R;
-        mbar_expect_tx(bar(0), (uint32_t)(rbox * G * HD * 2));
+        mbar_expect_tx(bar(0), (uint32_t)(G * HD * 2));
 #pragma unroll
         for (int b = 0; b < NB; b++)
             tma_load_3d(smem_u32(q_s + b * BLK_BYTES), &map_q, bar(0), b * 64, kvh * G, q_row);
@@ -234,20 +216,12 @@ attn_tc_rows_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         // ------------------------------------------------------------ row threads
         int qw = warp & 3;                      // the TMEM lanes this warp may read
         int r = qw * 32 + lane;                 // this thread's row of the block
-        int j = r / G, g = r - j * G;           // position within the block, head of the group
-        bool live = DECODE ? (r < G) : (j < q_count && j < R);
+        int g = r;                              // the head of the group
+        bool live = r < G;
         bool warp_live = __any_sync(0xffffffffu, live);
-        int pos = q_pos + j;
-        int lo = window > 0 && pos + 1 > window ? pos + 1 - window : 0;
+        int pos = q_pos;
         uint32_t lane_addr = (uint32_t)(qw * 32) << 16;
         const float c2 = scale * 1.4426950408889634f;      // scores in units of log2(e)
-        float m_run = -INFINITY, l_run = 0.0f;
-        float o[DECODE ? 1 : HD];
-        if (!DECODE) {
-#pragma unroll
-            for (int i = 0; i < HD; i++)
-                o[i] = 0.0f;
-        }
         bool ok = true;
         for (int it = 0; it < n_chunks; it++) {
             int c = c_first + it;
@@ -255,7 +229,7 @@ attn_tc_rows_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             ok = ok && mbar_wait(bar(5), it & 1, abort, err, 7);
             ok = __all_sync(0xffffffffu, ok);
             tc_fence_after();
-            float m_new = m_run, l_chunk = 0.0f, alpha = 1.0f;
+            float m_new = -INFINITY, l_chunk = 0.0f;   // every chunk is a partial of its own
             if (ok && warp_live) {
                 // first pass: the largest visible score of the chunk
                 float mx = -INFINITY;
@@ -270,10 +244,7 @@ attn_tc_rows_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                             mx = fmaxf(mx, sc[i] * c2);
                     }
                 }
-                m_new = DECODE ? mx : fmaxf(m_run, mx);
-                alpha = (m_run == -INFINITY || DECODE) ? 0.0f : exp2f(m_run - m_new);
-                if (m_new == -INFINITY)
-                    alpha = 1.0f;
+                m_new = mx;
                 // second pass: the weights, their sum, and P in bfloat16
 #pragma unroll 1
                 for (int cb = 0; cb < AT_KEYS / 32; cb++) {
@@ -313,64 +284,34 @@ attn_tc_rows_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             fence_async_smem();
             tc_fence_before();
             mbar_arrive(bar(6));
-            if (!DECODE) {
-                l_run = l_run * alpha + l_chunk;
-                m_run = m_new;
-            }
             ok = ok && mbar_wait(bar(7), it & 1, abort, err, 8);
             ok = __all_sync(0xffffffffu, ok);
             tc_fence_after();
             if (ok && warp_live) {
-                if (DECODE) {
-                    float *dst = nullptr;
-                    if (live) {
-                        size_t at = (((size_t)lrow * nh + kvh * G + g) * max_chunks + (c - c_base)) *
-                                    (size_t)(HD + 2);
-                        dst = part + at;
-                        // the merge works with exp(): natural-log units
-                        dst[0] = m_new * 0.6931471805599453f;
-                        dst[1] = l_chunk;
-                    }
+                float *dst = nullptr;
+                if (live) {
+                    size_t at = (((size_t)lrow * nh + kvh * G + g) * max_chunks + (c - c_base)) *
+                                (size_t)(HD + 2);
+                    dst = part + at;
+                    // the merge works with exp(): natural-log units
+                    dst[0] = m_new * 0.6931471805599453f;
+                    dst[1] = l_chunk;
+                }
 #pragma unroll 1
-                    for (int db = 0; db < HD / 32; db++) {
-                        float pv[32];
-                        tc_ld32(tmem_pv + lane_addr + db * 32, pv);
-                        if (live) {
+                for (int db = 0; db < HD / 32; db++) {
+                    float pv[32];
+                    tc_ld32(tmem_pv + lane_addr + db * 32, pv);
+                    if (live) {
 #pragma unroll
-                            // a partial is hd + 2 floats long: 8-byte aligned, not 16
-                            for (int i = 0; i < 32; i += 2)
-                                *reinterpret_cast<float2 *>(dst + 2 + db * 32 + i) =
-                                    make_float2(pv[i], pv[i + 1]);
-                        }
-                    }
-                } else {
-#pragma unroll
-                    for (int db = 0; db < HD / 32; db++) {
-                        float pv[32];
-                        tc_ld32(tmem_pv + lane_addr + db * 32, pv);
-#pragma unroll
-                        for (int i = 0; i < 32; i++)
-                            o[db * 32 + i] = o[db * 32 + i] * alpha + pv[i];
+                        // a partial is hd + 2 floats long: 8-byte aligned, not 16
+                        for (int i = 0; i < 32; i += 2)
+                            *reinterpret_cast<float2 *>(dst + 2 + db * 32 + i) =
+                                make_float2(pv[i], pv[i + 1]);
                     }
                 }
             }
             tc_fence_before();
             mbar_arrive(bar(8));
-        }
-        if (!DECODE && ok && live) {
-            float inv = 1.0f / l_run;
-            bf16 *dst = out + ((size_t)(q_row + j) * nh + kvh * G + g) * HD;
-#pragma unroll
-            for (int i = 0; i < HD; i += 8) {
-                uint32_t w[4];
-#pragma unroll
-                for (int e = 0; e < 4; e++) {
-                    __nv_bfloat162 pk =
-                        __floats2bfloat162_rn(o[i + 2 * e] * inv, o[i + 2 * e + 1] * inv);
-                    w[e] = *reinterpret_cast<uint32_t *>(&pk);
-                }
-                *reinterpret_cast<uint4 *>(dst + i) = make_uint4(w[0], w[1], w[2], w[3]);
-            }
         }
     }
 
@@ -1126,11 +1067,10 @@ static bool attn_tensor_map(const void *ptr, long long d0, long long d1, long lo
 
 template <int HD>
 static int launch_attn_rows(const void *q, const void *k_cache, const void *v_cache,
-                          long long n_pages, const int32_t *qblk, int n_blocks,
-                          const int32_t *row_pos, const int32_t *row_seq,
-                          const int32_t *block_table, int bt_stride, void *out, float *part, int n,
-                          int nh, int nkv, int R, int window, float scale, int max_chunks,
-                          int chunks_per_cta, int row0, int n_rows, cudaStream_t st)
+                            long long n_pages, const int32_t *row_pos, const int32_t *row_seq,
+                            const int32_t *block_table, int bt_stride, float *part, int n, int nh,
+                            int nkv, int window, float scale, int max_chunks, int chunks_per_cta,
+                            int row0, int n_rows, cudaStream_t st)
 {
     using Cfg = AttnCfg<HD>;
     int G = nh / nkv;
@@ -1150,9 +1090,9 @@ static int launch_attn_rows(const void *q, const void *k_cache, const void *v_ca
     unsigned gx = (unsigned)n_rows * ((max_chunks + chunks_per_cta - 1) / chunks_per_cta);
     if (gx == 0)
         return JB_OK;
-    launch(kern, dim3(gx, nkv), 192, Cfg::SMEM_BYTES, st, mq, mk, mv, qblk, row_pos, row_seq,
-           block_table, bt_stride, (bf16 *)out, part, nh, nkv, G, R, window, scale, max_chunks,
-           chunks_per_cta, row0);
+    launch(kern, dim3(gx, nkv), 192, Cfg::SMEM_BYTES, st, mq, mk, mv, row_pos, row_seq,
+           block_table, bt_stride, part, nh, nkv, G, window, scale, max_chunks, chunks_per_cta,
+           row0);
     return launch_status();
 }
 
@@ -1263,13 +1203,12 @@ extern "C" int jb_attn_tc_decode(const void *q, const void *k_cache, const void 
         return launch_status();
     }
     if (hd == 128)
-        return launch_attn_rows<128>(q, k_cache, v_cache, n_pages, nullptr, 0, row_pos, row_seq,
-                                         block_table, bt_stride, nullptr, part, n, nh, nkv, 0,
-                                         window, scale, max_chunks, chunks_per_cta, row0, n_rows,
-                                         st);
-    return launch_attn_rows<64>(q, k_cache, v_cache, n_pages, nullptr, 0, row_pos, row_seq,
-                                    block_table, bt_stride, nullptr, part, n, nh, nkv, 0, window,
-                                    scale, max_chunks, chunks_per_cta, row0, n_rows, st);
+        return launch_attn_rows<128>(q, k_cache, v_cache, n_pages, row_pos, row_seq, block_table,
+                                     bt_stride, part, n, nh, nkv, window, scale, max_chunks,
+                                     chunks_per_cta, row0, n_rows, st);
+    return launch_attn_rows<64>(q, k_cache, v_cache, n_pages, row_pos, row_seq, block_table,
+                                bt_stride, part, n, nh, nkv, window, scale, max_chunks,
+                                chunks_per_cta, row0, n_rows, st);
 }
 
 // Whether the decode kernel for these sizes runs over several chunks per CTA and
