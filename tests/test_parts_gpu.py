@@ -152,6 +152,74 @@ def test_attention_part(window, qk_norm, rope):
     assert (got - want).abs().max() <= 5e-6 * want.abs().max()
 
 
+def test_a_toy_position_encoding_is_registered_and_used_by_the_attention_part():
+    """Another position encoding, defined here: angles that grow linearly with the
+    pair's index (no powers of a base), given to the attention mixer by name.
+    Nothing in the framework knows it."""
+    from janas_b200.cache import Cache
+    from janas_b200.config import PartSpec
+    from janas_b200.parts import LayerCache, PositionEncoding, register_position_encoding
+
+    @register_position_encoding("toy_linear_angles")
+    class LinearAngles(PositionEncoding):
+        def __init__(self, spec, dtype, device):
+            super().__init__(spec, dtype, device)
+            self.rotary_dim = int(spec.params["rotary_dim"])
+            self.step = float(spec.params["step"])
+            self.cos = self.sin = None
+
+        def table(self, n):
+            half = self.rotary_dim // 2
+            ang = (torch.arange(n, dtype=torch.float64)[:, None] * self.step *
+                   torch.arange(1, half + 1, dtype=torch.float64)[None, :])
+            return torch.cos(ang).float(), torch.sin(ang).float()
+
+        def prepare(self, n_positions):
+            if self.cos is None or self.cos.shape[0] < n_positions:
+                c, s = self.table(n_positions)
+                self.cos, self.sin = c.to(self.device), s.to(self.device)
+
+        @property
+        def n_positions(self):
+            return 0 if self.cos is None else self.cos.shape[0]
+
+    nh, nkv, hd, dm, n = 4, 2, 64, 40, 75
+    pos = PartSpec("toy_linear_angles", {"rotary_dim": hd, "step": 0.013})
+    att = build("mixer", PartSpec("gqa_attention", {
+        "hidden_size": dm, "num_heads": nh, "num_kv_heads": nkv, "head_dim": hd,
+        "qk_norm_eps": 1e-6, "window": 0, "position": pos}))
+    w = give(att, "attn", seed=11)
+    att.prepare(128)
+    cache = Cache([att.kv_spec()], [None], 128, 1, torch.float32, DEV)
+    s = cache.new_sequence()
+    g = cache.groups[0]
+    x = torch.randn(n, dm)
+
+    def run(p0, cnt):
+        cache.reserve([s], [cnt])
+        bt = torch.from_numpy(cache.block_table(g, [s])).to(DEV)
+        lc = LayerCache(k=g.k[0], v=g.v[0], block_table=bt)
+        out = att.forward(context([p0], [cnt]), x[p0:p0 + cnt].contiguous().to(DEV), lc)
+        cache.advance([s], [cnt])
+        return out.sum(0).cpu()
+
+    got = torch.cat([run(0, 60)] + [run(p, 1) for p in range(60, n)])
+    q = plain.rms_norm((x @ w["attn.q_proj.weight"].T).view(n, nh, hd), w["attn.q_norm.weight"], 1e-6)
+    k = plain.rms_norm((x @ w["attn.k_proj.weight"].T).view(n, nkv, hd), w["attn.k_norm.weight"], 1e-6)
+    v = (x @ w["attn.v_proj.weight"].T).view(n, nkv, hd)
+    cs, sn = att.position.table(n)
+    q, k = plain.rope_neox(q, cs, sn), plain.rope_neox(k, cs, sn)
+    want = plain.attention(q, k, v, 0).reshape(n, nh * hd) @ w["attn.o_proj.weight"].T
+    assert (got - want).abs().max() <= 5e-6 * want.abs().max()
+    # and it does turn the heads: without it the answer is another
+    bare = plain.attention(plain.rms_norm((x @ w["attn.q_proj.weight"].T).view(n, nh, hd),
+                                          w["attn.q_norm.weight"], 1e-6),
+                           plain.rms_norm((x @ w["attn.k_proj.weight"].T).view(n, nkv, hd),
+                                          w["attn.k_norm.weight"], 1e-6), v, 0)
+    bare = bare.reshape(n, nh * hd) @ w["attn.o_proj.weight"].T
+    assert (bare - want).abs().max() > 1e-3 * want.abs().max()
+
+
 # ------------------------------------------------------------------ toy parts
 def register_toys():
     """A mixer whose output is the running mean of its inputs (its state: the
