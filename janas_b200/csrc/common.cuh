@@ -185,6 +185,19 @@ __device__ __forceinline__ float cluster_read(const float *mine, uint32_t rank)
     return v;
 }
 
+// SMs of the current device (148 on a B200), asked once.
+inline int sm_count()
+{
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0, n = 0;
+        cudaGetDevice(&dev);
+        sms = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess &&
+                      n > 0 ? n : 148;
+    }
+    return sms;
+}
+
 inline int launch_status()
 {
     return cudaGetLastError() == cudaSuccess ? JB_OK : JB_ELAUNCH;

@@ -408,14 +408,14 @@ extern "C" int jb_gemm_tc_ok(const void *A, const void *W, int n, int m, int k)
 // tokens the product is a stream of weights, and what one CTA pulls is limited
 // by the loads it can keep in flight: measured on B200, the products of a
 // decode step run fastest when their CTAs (feature tiles x parts of k) just
-// fill the SMs' 2 x 148 places for this kernel at once, as long as a part
+// fill the SMs' places for this kernel (two a SM) at once, as long as a part
 // keeps at least four 64-wide blocks of k.  More CTAs than places come in waves
 // whose last one straggles, so a product with more tiles than that is not cut.
 extern "C" int jb_gemm_tc_splits(int n, int m, int k)
 {
     if (n > 128)
         return 1;
-    const int PLACES = 2 * 148;
+    const int PLACES = 2 * sm_count();
     int bn = n <= 16 ? 16 : n <= 32 ? 32 : n <= 64 ? 64 : 128;
     long tiles = (long)((m + TILE_M - 1) / TILE_M) * ((n + bn - 1) / bn);
     int total_kb = (k + BK - 1) / BK;
@@ -439,14 +439,7 @@ extern "C" int jb_gemm_tc_splits(int n, int m, int k)
 // is why narrower tiles are not proportionally faster.
 static int many_tokens_tile(int n, int m, int k)
 {
-    static int sms = 0;
-    if (sms == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
-            sms <= 0)
-            sms = 148;
-    }
+    int sms = sm_count();
     const int choices[5] = {256, 224, 192, 160, 128};
     int kb = (k + BK - 1) / BK;
     long m_tiles = (m + 2 * TILE_M - 1) / (2 * TILE_M);

@@ -290,7 +290,7 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
     if tc:
         # CTAs per (token, KV head): each runs over per_cta chunks and leaves one partial
         if L.jb_attn_tc_decode_runs(nh, nkv, hd):
-            parts = _decode_parts(min(n, 4096) * nkv, max_chunks)
+            parts = _decode_parts(min(n, 4096) * nkv, max_chunks, 2 * _sm_count(q.device))
         else:
             parts = max_chunks
         per_cta = (max_chunks + parts - 1) // parts
@@ -320,10 +320,21 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
     return out
 
 
-def _decode_parts(pairs: int, chunks: int, sms: int = 296) -> int:
+_SM_COUNT = {}
+
+
+def _sm_count(device: torch.device) -> int:
+    key = torch.device(device).index or 0
+    if key not in _SM_COUNT:
+        _SM_COUNT[key] = torch.cuda.get_device_properties(key).multi_processor_count
+    return _SM_COUNT[key]
+
+
+def _decode_parts(pairs: int, chunks: int, places: int) -> int:
     """Into how many CTAs the chunks of one (token, KV head) pair are cut.  A CTA
-    costs about three chunks' time to set up, and CTAs beyond two per SM come in
-    waves: the cut that finishes first by that estimate."""
+    costs about three chunks' time to set up, and CTAs beyond the device's places
+    (two per SM) come in waves: the cut that finishes first by that estimate."""
+    sms = places
     best, best_t = 1, None
     for parts in range(1, chunks + 1):
         per_cta = -(-chunks // parts)

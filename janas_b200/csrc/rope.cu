@@ -298,7 +298,7 @@ extern "C" int jb_qk_norm_rope_append(const float *qkv, int S, long long split_s
         size_t tasks = (size_t)n * ((slots + per_warp - 1) / per_warp);
         if (tasks > 0xffffffffu)
             return JB_EINVAL;
-        unsigned grid = (unsigned)std::min<size_t>((tasks + 3) / 4, 148 * 16);
+        unsigned grid = (unsigned)std::min<size_t>((tasks + 3) / 4, (size_t)sm_count() * 16);
 #define JB_ROPE_V(TC, TW, L)                                                                   \
     launch(qk_norm_rope_append_vec_kernel<TC, TW, L>, grid, block, 0, st,                      \
         qkv, S, (size_t)split_stride, (const TW *)q_w, (const TW *)k_w, eps, cs, sn, rot_half, \
