@@ -25,6 +25,7 @@
 //
 // The reference has no counterpart: its products are quantized dot products on
 // CPU threads or dp4a (src/llm/cuda/matvec.cu:344-414).
+#include <algorithm>
 #include <map>
 #include <mutex>
 #include <tuple>
@@ -78,6 +79,113 @@ template <int BN, int MT> struct TileCfg {
     static constexpr int TMEM_COLS = MT * BN <= 32 ? 32 : MT * BN <= 64 ? 64 : MT * BN <= 128 ? 128 : MT * BN <= 256 ? 256 : 512;
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment */ + 256 /* barriers */;
 };
+
+// The epilogues.  A thread owns one feature (a TMEM lane) and, with the other
+// warp of its quarter, takes the groups of 32 token columns in turn (hgrp, hgrp
+// + 2, ...); the read of the next group is in flight while the last one is stored.
+//
+// Float partial sums: tile t's tokens are columns [t BN, t BN + BN).
+template <int BN, int MT>
+__device__ __forceinline__ void store_partial(uint32_t taddr, int hgrp, float *__restrict__ dst,
+                                              int f, int n0, int n, int m, int second_off)
+{
+    constexpr int COLS = MT * BN;
+    if constexpr (BN < 32) {
+        float v[16];
+        if (hgrp != 0)
+            return;
+        tc_ld16(taddr, v);
+        if (f < m) {
+#pragma unroll
+            for (int j = 0; j < 16; j++)
+                if (n0 + j < n)
+                    dst[(size_t)(n0 + j) * m + f] = v[j];
+        }
+    } else {
+        uint32_t va[32], vb[32];
+        auto store32 = [&](const uint32_t *v, int c) {
+            int t = c / BN, c0 = c - t * BN;
+            int ft = f + t * second_off;
+            if (ft >= m)
+                return;
+            float *p = dst + (size_t)(n0 + c0) * m + ft;
+            if (n0 + c0 + 32 <= n) {        // the usual case: no token is cut off
+#pragma unroll
+                for (int j = 0; j < 32; j++, p += m)
+                    *p = __uint_as_float(v[j]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; j++, p += m)
+                    if (n0 + c0 + j < n)
+                        *p = __uint_as_float(v[j]);
+            }
+        };
+        int c = 32 * hgrp;
+        if (c < COLS) {
+            tc_ld32_nowait(taddr + c, va);
+#pragma unroll 1
+            for (; c < COLS; c += 128) {
+                tc_ld_wait();
+                if (c + 64 < COLS)
+                    tc_ld32_nowait(taddr + c + 64, vb);
+                store32(va, c);
+                if (c + 64 < COLS) {
+                    tc_ld_wait();
+                    if (c + 128 < COLS)
+                        tc_ld32_nowait(taddr + c + 128, va);
+                    store32(vb, c + 64);
+                }
+            }
+        }
+    }
+}
+
+// SiLU(gate) * up in bfloat16: the gate's tokens are columns [0, BN), the up
+// projection's [BN, 2 BN).  SiLU(g) u = g u / (1 + 2^(-g log2 e)), with the
+// approximate exponential and reciprocal (a few units in the last place of a
+// float; the result is rounded to bfloat16).
+template <int BN>
+__device__ __forceinline__ void store_swiglu(uint32_t taddr, int hgrp, bf16 *__restrict__ out_act,
+                                             int f, int ff, int n0, int n)
+{
+    uint32_t ga[32], ua[32], gb[32], ub[32];
+    auto act32 = [&](const uint32_t *g, const uint32_t *u, int c0) {
+        if (f >= ff)
+            return;
+        bf16 *p = out_act + (size_t)(n0 + c0) * ff + f;
+        bool whole = n0 + c0 + 32 <= n;
+#pragma unroll
+        for (int j = 0; j < 32; j++, p += ff) {
+            if (whole || n0 + c0 + j < n) {
+                float gv = __uint_as_float(g[j]), uv = __uint_as_float(u[j]);
+                float e = fast_exp2(gv * -1.4426950408889634f);
+                *p = __float2bfloat16_rn(__fdividef(gv * uv, 1.0f + e));
+            }
+        }
+    };
+    int c = 32 * hgrp;
+    if (c < BN) {
+        tc_ld32_nowait(taddr + c, ga);
+        tc_ld32_nowait(taddr + BN + c, ua);
+#pragma unroll 1
+        for (; c < BN; c += 128) {
+            tc_ld_wait();
+            if (c + 64 < BN) {
+                tc_ld32_nowait(taddr + c + 64, gb);
+                tc_ld32_nowait(taddr + BN + c + 64, ub);
+            }
+            act32(ga, ua, c);
+            if (c + 64 < BN) {
+                tc_ld_wait();
+                if (c + 128 < BN) {
+                    tc_ld32_nowait(taddr + c + 128, ga);
+                    tc_ld32_nowait(taddr + BN + c + 128, ua);
+                }
+                act32(gb, ub, c + 64);
+            }
+        }
+    }
+}
 
 template <int BN, int MT, int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS)
@@ -209,100 +317,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         // The accumulator is read 32 columns (tokens) at a time; the read of the
         // next 32 is in flight while the last 32 are stored.
         int hgrp = (warp - 2) >> 2;             // which of the two warps of this quarter
-        if (EPI == EPI_PARTIAL) {
-            float *dst = out + (size_t)blockIdx.z * n * m;
-            constexpr int COLS = MT * BN;           // tile t's tokens are columns [t BN, t BN + BN)
-            if constexpr (BN < 32) {
-                float v[16];
-                if (ok && hgrp == 0)
-                    tc_ld16(taddr, v);
-                if (ok && hgrp == 0 && f < m) {
-#pragma unroll
-                    for (int j = 0; j < 16; j++)
-                        if (n0 + j < n)
-                            dst[(size_t)(n0 + j) * m + f] = v[j];
-                }
-            } else {
-                uint32_t va[32], vb[32];
-                auto store32 = [&](const uint32_t *v, int c) {
-                    int t = c / BN, c0 = c - t * BN;
-                    int ft = f + t * second_off;
-                    if (ft >= m)
-                        return;
-                    float *p = dst + (size_t)(n0 + c0) * m + ft;
-                    if (n0 + c0 + 32 <= n) {        // the usual case: no token is cut off
-#pragma unroll
-                        for (int j = 0; j < 32; j++, p += m)
-                            *p = __uint_as_float(v[j]);
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; j++, p += m)
-                            if (n0 + c0 + j < n)
-                                *p = __uint_as_float(v[j]);
-                    }
-                };
-                // this warp's groups of 32 columns: hgrp, hgrp + 2, ...; the read of the
-                // next group is in flight while the last one is stored
-                int c = 32 * hgrp;
-                if (ok && c < COLS) {
-                    tc_ld32_nowait(taddr + c, va);
-#pragma unroll 1
-                    for (; c < COLS; c += 128) {
-                        tc_ld_wait();
-                        if (c + 64 < COLS)
-                            tc_ld32_nowait(taddr + c + 64, vb);
-                        store32(va, c);
-                        if (c + 64 < COLS) {
-                            tc_ld_wait();
-                            if (c + 128 < COLS)
-                                tc_ld32_nowait(taddr + c + 128, va);
-                            store32(vb, c + 64);
-                        }
-                    }
-                }
-            }
-        } else {
-            int ff = second_off;
-            uint32_t ga[32], ua[32], gb[32], ub[32];
-            // SiLU(g) u = g u / (1 + 2^(-g log2 e)), with the approximate exponential
-            // and reciprocal (a few units in the last place of a float; the result is
-            // rounded to bfloat16)
-            auto act32 = [&](const uint32_t *g, const uint32_t *u, int c0) {
-                if (f >= ff)
-                    return;
-                bf16 *p = out_act + (size_t)(n0 + c0) * ff + f;
-                bool whole = n0 + c0 + 32 <= n;
-#pragma unroll
-                for (int j = 0; j < 32; j++, p += ff) {
-                    if (whole || n0 + c0 + j < n) {
-                        float gv = __uint_as_float(g[j]), uv = __uint_as_float(u[j]);
-                        float e = fast_exp2(gv * -1.4426950408889634f);
-                        *p = __float2bfloat16_rn(__fdividef(gv * uv, 1.0f + e));
-                    }
-                }
-            };
-            int c = 32 * hgrp;
-            if (ok && c < BN) {
-                tc_ld32_nowait(taddr + c, ga);
-                tc_ld32_nowait(taddr + BN + c, ua);
-#pragma unroll 1
-                for (; c < BN; c += 128) {
-                    tc_ld_wait();
-                    if (c + 64 < BN) {
-                        tc_ld32_nowait(taddr + c + 64, gb);
-                        tc_ld32_nowait(taddr + BN + c + 64, ub);
-                    }
-                    act32(ga, ua, c);
-                    if (c + 64 < BN) {
-                        tc_ld_wait();
-                        if (c + 128 < BN) {
-                            tc_ld32_nowait(taddr + c + 128, ga);
-                            tc_ld32_nowait(taddr + BN + c + 128, ua);
-                        }
-                        act32(gb, ub, c + 64);
-                    }
-                }
-            }
+        if (ok) {
+            if (EPI == EPI_PARTIAL)
+                store_partial<BN, MT>(taddr, hgrp, out + (size_t)blockIdx.z * n * m, f, n0, n, m,
+                                      second_off);
+            else
+                store_swiglu<BN>(taddr, hgrp, out_act, f, second_off, n0, n);
         }
     }
 
