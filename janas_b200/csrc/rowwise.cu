@@ -229,6 +229,54 @@ rmsnorm_cluster_kernel(float *__restrict__ x, const float *__restrict__ delta, i
     cluster_wait();                    // nobody leaves while its share may still be read
 }
 
+// The same for a middling number of rows, bfloat16 output: a block per row, four
+// consecutive values per thread (dm <= 4096, a multiple of 4), and everything a
+// thread adds fetched together, eight partial sums at a time.  Like the two
+// kernels above it serves the bfloat16 path only.
+template <typename TW>
+__global__ void __launch_bounds__(1024)
+rmsnorm_vec_kernel(float *__restrict__ x, const float *__restrict__ delta, int S,
+                   size_t delta_stride, const int32_t *__restrict__ row_idx,
+                   const TW *__restrict__ w, bf16 *__restrict__ out, int dm, float eps)
+{
+    __shared__ float red[32];
+    pdl_trigger();
+    int c = 4 * threadIdx.x;
+    bool mine = c < dm;
+    float4 wv = mine ? load4(w + c) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    pdl_wait();
+    size_t orow = blockIdx.x;
+    size_t row = row_idx ? (size_t)row_idx[orow] : orow;
+    float *xr = x + row * dm;
+    float4 v = mine ? load4(xr + c) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (delta && mine) {
+        const float *d = delta + row * dm + c;
+        for (int s0 = 0; s0 < S; s0 += 8) {
+            float4 t[8];
+#pragma unroll
+            for (int b = 0; b < 8; b++)
+                if (s0 + b < S)
+                    t[b] = load4(d + (size_t)(s0 + b) * delta_stride);
+#pragma unroll
+            for (int b = 0; b < 8; b++)
+                if (s0 + b < S) {
+                    v.x += t[b].x; v.y += t[b].y; v.z += t[b].z; v.w += t[b].w;
+                }
+        }
+        store4(xr + c, v);
+    }
+    float ss = v.x * v.x;
+    ss = fmaf(v.y, v.y, ss);
+    ss = fmaf(v.z, v.z, ss);
+    ss = fmaf(v.w, v.w, ss);
+    ss = block_sum(ss, red);
+    if (!mine)
+        return;
+    float scale = 1.0f / sqrtf(ss / (float)dm + eps);
+    store4(out + orow * dm + c, make_float4((v.x * scale) * wv.x, (v.y * scale) * wv.y,
+                                            (v.z * scale) * wv.z, (v.w * scale) * wv.w));
+}
+
 // gu: S stacked [n, 2 ff] float partial sums; columns [0, ff) are the gate,
 // [ff, 2 ff) the up projection.  out[n, ff] = SiLU(gate) * up.  VEC values per
 // thread (4 when ff is a multiple of 4 and nothing is split, else 1).
@@ -339,6 +387,20 @@ extern "C" int jb_rmsnorm(float *x, const float *delta, int S, long long delta_s
             JB_NORM_CK(bf16);
 #undef JB_NORM_C
 #undef JB_NORM_CK
+        return launch_status();
+    }
+    // a middling number of rows of the bfloat16 path: four values per thread
+    if (out != nullptr && out_dt == JB_BF16 && n_out > 32 && dm % 4 == 0 && dm <= 4096 &&
+        (w_dt == JB_F32 || w_dt == JB_BF16) && (uintptr_t)x % 16 == 0 &&
+        (uintptr_t)delta % 16 == 0 && (uintptr_t)out % 8 == 0 &&
+        (uintptr_t)w % (w_dt == JB_F32 ? 16 : 8) == 0 && (delta == nullptr || delta_stride % 4 == 0)) {
+        unsigned threads = (unsigned)((dm / 4 + 31) / 32 * 32);
+        if (w_dt == JB_F32)
+            launch(rmsnorm_vec_kernel<float>, n_out, threads, 0, st, x, delta, S,
+                   (size_t)delta_stride, row_idx, (const float *)w, (bf16 *)out, dm, eps);
+        else
+            launch(rmsnorm_vec_kernel<bf16>, n_out, threads, 0, st, x, delta, S,
+                   (size_t)delta_stride, row_idx, (const bf16 *)w, (bf16 *)out, dm, eps);
         return launch_status();
     }
     int threads = norm_threads(dm);

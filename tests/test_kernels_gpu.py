@@ -60,10 +60,12 @@ def test_rmsnorm(wdt, odt, n, dm):
 
 @pytest.mark.parametrize("wdt", DTYPES)
 @pytest.mark.parametrize("n,dm,S", [(1, 1024, 1), (8, 2560, 14), (3, 1027, 17), (5, 9000, 2),
-                                    (2, 17000, 3)])
+                                    (2, 17000, 3), (64, 2560, 14), (40, 100, 9), (33, 4096, 1),
+                                    (200, 1000, 20)])
 def test_rmsnorm_few_rows(wdt, n, dm, S):
-    """Few rows with bfloat16 output: a row shared out among the CTAs of a cluster.
-    One value of each row is large, so that a CTA's missing share would show."""
+    """Few rows with bfloat16 output (a row shared out among the CTAs of a cluster)
+    and a middling number (a block per row, four values per thread).  One value of
+    each row is large, so that a missing share would show."""
     x = rnd(n, dm, scale=3.0)
     x[:, dm - 3] = 200.0
     w = (1 + 0.1 * rnd(dm)).to(wdt)
