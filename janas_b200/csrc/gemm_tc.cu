@@ -431,10 +431,12 @@ extern "C" int jb_gemm_tc_ok(const void *A, const void *W, int n, int m, int k)
 // fill the SMs' places for this kernel (two a SM) at once, as long as a part
 // keeps at least four 64-wide blocks of k.  More CTAs than places come in waves
 // whose last one straggles, so a product with more tiles than that is not cut.
+static int many_tokens_splits(int n, int m, int k);
+
 extern "C" int jb_gemm_tc_splits(int n, int m, int k)
 {
     if (n > 128)
-        return 1;
+        return many_tokens_splits(n, m, k);
     const int PLACES = 2 * sm_count();
     int bn = n <= 16 ? 16 : n <= 32 ? 32 : n <= 64 ? 64 : 128;
     long tiles = (long)((m + TILE_M - 1) / TILE_M) * ((n + bn - 1) / bn);
@@ -452,28 +454,55 @@ extern "C" int jb_gemm_tc_splits(int n, int m, int k)
 }
 
 // Tokens per tile (256 features x this many tokens) for a product over many
-// tokens.  One CTA fits an SM, so tiles run in rounds of as many as there are
-// SMs; a narrower tile can turn a mostly empty last round into none.  A tile's
-// time is a fixed part plus, per 64-wide block of k, the larger of its MMA time
-// and the time to bring its operands in (measured: about 116 GB/s per SM), which
-// is why narrower tiles are not proportionally faster.
-static int many_tokens_tile(int n, int m, int k)
+// tokens whose k is cut into `splits` parts, and the estimate of its time in
+// microseconds.  One CTA fits an SM, so tiles run in rounds of as many as there
+// are SMs; a narrower tile can turn a mostly empty last round into none.  A
+// tile's time is a fixed part plus, per 64-wide block of k, the larger of its MMA
+// time and the time to bring its operands in (measured: about 116 GB/s per SM),
+// which is why narrower tiles are not proportionally faster.  Every part beyond
+// the first also costs the writing and the reading back of a float partial sum.
+static int many_tokens_tile(int n, int m, int k, int splits, double *time_us = nullptr)
 {
     int sms = sm_count();
     const int choices[5] = {256, 224, 192, 160, 128};
     int kb = (k + BK - 1) / BK;
+    int kbps = (kb + splits - 1) / splits;
     long m_tiles = (m + 2 * TILE_M - 1) / (2 * TILE_M);
     int best = 256;
     double best_t = 1e30;
     for (int c = 0; c < 5; c++) {
         int bn = choices[c];
-        long tiles = m_tiles * ((n + bn - 1) / bn);
+        long tiles = m_tiles * ((n + bn - 1) / bn) * splits;
         long rounds = (tiles + sms - 1) / sms;
         double mma = 0.55 * bn / 256.0, load = (32768.0 + bn * 128.0) / 116000.0;
-        double t = rounds * (8.0 + kb * (mma > load ? mma : load));
+        double t = rounds * (8.0 + kbps * (mma > load ? mma : load)) +
+                   (splits - 1) * (double)n * m * 8.0 / 5e6;
         if (t < best_t * 0.98) {
             best_t = t;
             best = bn;
+        }
+    }
+    if (time_us)
+        *time_us = best_t;
+    return best;
+}
+
+// Parts of k for a product over many tokens: more than one only where the tiles
+// alone leave most SMs idle (a few hundred tokens times a narrow weight matrix).
+static int many_tokens_splits(int n, int m, int k)
+{
+    int kb = (k + BK - 1) / BK;
+    int best = 1;
+    double best_t = 1e30;
+    for (int s = 1; s <= 8; s++) {
+        int kbps = (kb + s - 1) / s;
+        if (s > 1 && (kbps < 8 || (s - 1) * kbps >= kb))
+            continue;
+        double t;
+        many_tokens_tile(n, m, k, s, &t);
+        if (t < best_t * 0.95) {
+            best_t = t;
+            best = s;
         }
     }
     return best;
@@ -486,15 +515,15 @@ extern "C" int jb_gemm_tc(const void *A, const void *W, float *out, int n, int m
     if (!jb_gemm_tc_ok(A, W, n, m, k) || splits < 1)
         return JB_EINVAL;
     if (n > 128) {
-        if (splits != 1)
-            return JB_EINVAL;
-        switch (many_tokens_tile(n, m, k)) {
-        case 128: return launch_tc<128, 2, EPI_PARTIAL>(A, W, out, nullptr, n, m, k, m, TILE_M, 1, st);
-        case 160: return launch_tc<160, 2, EPI_PARTIAL>(A, W, out, nullptr, n, m, k, m, TILE_M, 1, st);
-        case 192: return launch_tc<192, 2, EPI_PARTIAL>(A, W, out, nullptr, n, m, k, m, TILE_M, 1, st);
-        case 224: return launch_tc<224, 2, EPI_PARTIAL>(A, W, out, nullptr, n, m, k, m, TILE_M, 1, st);
-        default: return launch_tc<256, 2, EPI_PARTIAL>(A, W, out, nullptr, n, m, k, m, TILE_M, 1, st);
+#define JB_MANY(B) launch_tc<B, 2, EPI_PARTIAL>(A, W, out, nullptr, n, m, k, m, TILE_M, splits, st)
+        switch (many_tokens_tile(n, m, k, splits)) {
+        case 128: return JB_MANY(128);
+        case 160: return JB_MANY(160);
+        case 192: return JB_MANY(192);
+        case 224: return JB_MANY(224);
+        default: return JB_MANY(256);
         }
+#undef JB_MANY
     }
     if (n <= 16)
         return launch_tc<16, 1, EPI_PARTIAL>(A, W, out, nullptr, n, m, k, m, TILE_M, splits, st);
@@ -515,7 +544,7 @@ extern "C" int jb_gemm_tc_swiglu(const void *A, const void *W, void *out_act, in
     if (n > 128) {
 #define JB_SWIGLU(B)                                                                           \
     launch_tc<B, 2, EPI_SWIGLU>(A, W, nullptr, (bf16 *)out_act, n, 2 * ff, k, 2 * ff, ff, 1, st)
-        switch (many_tokens_tile(n, 2 * ff, k)) {
+        switch (many_tokens_tile(n, 2 * ff, k, 1)) {
         case 128: return JB_SWIGLU(128);
         case 160: return JB_SWIGLU(160);
         case 192: return JB_SWIGLU(192);

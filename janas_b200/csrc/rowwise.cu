@@ -122,14 +122,17 @@ rmsnorm_rows_kernel(float *__restrict__ x, const float *__restrict__ delta, int 
         float4 v = xr[i];
         if (delta) {
             const float *d = delta + row * dm + 4 * i;
-            if (S == 1) {
-                float4 a = *reinterpret_cast<const float4 *>(d);
-                v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
-            } else {
-                v.x = add_partials(v.x, d, S, delta_stride);
-                v.y = add_partials(v.y, d + 1, S, delta_stride);
-                v.z = add_partials(v.z, d + 2, S, delta_stride);
-                v.w = add_partials(v.w, d + 3, S, delta_stride);
+            for (int s0 = 0; s0 < S; s0 += 4) {      // four partial sums are fetched together
+                float4 t[4];
+#pragma unroll
+                for (int b = 0; b < 4; b++)
+                    if (s0 + b < S)
+                        t[b] = load4(d + (size_t)(s0 + b) * delta_stride);
+#pragma unroll
+                for (int b = 0; b < 4; b++)
+                    if (s0 + b < S) {
+                        v.x += t[b].x; v.y += t[b].y; v.z += t[b].z; v.w += t[b].w;
+                    }
             }
             xr[i] = v;
         }
