@@ -1080,13 +1080,9 @@ static int launch_attn_rows(const void *q, const void *k_cache, const void *v_ca
         !attn_tensor_map(v_cache, HD, n_pages * nkv * PAGE, 0, PAGE, 0, &mv))
         return JB_EINVAL;
     auto kern = attn_tc_rows_kernel<HD>;
-    static bool attr_set = false;
-    if (!attr_set) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 Cfg::SMEM_BYTES) != cudaSuccess)
-            return JB_ELAUNCH;
-        attr_set = true;
-    }
+    static unsigned long long smem_allowed = 0;
+    if (!allow_dynamic_smem(kern, Cfg::SMEM_BYTES, smem_allowed))
+        return JB_ELAUNCH;
     unsigned gx = (unsigned)n_rows * ((max_chunks + chunks_per_cta - 1) / chunks_per_cta);
     if (gx == 0)
         return JB_OK;
@@ -1137,14 +1133,10 @@ extern "C" int jb_attn_tc_prefill(const void *q, const void *k_cache, const void
         return JB_OK;
 #define JB_PF(HDV)                                                                             \
     do {                                                                                       \
-        static bool attr_set = false;                                                          \
-        if (!attr_set) {                                                                       \
-            if (cudaFuncSetAttribute(attn_tc_prefill_kernel<HDV>,                              \
-                                     cudaFuncAttributeMaxDynamicSharedMemorySize,              \
-                                     PrefillCfg<HDV>::SMEM_BYTES) != cudaSuccess)              \
-                return JB_ELAUNCH;                                                             \
-            attr_set = true;                                                                   \
-        }                                                                                      \
+        static unsigned long long smem_allowed = 0;                                            \
+        if (!allow_dynamic_smem(attn_tc_prefill_kernel<HDV>, PrefillCfg<HDV>::SMEM_BYTES,      \
+                                smem_allowed))                                                 \
+            return JB_ELAUNCH;                                                                 \
         launch(attn_tc_prefill_kernel<HDV>, dim3((unsigned)n_blocks * nkv), PF_THREADS,        \
                PrefillCfg<HDV>::SMEM_BYTES, st, mq, mk, mv, qblk, block_table, bt_stride,      \
                (bf16 *)out, nh, nkv, G, R, window, scale);                                     \
@@ -1177,14 +1169,9 @@ extern "C" int jb_attn_tc_decode(const void *q, const void *k_cache, const void 
         unsigned gx = (unsigned)n_rows * ((max_chunks + chunks_per_cta - 1) / chunks_per_cta);
 #define JB_DQ(GP)                                                                              \
     do {                                                                                       \
-        static bool attr_set = false;                                                          \
-        if (!attr_set) {                                                                       \
-            if (cudaFuncSetAttribute(attn_tc_decode_kernel<GP>,                                \
-                                     cudaFuncAttributeMaxDynamicSharedMemorySize,              \
-                                     DQ_SMEM) != cudaSuccess)                                  \
-                return JB_ELAUNCH;                                                             \
-            attr_set = true;                                                                   \
-        }                                                                                      \
+        static unsigned long long smem_allowed = 0;                                            \
+        if (!allow_dynamic_smem(attn_tc_decode_kernel<GP>, DQ_SMEM, smem_allowed))             \
+            return JB_ELAUNCH;                                                                 \
         launch(attn_tc_decode_kernel<GP>, dim3(gx, nkv), 192, DQ_SMEM, st,                     \
                mq, mk, mv, row_pos, row_seq, block_table, bt_stride, part, nh, nkv, G, window, \
                scale, max_chunks, chunks_per_cta, row0);                                       \

@@ -185,17 +185,37 @@ __device__ __forceinline__ float cluster_read(const float *mine, uint32_t rank)
     return v;
 }
 
-// SMs of the current device (148 on a B200), asked once.
+// SMs of the current device (148 on a B200), asked once per device.
 inline int sm_count()
 {
-    static int sms = 0;
-    if (sms == 0) {
-        int dev = 0, n = 0;
-        cudaGetDevice(&dev);
-        sms = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess &&
-                      n > 0 ? n : 148;
+    static int sms[64] = {0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    int slot = dev >= 0 && dev < 64 ? dev : 0;
+    if (sms[slot] == 0) {
+        int n = 0;
+        sms[slot] = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess &&
+                            n > 0 ? n : 148;
     }
-    return sms;
+    return sms[slot];
+}
+
+// Lets a kernel use `bytes` of dynamic shared memory on the current device; `done`
+// is the caller's record (a bit per device) of where that has been said already.
+template <typename Kernel>
+inline bool allow_dynamic_smem(Kernel kern, int bytes, unsigned long long &done)
+{
+    int dev = 0;
+    cudaGetDevice(&dev);
+    bool tracked = dev >= 0 && dev < 64;
+    if (tracked && (done >> dev & 1))
+        return true;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) !=
+        cudaSuccess)
+        return false;
+    if (tracked)
+        done |= 1ull << dev;
+    return true;
 }
 
 inline int launch_status()

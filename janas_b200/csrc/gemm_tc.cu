@@ -391,13 +391,9 @@ static int launch_tc(const void *A, const void *W, float *out, bf16 *out_act, in
     if (!tensor_map(W, w_rows, k, TILE_M, &map_w) || !tensor_map(A, n, k, BN, &map_a))
         return JB_EINVAL;
     auto kern = gemm_tc_kernel<BN, MT, EPI>;
-    static bool attr_set = false;
-    if (!attr_set) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 Cfg::SMEM_BYTES) != cudaSuccess)
-            return JB_ELAUNCH;
-        attr_set = true;
-    }
+    static unsigned long long smem_allowed = 0;
+    if (!allow_dynamic_smem(kern, Cfg::SMEM_BYTES, smem_allowed))
+        return JB_ELAUNCH;
     int total_kb = (k + BK - 1) / BK;
     int kbps = (total_kb + splits - 1) / splits;
     if ((splits - 1) * kbps >= total_kb)
