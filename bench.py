@@ -1,8 +1,8 @@
 #!/usr/bin/env python3
 """Measures decoding and prefill speed of the engine on one B200.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--batch B]
-                    [--context C] [--dtype bfloat16|float32] [--no-points]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--model 4b|8b|32b] [--layers L]
+                    [--batch B] [--context C] [--dtype bfloat16|float32] [--no-points]
     python bench.py --impl reference ...     (prints why it is unavailable)
     python bench.py --only decode|prefill|timeline ...   (one part, for profiling)
 
@@ -38,6 +38,13 @@ QWEN3_4B = dict(
     intermediate_size=9728, vocab_size=151936, rope_theta=1e6, rms_norm_eps=1e-6,
     tie_word_embeddings=True, max_position_embeddings=8192)
 FULL_LAYERS = QWEN3_4B["num_hidden_layers"]
+# the other sizes of the same architecture, for --model (the default run is the 4B one)
+MODELS = {
+    "4b": QWEN3_4B,
+    "8b": dict(QWEN3_4B, hidden_size=4096, intermediate_size=12288, tie_word_embeddings=False),
+    "32b": dict(QWEN3_4B, num_hidden_layers=64, hidden_size=5120, num_attention_heads=64,
+                intermediate_size=25600, tie_word_embeddings=False, max_position_embeddings=4096),
+}
 
 # used only when MEASURED_PEAKS.json is absent: an earlier measurement on this pool
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
@@ -118,7 +125,7 @@ def build_engine(args, n_layers, max_tokens, max_seqs):
     from janas_b200.config import config_from_dict
     from janas_b200.engine import DecoderModel, Engine
     from janas_b200.weights import random_tensors
-    cfg = config_from_dict(dict(QWEN3_4B, num_hidden_layers=n_layers))
+    cfg = config_from_dict(dict(MODELS[args.model], num_hidden_layers=n_layers))
     dt = torch.bfloat16 if args.dtype == "bfloat16" else torch.float32
     model = DecoderModel(cfg.to_model_spec(), dt, "cuda:0")
     with torch.cuda.device(0):
@@ -223,7 +230,9 @@ def main():
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--layers", type=int, default=FULL_LAYERS)
+    ap.add_argument("--model", default="4b", choices=sorted(MODELS),
+                    help="layer sizes: Qwen3-4B (the default run), 8B or 32B")
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=2048)
     ap.add_argument("--prefill-tokens", type=int, default=2048)
@@ -243,6 +252,9 @@ def main():
     if args.gpus != 1:
         print("bench.py: this engine runs on one GPU; --gpus must be 1")
         return 2
+    full_layers = MODELS[args.model]["num_hidden_layers"]
+    if args.layers <= 0:
+        args.layers = full_layers
     args.warmup = max(args.warmup, 3)
 
     import numpy as np
@@ -257,7 +269,7 @@ def main():
     room = (args.context + 2 * total_steps + 63) // 64 * 64
     big_batch = 64 if not args.no_points else args.batch
     eng = build_engine(args, args.layers, room * max(big_batch, args.batch), max(big_batch, args.batch))
-    cfg = dict(QWEN3_4B)
+    cfg = dict(MODELS[args.model])
 
     if args.only == "timeline":
         slots, toks = fill(eng, args.batch, args.context, rng)
@@ -333,11 +345,12 @@ def main():
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16" if args.dtype == "bfloat16" else "fp32", "data": "synthetic",
-        "config": {"model": "Qwen3-4B sizes, random weights", "layers": args.layers,
-                   "layers_full": FULL_LAYERS, "hidden": cfg["hidden_size"],
+        "config": {"model": f"Qwen3-{args.model.upper()} sizes, random weights",
+                   "layers": args.layers, "layers_full": full_layers, "hidden": cfg["hidden_size"],
                    "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
                    "head_dim": cfg["head_dim"], "ffn": cfg["intermediate_size"],
-                   "vocab": cfg["vocab_size"], "tied_head": True, "global_batch": args.batch,
+                   "vocab": cfg["vocab_size"], "tied_head": bool(cfg["tie_word_embeddings"]),
+                   "global_batch": args.batch,
                    "seq_len": args.context, "max_context": cfg["max_position_embeddings"],
                    "parallelism": "1 GPU", "l2": "inputs larger than L2 (weights read once a step)",
                    "peaks": pk["source"]},
