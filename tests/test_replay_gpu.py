@@ -131,3 +131,40 @@ def test_unequal_batches_with_slot_reuse(name, dtype):
         b = np.stack([got[rid][p] for p in range(len(toks))])
         e = rel_err(b, a)
         assert e <= tol, f"{name} {rid}: batched and alone differ by {e:.3e}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name,seed", [("A", 1), ("B", 2), ("C", 3), ("D", 4), ("E", 5), ("F", 6)])
+def test_batches_drawn_at_random(name, seed, dtype):
+    """Batches whose sizes, prompt lengths and numbers of decoded tokens are drawn
+    from a seeded generator (lengths around the page and chunk edges among them),
+    in a cache with just enough room for the largest batch: against the plain
+    implementation, and in 32-bit bit for bit against each request alone."""
+    from janas_b200.engine import Engine
+    c = TINY[name]
+    rng = np.random.default_rng(1000 + seed)
+    edges = [1, 2, 63, 64, 65, 127, 128, 129, 191, 192, 193, 255, 256, 257]
+    cap = min(c["max_position_embeddings"], 420)
+    batches = []
+    for _ in range(4):
+        batch = []
+        for _ in range(int(rng.integers(1, 6))):
+            total = int(rng.choice(edges)) if rng.random() < 0.5 else int(rng.integers(1, cap + 1))
+            total = min(total, cap)
+            decoded = int(rng.integers(0, min(total, 40)))      # tokens that come one by one
+            batch.append((tokens(rng, total, c["vocab_size"]), total - decoded))
+        batches.append(batch)
+    need = max(sum((len(t) + 63) // 64 * 64 for t, _ in b) for b in batches)
+    eng = Engine.open(model_dir(name), dtype=dtype, max_tokens=need, max_seqs=5)
+    got = run_trace(eng, trace_batches(batches))
+    eng.cache.check()
+    assert eng.cache.tokens_held() == 0
+    reqs = [t for b in batches for (t, _) in b]
+    ids = [f"b{b}r{i}" for b, batch in enumerate(batches) for i in range(len(batch))]
+    check_against_plain(name, dtype, got, reqs, ids)
+    if dtype == "float32":
+        alone = run_trace(engine(name, dtype), trace_whole(reqs))
+        for k, (rid, toks) in enumerate(zip(ids, reqs)):
+            a = np.stack([alone[f"r{k}"][p] for p in range(len(toks))])
+            b = np.stack([got[rid][p] for p in range(len(toks))])
+            assert rel_err(b, a) <= FP32_CUT_TOL, f"{name} {rid}: batched and alone differ"
