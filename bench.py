@@ -68,7 +68,8 @@ def peaks():
                 return None
             hbm, tf = find(d, "hbm_gbs"), find(d, "bf16_tflops")
             if hbm and tf:
-                return {"hbm_gbs": hbm, "bf16_tflops": tf, "source": "measured"}
+                return {"hbm_gbs": hbm, "bf16_tflops": tf, "source": "measured",
+                        "bf16_tflops_sustained": find(d, "bf16_tflops_sustained")}
         except (OSError, ValueError):
             pass
     return dict(FALLBACK_PEAKS)
@@ -306,6 +307,10 @@ def main():
     dense_peak = pk["bf16_tflops"] * 1e12 * (1.0 if args.dtype == "bfloat16" else 1.0)
     prefill = {"value": round(T / (pre_ms / 1e3), 1), "tokens": T, "ms": round(pre_ms, 3),
                "frac": round(flops / (pre_ms / 1e3) / dense_peak, 4)}
+    if pk.get("bf16_tflops_sustained"):
+        # against the library's throughput in a seconds-long loop under the power cap
+        prefill["frac_sustained"] = round(
+            flops / (pre_ms / 1e3) / (pk["bf16_tflops_sustained"] * 1e12), 4)
 
     # ---- decoding, device-timed
     def decode_point(batch, steps, warmup):
