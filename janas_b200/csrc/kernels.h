@@ -64,10 +64,12 @@ int jb_gemm_tc_swiglu(const void *A, const void *W, void *out_act, int n, int ff
                       cudaStream_t st);
 int jb_gemm_tc_error(void);
 int jb_sample_small_cap(void);
+long long jb_sample_scratch(int rows, int V);
 int jb_sample(const float *logits, int rows, int V, const int32_t *row_slot,
               const float *temperature, const int32_t *top_k, const float *top_p,
               const float *min_p, unsigned long long *rng, unsigned long long *big_keys,
-              float *big_probs, long long big_cap, int32_t *out, int32_t *forced, cudaStream_t st);
+              float *big_probs, long long big_cap, unsigned long long *chunk_keys, int32_t *out,
+              int32_t *forced, cudaStream_t st);
 
 #ifdef __cplusplus
 }

@@ -41,7 +41,7 @@ def lib() -> ctypes.CDLL:
                     _lib = ctypes.CDLL(path)
                 except OSError as e:
                     raise KernelError(f"janas_b200: cannot load {path}: {e}") from None
-                for name in ("jb_attention_scratch",):
+                for name in ("jb_attention_scratch", "jb_sample_scratch"):
                     getattr(_lib, name).restype = ctypes.c_longlong
     return _lib
 
@@ -449,9 +449,14 @@ def sample(logits: torch.Tensor, out: Optional[torch.Tensor] = None,
         big_cap = big_keys.shape[1]
     if temperature is not None and rng is None:
         raise KernelError("sample: temperature needs the random states")
-    _check(lib().jb_sample(_p(logits), rows, V, _p(row_slot), _p(temperature), _p(top_k),
-                           _p(top_p), _p(min_p), _p(rng), _p(big_keys), _p(big_probs),
-                           ctypes.c_longlong(big_cap), _p(out), _p(forced), _stream()), "sample")
+    L = lib()
+    words = int(L.jb_sample_scratch(rows, V))
+    chunk_keys = (torch.empty((words,), dtype=torch.int64, device=logits.device)
+                  if words > 0 else None)
+    _check(L.jb_sample(_p(logits), rows, V, _p(row_slot), _p(temperature), _p(top_k),
+                       _p(top_p), _p(min_p), _p(rng), _p(big_keys), _p(big_probs),
+                       ctypes.c_longlong(big_cap), _p(chunk_keys), _p(out), _p(forced), _stream()),
+           "sample", kernels=2 if words > 0 else 1)
     return out
 
 

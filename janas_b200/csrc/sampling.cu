@@ -11,8 +11,13 @@
 // sum, picks by walking the prefix.  A row with T <= 0 takes the first index
 // of the maximum (src/llm/sample.c:141-148) and uses no random number.
 //
-// One block works on one row.  Up to SMALL_CAP candidates are sorted in shared
-// memory; more than that (top_k off or very large) needs the caller's scratch.
+// Two kernels.  The first cuts every row into chunks of CHUNK logits and lets a
+// block sort each chunk (value falling, id rising) and keep its CHUNK_KEEP best;
+// with ids in the keys that is exact.  The second has one block per row: it sorts
+// the chunks' candidates, which hold the row's CHUNK_KEEP best, and draws.  A row
+// that wants more candidates than that (top_k off or above CHUNK_KEEP) goes the
+// long way in the second kernel, over all its logits: up to SMALL_CAP candidates
+// in shared memory, more in the caller's scratch.
 #include "common.cuh"
 #include "kernels.h"
 
@@ -20,6 +25,9 @@ namespace jb {
 
 constexpr int SAMPLE_THREADS = 1024;
 constexpr int SMALL_CAP = 2048;
+constexpr int CHUNK = 4096;          // logits a block of the first kernel sorts
+constexpr int CHUNK_KEEP = 64;       // candidates it keeps
+constexpr int MERGE_CAP = 4096;      // candidates of all chunks of a row that the second kernel sorts
 
 __device__ __forceinline__ uint32_t ordered_key(float f)
 {
@@ -61,20 +69,121 @@ __device__ void bitonic_sort(uint64_t *keys, int n)
     __syncthreads();
 }
 
+// The draw among nc candidates in their order (falling probability), by one
+// thread: top_p keeps the shortest prefix whose mass reaches top_p * sum, min_p
+// drops what lies below min_p * p_0, one splitmix64 number picks by walking.
+__device__ void draw(const uint64_t *keys, const float *probs, unsigned nc, float tp, float mp,
+                     uint64_t *rng_state, int32_t *out, int32_t *forced)
+{
+    double sum = 0.0;
+    for (unsigned i = 0; i < nc; i++)
+        sum += (double)probs[i];
+    if (tp > 0.0f && tp < 1.0f) {
+        double c = 0.0;
+        double lim = (double)tp * sum;
+        unsigned kk = 0;
+        while (kk < nc && c < lim)
+            c += (double)probs[kk++];
+        nc = kk;
+        sum = c;
+    }
+    if (mp > 0.0f) {
+        unsigned kk = 1;
+        float lim = mp * probs[0];
+        while (kk < nc && probs[kk] >= lim)
+            kk++;
+        for (unsigned i = kk; i < nc; i++)
+            sum -= (double)probs[i];
+        nc = kk;
+    }
+    if (forced)
+        *forced = nc <= 1;
+    uint64_t state = *rng_state;
+    double u = (double)(splitmix64(&state) >> 11) * 0x1.0p-53 * sum;
+    *rng_state = state;
+    int32_t pick = (int32_t)(uint32_t)keys[nc - 1];
+    for (unsigned i = 0; i + 1 < nc; i++) {
+        u -= (double)probs[i];
+        if (u < 0) {
+            pick = (int32_t)(uint32_t)keys[i];
+            break;
+        }
+    }
+    *out = pick;
+}
+
+
+// keys of a candidate: the logit's order-preserving bits inverted in the upper
+// half, its id in the lower, so that ascending keys are falling logits and, among
+// equal logits, rising ids
+__device__ __forceinline__ uint64_t candidate_key(float v, int id)
+{
+    return ((uint64_t)(~ordered_key(v)) << 32) | (uint32_t)id;
+}
+
+// Block (row, chunk): the chunk's CHUNK_KEEP best candidates, in order, into
+// chunk_keys[row][chunk][CHUNK_KEEP] (first_only: only the best one).
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+sample_chunks_kernel(const float *__restrict__ logits, int V, int chunks,
+                     uint64_t *__restrict__ chunk_keys, int first_only)
+{
+    __shared__ uint64_t keys[CHUNK];
+    pdl_trigger();
+    pdl_wait();
+    int row = blockIdx.x / chunks, c = blockIdx.x % chunks, tid = threadIdx.x;
+    const float *lg = logits + (size_t)row * V;
+    uint64_t *dst = chunk_keys + ((size_t)row * chunks + c) * CHUNK_KEEP;
+    uint64_t mine[CHUNK / SAMPLE_THREADS];
+#pragma unroll
+    for (int j = 0; j < CHUNK / SAMPLE_THREADS; j++) {
+        int i = c * CHUNK + tid + j * SAMPLE_THREADS;
+        mine[j] = i < V ? candidate_key(lg[i], i) : ~0ull;
+    }
+    if (first_only) {
+        uint64_t best = mine[0];
+#pragma unroll
+        for (int j = 1; j < CHUNK / SAMPLE_THREADS; j++)
+            best = min(best, mine[j]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+            best = min(best, __shfl_xor_sync(0xffffffffu, best, o));
+        if ((tid & 31) == 0)
+            keys[tid >> 5] = best;
+        __syncthreads();
+        if (tid < 32) {
+            best = keys[tid];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1)
+                best = min(best, __shfl_xor_sync(0xffffffffu, best, o));
+            if (tid == 0)
+                dst[0] = best;
+        }
+        return;
+    }
+#pragma unroll
+    for (int j = 0; j < CHUNK / SAMPLE_THREADS; j++)
+        keys[tid + j * SAMPLE_THREADS] = mine[j];
+    bitonic_sort(keys, CHUNK);
+    if (tid < CHUNK_KEEP)
+        dst[tid] = keys[tid];
+}
+
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const float *__restrict__ logits, int V, const int32_t *__restrict__ row_slot,
               const float *__restrict__ temperature, const int32_t *__restrict__ top_k,
               const float *__restrict__ top_p, const float *__restrict__ min_p,
               uint64_t *__restrict__ rng, uint64_t *__restrict__ big_keys,
-              float *__restrict__ big_probs, long long big_cap, int32_t *__restrict__ out,
-              int32_t *__restrict__ forced)
+              float *__restrict__ big_probs, long long big_cap,
+              const uint64_t *__restrict__ chunk_keys, int chunks, int chunk_kept,
+              int32_t *__restrict__ out, int32_t *__restrict__ forced)
 {
     __shared__ float red_v[32];
     __shared__ int red_i[32];
     __shared__ uint32_t hist[256];
-    __shared__ uint64_t small_keys[SMALL_CAP];
+    __shared__ uint64_t small_keys[MERGE_CAP];
     __shared__ float small_probs[SMALL_CAP];
     __shared__ unsigned n_fill, n_elig, sh_prefix, sh_remain;
+    __shared__ unsigned tie_ids[256];
 
     pdl_trigger();
     pdl_wait();
@@ -82,6 +191,66 @@ sample_kernel(const float *__restrict__ logits, int V, const int32_t *__restrict
     int lane = tid & 31, warp = tid >> 5;
     const float *lg = logits + (size_t)row * V;
     int slot = row_slot ? row_slot[row] : row;
+
+    // ---- the short way: the chunks' candidates hold all this row can want
+    if (chunk_keys != nullptr) {
+        float T = temperature ? temperature[slot] : 0.0f;
+        int tk = top_k ? top_k[slot] : 0;
+        const uint64_t *src = chunk_keys + (size_t)row * chunks * CHUNK_KEEP;
+        if (!(T > 0.0f)) {
+            // the first maximum: the least key among the chunks' best
+            uint64_t best = ~0ull;
+            for (int c = tid; c < chunks; c += SAMPLE_THREADS)
+                best = min(best, src[(size_t)c * CHUNK_KEEP]);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1)
+                best = min(best, __shfl_xor_sync(0xffffffffu, best, o));
+            if (lane == 0)
+                small_keys[warp] = best;
+            __syncthreads();
+            if (warp == 0) {
+                best = small_keys[lane];
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1)
+                    best = min(best, __shfl_xor_sync(0xffffffffu, best, o));
+                if (lane == 0) {
+                    out[row] = (int32_t)(uint32_t)best;
+                    if (forced)
+                        forced[row] = 0;
+                }
+            }
+            return;
+        }
+        if (tk > 0 && tk <= chunk_kept && tk < V) {
+            int have = chunks * chunk_kept;
+            int P = 1;
+            while (P < have)
+                P <<= 1;
+            for (int i = tid; i < P; i += SAMPLE_THREADS)
+                small_keys[i] = i < have ? src[(size_t)(i / chunk_kept) * CHUNK_KEEP + i % chunk_kept]
+                                         : ~0ull;
+            bitonic_sort(small_keys, P);
+            // the tk best of the row, of which those not below max - 30 T count
+            float top = key_value(~(uint32_t)(small_keys[0] >> 32));
+            float floor_v = top - 30.0f * T;
+            if (tid == 0)
+                n_elig = 0;
+            __syncthreads();
+            if (tid < tk) {
+                uint64_t k = small_keys[tid];
+                float l = key_value(~(uint32_t)(k >> 32));
+                bool in = k != ~0ull && l >= floor_v;
+                small_probs[tid] = in ? expf((l - top) / T) : 0.0f;
+                if (in)
+                    atomicAdd(&n_elig, 1u);      // they are a prefix: the keys are sorted
+            }
+            __syncthreads();
+            if (tid == 0)
+                draw(small_keys, small_probs, n_elig, top_p ? top_p[slot] : 0.0f,
+                     min_p ? min_p[slot] : 0.0f, rng + slot, out + row, forced ? forced + row : nullptr);
+            return;
+        }
+    }
 
     // ---- the first maximum
     float bv = -INFINITY;
@@ -214,15 +383,30 @@ sample_kernel(const float *__restrict__ logits, int V, const int32_t *__restrict
         keys[at] = ((uint64_t)(~u) << 32) | (uint32_t)i;
     }
     __syncthreads();
-    if (E > K && tid == 0) {
-        // the candidates equal to the K-th: the lowest ids first
+    if (E > K) {
+        // the candidates equal to the K-th: the lowest ids first.  Ranges of
+        // SAMPLE_THREADS consecutive ids are looked at together; a range's tied ids
+        // are counted in order (ballots), so the ones taken are the lowest.
         unsigned at = n_fill, got = 0;
-        for (int i = 0; i < V && got < need_eq; i++) {
-            float v = lg[i];
-            if (v >= floor_v && ordered_key(v) == thr) {
-                keys[at++] = ((uint64_t)(~thr) << 32) | (uint32_t)i;
-                got++;
+        __syncthreads();
+        for (int base = 0; base < V && got < need_eq; base += SAMPLE_THREADS) {
+            int i = base + tid;
+            bool tie = i < V && lg[i] >= floor_v && ordered_key(lg[i]) == thr;
+            unsigned ballot = __ballot_sync(0xffffffffu, tie);
+            if (lane == 0)
+                tie_ids[warp] = __popc(ballot);
+            __syncthreads();
+            unsigned before = 0, total = 0;
+            for (int w = 0; w < SAMPLE_THREADS / 32; w++) {
+                unsigned c = tie_ids[w];
+                before += w < warp ? c : 0;
+                total += c;
             }
+            unsigned rank = got + before + __popc(ballot & ((1u << lane) - 1));
+            if (tie && rank < need_eq)
+                keys[at + rank] = ((uint64_t)(~thr) << 32) | (uint32_t)i;
+            got += total;
+            __syncthreads();
         }
     }
     for (int i = n_sel + tid; i < P; i += SAMPLE_THREADS)
@@ -236,74 +420,59 @@ sample_kernel(const float *__restrict__ logits, int V, const int32_t *__restrict
         probs[i] = expf((l - top) / T);
     }
     __syncthreads();
-    if (tid != 0)
-        return;
-
-    // ---- the draw, in the candidates' order
-    unsigned nc = n_sel;
-    double sum = 0.0;
-    for (unsigned i = 0; i < nc; i++)
-        sum += (double)probs[i];
-    float tp = top_p ? top_p[slot] : 0.0f;
-    if (tp > 0.0f && tp < 1.0f) {
-        double c = 0.0;
-        double lim = (double)tp * sum;
-        unsigned kk = 0;
-        while (kk < nc && c < lim)
-            c += (double)probs[kk++];
-        nc = kk;
-        sum = c;
-    }
-    float mp = min_p ? min_p[slot] : 0.0f;
-    if (mp > 0.0f) {
-        unsigned kk = 1;
-        float lim = mp * probs[0];
-        while (kk < nc && probs[kk] >= lim)
-            kk++;
-        for (unsigned i = kk; i < nc; i++)
-            sum -= (double)probs[i];
-        nc = kk;
-    }
-    if (forced)
-        forced[row] = nc <= 1;
-    uint64_t state = rng[slot];
-    double u = (double)(splitmix64(&state) >> 11) * 0x1.0p-53 * sum;
-    rng[slot] = state;
-    int32_t pick = (int32_t)(uint32_t)keys[nc - 1];
-    for (unsigned i = 0; i + 1 < nc; i++) {
-        u -= (double)probs[i];
-        if (u < 0) {
-            pick = (int32_t)(uint32_t)keys[i];
-            break;
-        }
-    }
-    out[row] = pick;
+    if (tid == 0)
+        draw(keys, probs, n_sel, top_p ? top_p[slot] : 0.0f, min_p ? min_p[slot] : 0.0f,
+             rng + slot, out + row, forced ? forced + row : nullptr);
 }
 
 }  // namespace jb
+
 
 using namespace jb;
 
 extern "C" int jb_sample_small_cap() { return SMALL_CAP; }
 
+// 64-bit words of scratch that jb_sample wants for rows x V logits (0: none, the
+// vocabulary is too large for the short way and every row goes the long one).
+extern "C" long long jb_sample_scratch(int rows, int V)
+{
+    long long chunks = (V + CHUNK - 1) / CHUNK;
+    if (rows <= 0 || V <= 0 || chunks * CHUNK_KEEP > MERGE_CAP)
+        return 0;
+    return (long long)rows * chunks * CHUNK_KEEP;
+}
+
 // logits: [rows, V] float.  The per-sequence settings and the random state
 // are indexed by row_slot[row] (by the row itself when row_slot is null);
-// temperature null means every row takes the first maximum.  big_keys
-// [rows, big_cap] and big_probs [rows, big_cap] are needed only when a row may
-// keep more than jb_sample_small_cap() candidates; big_cap must then be a power
-// of two not below V.  out[row] is the token, or -1 when that scratch was
-// needed and not given.
+// temperature null means every row takes the first maximum.  chunk_keys:
+// jb_sample_scratch(rows, V) words of scratch (or null: every row goes the long
+// way).  big_keys [rows, big_cap] and big_probs [rows, big_cap] are needed only
+// when a row may keep more than jb_sample_small_cap() candidates; big_cap must
+// then be a power of two not below V.  out[row] is the token, or -1 when that
+// scratch was needed and not given.
 extern "C" int jb_sample(const float *logits, int rows, int V, const int32_t *row_slot,
                          const float *temperature, const int32_t *top_k, const float *top_p,
                          const float *min_p, unsigned long long *rng,
                          unsigned long long *big_keys, float *big_probs, long long big_cap,
-                         int32_t *out, int32_t *forced, cudaStream_t st)
+                         unsigned long long *chunk_keys, int32_t *out, int32_t *forced,
+                         cudaStream_t st)
 {
     if (rows <= 0)
         return JB_OK;
     if (V <= 0 || (temperature != nullptr && rng == nullptr))
         return JB_EINVAL;
+    int chunks = (V + CHUNK - 1) / CHUNK;
+    if (chunk_keys != nullptr && jb_sample_scratch(rows, V) == 0)
+        chunk_keys = nullptr;
+    int kept = temperature == nullptr ? 1 : CHUNK_KEEP;      // greedy: a chunk's best is enough
+    if (chunk_keys != nullptr) {
+        launch(sample_chunks_kernel, (unsigned)(rows * chunks), SAMPLE_THREADS, 0, st, logits, V,
+               chunks, (uint64_t *)chunk_keys, temperature == nullptr ? 1 : 0);
+        if (cudaGetLastError() != cudaSuccess)
+            return JB_ELAUNCH;
+    }
     launch(sample_kernel, rows, SAMPLE_THREADS, 0, st, logits, V, row_slot, temperature, top_k, top_p,
-           min_p, (uint64_t *)rng, (uint64_t *)big_keys, big_probs, big_cap, out, forced);
+           min_p, (uint64_t *)rng, (uint64_t *)big_keys, big_probs, big_cap,
+           (const uint64_t *)chunk_keys, chunks, kept, out, forced);
     return launch_status();
 }
