@@ -121,51 +121,120 @@ __device__ __forceinline__ uint64_t candidate_key(float v, int id)
     return ((uint64_t)(~ordered_key(v)) << 32) | (uint32_t)id;
 }
 
+// Ascending sort of the 128 keys of a warp, four per lane: key j of lane l is
+// element 4 l + j.  A bitonic network; steps between lanes go through shuffles.
+__device__ __forceinline__ void warp_sort128(uint64_t (&k)[4], int lane)
+{
+#pragma unroll
+    for (int size = 2; size <= 128; size <<= 1) {
+#pragma unroll
+        for (int stride = size >> 1; stride > 0; stride >>= 1) {
+            if (stride >= 4) {
+                bool lower = (lane & (stride >> 2)) == 0;
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    uint64_t other = __shfl_xor_sync(0xffffffffu, k[j], stride >> 2);
+                    bool up = (((lane << 2) | j) & size) == 0;
+                    k[j] = (lower == up) ? min(k[j], other) : max(k[j], other);
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    if ((j & stride) == 0) {
+                        bool up = (((lane << 2) | j) & size) == 0;
+                        uint64_t a = k[j], c = k[j | stride];
+                        k[j] = up ? min(a, c) : max(a, c);
+                        k[j | stride] = up ? max(a, c) : min(a, c);
+                    }
+                }
+            }
+        }
+    }
+}
+
+// Ascending sort of a bitonic sequence of 64 keys, two per lane (element 2 l + j).
+__device__ __forceinline__ void warp_merge64(uint64_t (&v)[2], int lane)
+{
+#pragma unroll
+    for (int stride = 32; stride >= 2; stride >>= 1) {
+        bool lower = (lane & (stride >> 1)) == 0;
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+            uint64_t other = __shfl_xor_sync(0xffffffffu, v[j], stride >> 1);
+            v[j] = lower ? min(v[j], other) : max(v[j], other);
+        }
+    }
+    uint64_t a = v[0], c = v[1];
+    v[0] = min(a, c);
+    v[1] = max(a, c);
+}
+
 // Block (row, chunk): the chunk's CHUNK_KEEP best candidates, in order, into
-// chunk_keys[row][chunk][CHUNK_KEEP] (first_only: only the best one).
+// chunk_keys[row][chunk][CHUNK_KEEP] (first_only: only the best one).  Every warp
+// sorts its 128 keys in registers and keeps the best 64; the warps' lists are then
+// merged two by two, each time keeping the best 64 of 128, until one is left.
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_chunks_kernel(const float *__restrict__ logits, int V, int chunks,
                      uint64_t *__restrict__ chunk_keys, int first_only)
 {
-    __shared__ uint64_t keys[CHUNK];
+    static_assert(CHUNK == 4 * SAMPLE_THREADS && CHUNK_KEEP == 64, "the merge below is for these");
+    __shared__ uint64_t lists[2][SAMPLE_THREADS / 32][CHUNK_KEEP];
     pdl_trigger();
     pdl_wait();
     int row = blockIdx.x / chunks, c = blockIdx.x % chunks, tid = threadIdx.x;
+    int lane = tid & 31, warp = tid >> 5;
     const float *lg = logits + (size_t)row * V;
     uint64_t *dst = chunk_keys + ((size_t)row * chunks + c) * CHUNK_KEEP;
-    uint64_t mine[CHUNK / SAMPLE_THREADS];
+    uint64_t mine[4];
 #pragma unroll
-    for (int j = 0; j < CHUNK / SAMPLE_THREADS; j++) {
+    for (int j = 0; j < 4; j++) {
         int i = c * CHUNK + tid + j * SAMPLE_THREADS;
         mine[j] = i < V ? candidate_key(lg[i], i) : ~0ull;
     }
     if (first_only) {
-        uint64_t best = mine[0];
-#pragma unroll
-        for (int j = 1; j < CHUNK / SAMPLE_THREADS; j++)
-            best = min(best, mine[j]);
+        uint64_t best = min(min(mine[0], mine[1]), min(mine[2], mine[3]));
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1)
             best = min(best, __shfl_xor_sync(0xffffffffu, best, o));
-        if ((tid & 31) == 0)
-            keys[tid >> 5] = best;
+        if (lane == 0)
+            lists[0][0][warp] = best;
         __syncthreads();
-        if (tid < 32) {
-            best = keys[tid];
+        if (warp == 0) {
+            best = lists[0][0][lane];
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1)
                 best = min(best, __shfl_xor_sync(0xffffffffu, best, o));
-            if (tid == 0)
+            if (lane == 0)
                 dst[0] = best;
         }
         return;
     }
+    warp_sort128(mine, lane);
+    if (lane < 16) {                            // elements 0 .. 63: the warp's best
 #pragma unroll
-    for (int j = 0; j < CHUNK / SAMPLE_THREADS; j++)
-        keys[tid + j * SAMPLE_THREADS] = mine[j];
-    bitonic_sort(keys, CHUNK);
+        for (int j = 0; j < 4; j++)
+            lists[0][warp][4 * lane + j] = mine[j];
+    }
+    __syncthreads();
+    int buf = 0;
+    for (int n = SAMPLE_THREADS / 32; n > 1; n >>= 1, buf ^= 1) {
+        if (warp < n / 2) {
+            // A rising, B falling: a bitonic sequence whose lower half after one
+            // compare step holds the best 64 of the 128
+            uint64_t v[2];
+#pragma unroll
+            for (int j = 0; j < 2; j++) {
+                int i = 2 * lane + j;
+                v[j] = min(lists[buf][2 * warp][i], lists[buf][2 * warp + 1][CHUNK_KEEP - 1 - i]);
+            }
+            warp_merge64(v, lane);
+            lists[buf ^ 1][warp][2 * lane] = v[0];
+            lists[buf ^ 1][warp][2 * lane + 1] = v[1];
+        }
+        __syncthreads();
+    }
     if (tid < CHUNK_KEEP)
-        dst[tid] = keys[tid];
+        dst[tid] = lists[buf][0][tid];
 }
 
 __global__ void __launch_bounds__(SAMPLE_THREADS)
@@ -221,15 +290,30 @@ sample_kernel(const float *__restrict__ logits, int V, const int32_t *__restrict
             }
             return;
         }
-        if (tk > 0 && tk <= chunk_kept && tk < V) {
-            int have = chunks * chunk_kept;
-            int P = 1;
-            while (P < have)
-                P <<= 1;
-            for (int i = tid; i < P; i += SAMPLE_THREADS)
-                small_keys[i] = i < have ? src[(size_t)(i / chunk_kept) * CHUNK_KEEP + i % chunk_kept]
-                                         : ~0ull;
-            bitonic_sort(small_keys, P);
+        if (tk > 0 && tk <= chunk_kept && chunk_kept == CHUNK_KEEP && tk < V) {
+            // the chunks' lists (each sorted, up to 64 of them) are merged two by two,
+            // keeping the best 64 of 128 each time, in place: the warp that merges
+            // lists a and a + step writes into a
+            static_assert(MERGE_CAP == 64 * CHUNK_KEEP, "64 lists of CHUNK_KEEP keys");
+            for (int i = tid; i < MERGE_CAP; i += SAMPLE_THREADS)
+                small_keys[i] = i / CHUNK_KEEP < chunks ? src[i] : ~0ull;
+            __syncthreads();
+            for (int step = 1; step < 64; step <<= 1) {
+                int a = 2 * step * warp;
+                if (a + step < 64) {
+                    uint64_t v[2];
+#pragma unroll
+                    for (int j = 0; j < 2; j++) {
+                        int i = 2 * lane + j;
+                        v[j] = min(small_keys[a * CHUNK_KEEP + i],
+                                   small_keys[(a + step) * CHUNK_KEEP + CHUNK_KEEP - 1 - i]);
+                    }
+                    warp_merge64(v, lane);
+                    small_keys[a * CHUNK_KEEP + 2 * lane] = v[0];
+                    small_keys[a * CHUNK_KEEP + 2 * lane + 1] = v[1];
+                }
+                __syncthreads();
+            }
             // the tk best of the row, of which those not below max - 30 T count
             float top = key_value(~(uint32_t)(small_keys[0] >> 32));
             float floor_v = top - 30.0f * T;
