@@ -65,6 +65,7 @@ int jb_gemm_tc_swiglu(const void *A, const void *W, void *out_act, int n, int ff
 int jb_gemm_tc_error(void);
 int jb_sample_small_cap(void);
 long long jb_sample_scratch(int rows, int V);
+int jb_sample_launches(int V, long long big_cap, int sampled);
 int jb_sample(const float *logits, int rows, int V, const int32_t *row_slot,
               const float *temperature, const int32_t *top_k, const float *top_p,
               const float *min_p, unsigned long long *rng, unsigned long long *big_keys,

@@ -450,13 +450,13 @@ def sample(logits: torch.Tensor, out: Optional[torch.Tensor] = None,
     if temperature is not None and rng is None:
         raise KernelError("sample: temperature needs the random states")
     L = lib()
-    words = int(L.jb_sample_scratch(rows, V))
-    chunk_keys = (torch.empty((words,), dtype=torch.int64, device=logits.device)
-                  if words > 0 else None)
+    chunk_keys = torch.empty((int(L.jb_sample_scratch(rows, V)),), dtype=torch.int64,
+                             device=logits.device)
+    launches = int(L.jb_sample_launches(V, ctypes.c_longlong(big_cap), int(temperature is not None)))
     _check(L.jb_sample(_p(logits), rows, V, _p(row_slot), _p(temperature), _p(top_k),
                        _p(top_p), _p(min_p), _p(rng), _p(big_keys), _p(big_probs),
                        ctypes.c_longlong(big_cap), _p(chunk_keys), _p(out), _p(forced), _stream()),
-           "sample", kernels=2 if words > 0 else 1)
+           "sample", kernels=launches)
     return out
 
 

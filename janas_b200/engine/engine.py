@@ -77,6 +77,7 @@ class Engine:
             getattr(b.mixer, "graph_safe", False) for b in model.blocks)
         self._graphs: Dict[Tuple[int, int, bool], "DecodeGraph"] = {}
         self._graph_pool = None
+        self._sampler_scratch = None
         # run-order entry -> (group, index within the group) of the cache it uses
         self._cache_entry: List[Optional[int]] = []
         for e, entry in enumerate(model.spec.run_order):
@@ -217,7 +218,7 @@ class Engine:
         context bound, else they are launched one by one."""
         from ..csrc import ops
         entries = [StepEntry(s, [int(t)], [0]) for s, t in zip(slots, tokens)]
-        if not self.use_graphs or big is not None:
+        if not self.use_graphs:
             logits = self.step(entries)
             return self._sample(logits, list(slots), sampled, big)
         kind, toks, pos0, lens = self.plan(entries)
@@ -227,13 +228,29 @@ class Engine:
         # 256 positions keeps them close to what the step needs
         need = int(pos0.max()) + 1
         bound = min((need + 255) // 256 * 256, self.max_positions)
-        key = (len(slots), bound, bool(sampled))
+        # ``big``: some row may keep more candidates than the sampler's short way
+        # holds; the graph then sorts all of a row's logits in the engine's scratch
+        key = (len(slots), bound, bool(sampled), big is not None and bool(sampled))
         g = self._graphs.get(key)
         if g is None:
-            g = self._graphs[key] = DecodeGraph(self, len(slots), bound, bool(sampled))
+            g = self._graphs[key] = DecodeGraph(self, len(slots), bound, bool(sampled), key[3])
         out = g.run(slots, toks, pos0)
         self.cache.advance(slots, lens.tolist())
         return out
+
+    def sampler_scratch(self, rows: int):
+        """Room for every logit of ``rows`` rows as a sort key and as a probability:
+        what the sampler needs for rows that keep more candidates than its short way
+        holds (top-k off or large).  One allocation for the engine's life."""
+        if self._sampler_scratch is None:
+            vocab = self.model.spec.vocab_size
+            cap = 1 << (vocab - 1).bit_length()
+            n = self.cache.max_seqs
+            self._sampler_scratch = (
+                torch.empty((n, cap), dtype=torch.int64, device=self.device),
+                torch.empty((n, cap), dtype=torch.float32, device=self.device))
+        k, p = self._sampler_scratch
+        return k[:rows], p[:rows]
 
     def _sample(self, logits: torch.Tensor, slots: List[int], sampled: bool, big) -> np.ndarray:
         from ..csrc import ops
@@ -258,9 +275,11 @@ class DecodeGraph:
     depend on the context (the attention's chunk count) are fixed at ``bound``;
     rows whose range is shorter leave those chunks at once."""
 
-    def __init__(self, engine: "Engine", batch: int, bound: int, sampled: bool):
+    def __init__(self, engine: "Engine", batch: int, bound: int, sampled: bool,
+                 long_way: bool = False):
         from ..cache.pages import pages_for
         self.engine, self.batch, self.bound, self.sampled = engine, batch, bound, sampled
+        self.long_way = long_way
         self.width = (pages_for(bound) + 7) // 8 * 8
         n_groups = len(engine.cache.groups)
         total = 4 * batch + n_groups * batch * self.width
@@ -286,8 +305,10 @@ class DecodeGraph:
         logits = eng.model.forward(ctx, v(0), eng._layer_caches(bt), None)
         c = eng.cache
         if self.sampled:
+            big = eng.sampler_scratch(B) if self.long_way else (None, None)
             ops.sample(logits, out=self.out_dev, row_slot=v(3), temperature=c.temperature,
-                       top_k=c.top_k, top_p=c.top_p, min_p=c.min_p, rng=c.rng)
+                       top_k=c.top_k, top_p=c.top_p, min_p=c.min_p, rng=c.rng,
+                       big_keys=big[0], big_probs=big[1])
         else:
             ops.sample(logits, out=self.out_dev)
         self.out_host.copy_(self.out_dev, non_blocking=True)

@@ -172,9 +172,13 @@ def generate(engine, requests: Sequence[Request], max_batch: int = 64,
             if sampled and any(requests[i].options.temperature > 0 and
                                not 0 < requests[i].options.top_k <= ops.sample_small_cap()
                                for i in live):
-                cap = 1 << (vocab - 1).bit_length()
-                big = (torch.empty((len(live), cap), dtype=torch.int64, device=engine.device),
-                       torch.empty((len(live), cap), dtype=torch.float32, device=engine.device))
+                if hasattr(engine, "sampler_scratch"):
+                    big = engine.sampler_scratch(len(live))
+                else:
+                    cap = 1 << (vocab - 1).bit_length()
+                    big = (torch.empty((len(live), cap), dtype=torch.int64, device=engine.device),
+                           torch.empty((len(live), cap), dtype=torch.float32,
+                                       device=engine.device))
             out = {i: [] for i in live}
             stops = {i: requests[i].options.stop_set() for i in live}
 
