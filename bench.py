@@ -5,6 +5,7 @@
                     [--batch B] [--context C] [--dtype bfloat16|float32] [--no-points]
     python bench.py --impl reference ...     (prints why it is unavailable)
     python bench.py --only decode|prefill|timeline ...   (one part, for profiling)
+    python bench.py --only generate [--model 8b] ...      (unequal prompts, then 256 tokens each)
 
 The default run has the layer sizes of Qwen3-4B (36 layers, hidden 2560, 32
 heads, 8 KV heads, head size 128, feed-forward 9728, vocabulary 151936, tied
@@ -225,6 +226,28 @@ def prefill_flops(cfg, n_layers, tokens):
     return n_layers * (per_token * tokens + attn) + 2 * dm * cfg["vocab_size"]
 
 
+def generate_workload(eng, args, rng, new_tokens=256):
+    """A batch of unequal prompts through the entry point: host token lists in, host
+    token lists out.  Prints one line per run; the first run pays for graph captures."""
+    import janas_b200
+    from janas_b200.engine.generate import GenOptions
+    vocab = MODELS[args.model]["vocab_size"]
+    llm = janas_b200.LLM(eng, janas_b200.LLMParams(n_ctx=eng.max_positions, dtype=args.dtype,
+                                                  max_batch=args.batch))
+    for run in range(3):
+        lens = rng.integers(64, args.context + 1, size=args.batch).tolist()
+        prompts = [rng.integers(0, vocab, size=n).tolist() for n in lens]
+        t0 = time.perf_counter()
+        outs, st = llm.generate_batch(prompts, new_tokens, GenOptions(eos=-1))
+        wall = time.perf_counter() - t0
+        print(f"generate run {run}: prompts {lens} ({sum(lens)} tokens) prefill "
+              f"{1e3 * st.prefill_seconds:.1f} ms ({sum(lens) / st.prefill_seconds:,.0f} tokens/s), "
+              f"{st.new_tokens} new tokens in {st.passes} steps, "
+              f"{1e3 * st.decode_seconds / max(st.passes, 1):.3f} ms a step "
+              f"({args.batch * st.passes / st.decode_seconds:,.0f} tokens/s), "
+              f"whole call {wall:.3f} s", flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -239,9 +262,11 @@ def main():
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--no-points", action="store_true", help="skip decoding at batch 1 and 64")
-    ap.add_argument("--only", default="", choices=["", "decode", "prefill", "timeline"],
+    ap.add_argument("--only", default="", choices=["", "decode", "prefill", "timeline", "generate"],
                     help="run one part only and print its time (for profiling; no JSON line); "
-                         "timeline: when each kernel of one replayed decode step ends")
+                         "timeline: when each kernel of one replayed decode step ends; "
+                         "generate: --batch prompts of lengths uniform in [64, --context], all in "
+                         "one step, then 256 tokens each through the Python entry point")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -269,12 +294,18 @@ def main():
     total_steps = args.warmup + args.steps + 8
     room = (args.context + 2 * total_steps + 63) // 64 * 64
     big_batch = 64 if not args.no_points else args.batch
+    if args.only == "generate":
+        room, big_batch = (args.context + 256 + 127) // 64 * 64, args.batch
     eng = build_engine(args, args.layers, room * max(big_batch, args.batch), max(big_batch, args.batch))
     cfg = dict(MODELS[args.model])
 
     if args.only == "timeline":
         slots, toks = fill(eng, args.batch, args.context, rng)
         decode_timeline(eng, slots, toks, args.warmup)
+        return 0
+
+    if args.only == "generate":
+        generate_workload(eng, args, rng)
         return 0
 
     if args.only == "decode":

@@ -77,6 +77,7 @@ class Engine:
             getattr(b.mixer, "graph_safe", False) for b in model.blocks)
         self._graphs: Dict[Tuple[int, int, bool], "DecodeGraph"] = {}
         self._graph_pool = None
+        self._capture_stream = None
         self._sampler_scratch = None
         # run-order entry -> (group, index within the group) of the cache it uses
         self._cache_entry: List[Optional[int]] = []
@@ -338,10 +339,23 @@ class DecodeGraph:
                 graph = torch.cuda.CUDAGraph()
                 if eng._graph_pool is None:
                     eng._graph_pool = torch.cuda.graph_pool_handle()
+                    eng._capture_stream = torch.cuda.Stream(eng.device)
                 from ..csrc import ops
                 before = ops.COUNTERS["launches"]
-                with torch.cuda.graph(graph, pool=eng._graph_pool):
-                    self._launch()
+                # capture_begin/capture_end on a stream of the engine's own, not the
+                # torch.cuda.graph context: that one collects garbage and empties the
+                # allocator's cache first, which gives the last prefill's blocks back
+                # to the driver (0.3 s and more after a long prompt, and the next
+                # prefill pays for getting them again)
+                side = eng._capture_stream
+                side.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(side):
+                    graph.capture_begin(pool=eng._graph_pool)
+                    try:
+                        self._launch()
+                    finally:
+                        graph.capture_end()
+                torch.cuda.current_stream().wait_stream(side)
                 self.kernels = ops.COUNTERS["launches"] - before   # kernels per replay
                 ops.COUNTERS["launches"] = before
                 self.graph = graph
