@@ -75,7 +75,10 @@ class Engine:
         self.h2d_bytes = 0       # bytes of step inputs copied to the device so far
         self.use_graphs = os.environ.get("JANAS_B200_GRAPHS", "1") != "0" and all(
             getattr(b.mixer, "graph_safe", False) for b in model.blocks)
-        self._graphs: Dict[Tuple[int, int, bool], "DecodeGraph"] = {}
+        # captured decode steps by (batch, context bound, sampled, long way), the one
+        # used last at the end; the oldest goes when there are more than max_graphs
+        self._graphs: Dict[Tuple[int, int, bool, bool], "DecodeGraph"] = {}
+        self.max_graphs = 64
         self._graph_pool = None
         self._capture_stream = None
         self._sampler_scratch = None
@@ -232,9 +235,14 @@ class Engine:
         # ``big``: some row may keep more candidates than the sampler's short way
         # holds; the graph then sorts all of a row's logits in the engine's scratch
         key = (len(slots), bound, bool(sampled), big is not None and bool(sampled))
-        g = self._graphs.get(key)
+        g = self._graphs.pop(key, None)
         if g is None:
-            g = self._graphs[key] = DecodeGraph(self, len(slots), bound, bool(sampled), key[3])
+            g = DecodeGraph(self, len(slots), bound, bool(sampled), key[3])
+            while len(self._graphs) >= max(self.max_graphs, 1):
+                del self._graphs[next(iter(self._graphs))]
+            if not self._graphs:
+                self._graph_pool = None     # a pool ends with its last graph: take a new one
+        self._graphs[key] = g
         out = g.run(slots, toks, pos0)
         self.cache.advance(slots, lens.tolist())
         return out
@@ -339,6 +347,7 @@ class DecodeGraph:
                 graph = torch.cuda.CUDAGraph()
                 if eng._graph_pool is None:
                     eng._graph_pool = torch.cuda.graph_pool_handle()
+                if eng._capture_stream is None:
                     eng._capture_stream = torch.cuda.Stream(eng.device)
                 from ..csrc import ops
                 before = ops.COUNTERS["launches"]

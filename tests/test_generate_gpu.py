@@ -185,3 +185,26 @@ def test_replayed_decode_steps_equal_launched_ones(dtype):
         b, _ = m.generate_batch(ps, news, opts)
         assert a == b
         m.engine.cache.check()
+
+
+def test_old_decode_graphs_are_dropped_and_captured_again():
+    """No more than ``max_graphs`` captured steps are kept: the one used longest ago
+    goes, and a batch shape that comes back is captured again with the same tokens."""
+    import janas_b200
+    rng = np.random.default_rng(32)
+    v = TINY["B"]["vocab_size"]
+    ps = [tokens(rng, n, v) for n in (9, 30, 2, 70)]
+    news = [25, 8, 16, 12]
+    m = janas_b200.open(model_dir("B"), janas_b200.LLMParams(n_ctx=256, dtype="bfloat16",
+                                                            max_batch=4, max_tokens=1024))
+    first, _ = m.generate_batch(ps, news)
+    shapes = len(m.engine._graphs)
+    assert shapes >= 3
+    m.engine._graphs.clear()
+    m.engine.max_graphs = 2
+    again, _ = m.generate_batch(ps, news)
+    assert again == first
+    assert len(m.engine._graphs) == 2
+    third, _ = m.generate_batch(ps, news)       # the first shapes were dropped meanwhile
+    assert third == first
+    m.engine.cache.check()
