@@ -244,13 +244,15 @@ __global__ void attn_merge_kernel(const float *__restrict__ part,
     const float *base = part + part_at((size_t)lrow, nh, h, max_chunks, 0, hd);
     size_t stride = part_at(0, nh, 0, max_chunks, 1, hd);
     float m = -INFINITY, l = 0.0f, o = 0.0f;
-    // a row with few partials fetches four at a time, one with many sixteen: most
-    // rows need one trip to memory
+    // a row with few partials fetches four at a time, one with more sixteen, one
+    // with many thirty-two: most rows need one trip to memory
     if (n_chunks <= 4) {
         merge_partials<4>(base, stride, 0, n_chunks, d, hd, m, l, o);
+    } else if (n_chunks <= 16) {
+        merge_partials<16>(base, stride, 0, n_chunks, d, hd, m, l, o);
     } else {
-        for (int c0 = 0; c0 < n_chunks; c0 += 16)
-            merge_partials<16>(base, stride, c0, n_chunks, d, hd, m, l, o);
+        for (int c0 = 0; c0 < n_chunks; c0 += 32)
+            merge_partials<32>(base, stride, c0, n_chunks, d, hd, m, l, o);
     }
     if (d < hd)
         out[((size_t)row * nh + h) * hd + d] = from_f<T>(o / l);

@@ -255,6 +255,117 @@ qk_norm_rope_append_vec_kernel(
     }
 }
 
+// The same arithmetic, head by head, for many rows: a block has one row, its four
+// warps take the row's groups of head slots in turn, three groups at a time so that
+// their loads are in flight together.  What belongs to the row (position, page,
+// rotation, norm weights) is fetched once per warp instead of once per group; the
+// kernel above spends three quarters of its instructions on that.  Each head's sums
+// run in the order of the kernel above, so that which of the two runs changes nothing.
+template <typename TC, typename TW, int LPH>
+__global__ void __launch_bounds__(128)
+qk_norm_rope_append_row_kernel(
+    const float *__restrict__ qkv, int S, size_t split_stride, const TW *__restrict__ q_w,
+    const TW *__restrict__ k_w, float eps, const float *__restrict__ cs,
+    const float *__restrict__ sn, int rot_half, const int32_t *__restrict__ row_pos,
+    const int32_t *__restrict__ row_seq, const int32_t *__restrict__ block_table, int bt_stride,
+    TC *__restrict__ q_out, TC *__restrict__ k_cache, TC *__restrict__ v_cache, int n, int nh,
+    int nkv)
+{
+    constexpr int SLOTS_PER_WARP = 32 / LPH, U = 3;
+    constexpr int half = 4 * LPH, hd = 2 * half;
+    pdl_trigger();
+    unsigned row = blockIdx.x;
+    int slots = nh + 2 * nkv;
+    int groups = (slots + SLOTS_PER_WARP - 1) / SLOTS_PER_WARP;
+    int at4 = 4 * (threadIdx.x % LPH), sub = threadIdx.x / LPH;
+    int pos = row_pos[row];
+    int page = k_cache != nullptr ? block_table[(size_t)row_seq[row] * bt_stride + pos / PAGE] : 0;
+    bool has_norm = q_w != nullptr, has_rot = rot_half == half;
+    float4 one = make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+    float4 co = one, si = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    float4 qwl = one, qwh = one, kwl = one, kwh = one;
+    if (has_rot) {
+        co = load4(cs + (size_t)pos * half + at4);
+        si = load4(sn + (size_t)pos * half + at4);
+    }
+    if (has_norm) {
+        qwl = load4(q_w + at4);
+        qwh = load4(q_w + half + at4);
+        kwl = load4(k_w + at4);
+        kwh = load4(k_w + half + at4);
+    }
+    pdl_wait();
+    const float *src_row = qkv + (size_t)row * slots * hd + at4;
+    TC *q_row = q_out + (size_t)row * nh * hd + at4;
+    size_t cache_at = ((size_t)page * nkv * PAGE + (pos % PAGE)) * hd + at4;
+    for (int g0 = threadIdx.y; g0 < groups; g0 += 4 * U) {
+        float4 lo[U], hi[U];
+        int hs[U];
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            int g = g0 + 4 * u;
+            hs[u] = g < groups && g * SLOTS_PER_WARP + sub < slots ? g * SLOTS_PER_WARP + sub : -1;
+            lo[u] = hi[u] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        }
+        for (int s = 0; s < S; s++) {
+            float4 a[U], b[U];
+#pragma unroll
+            for (int u = 0; u < U; u++)
+                if (hs[u] >= 0) {
+                    const float *src = src_row + (size_t)s * split_stride + (size_t)hs[u] * hd;
+                    a[u] = load4(src);
+                    b[u] = load4(src + half);
+                }
+#pragma unroll
+            for (int u = 0; u < U; u++)
+                if (hs[u] >= 0) {
+                    lo[u].x += a[u].x; lo[u].y += a[u].y; lo[u].z += a[u].z; lo[u].w += a[u].w;
+                    hi[u].x += b[u].x; hi[u].y += b[u].y; hi[u].z += b[u].z; hi[u].w += b[u].w;
+                }
+        }
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            float4 l = lo[u], h = hi[u];
+            float ss = l.x * l.x;
+            ss = fmaf(l.y, l.y, ss); ss = fmaf(l.z, l.z, ss); ss = fmaf(l.w, l.w, ss);
+            ss = fmaf(h.x, h.x, ss); ss = fmaf(h.y, h.y, ss);
+            ss = fmaf(h.z, h.z, ss); ss = fmaf(h.w, h.w, ss);
+#pragma unroll
+            for (int o = LPH / 2; o > 0; o >>= 1)
+                ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            if (hs[u] < 0)
+                continue;
+            bool is_q = hs[u] < nh, is_v = hs[u] >= nh + nkv;
+            TC *dst;
+            if (is_q) {
+                dst = q_row + (size_t)hs[u] * hd;
+            } else {
+                if (k_cache == nullptr)
+                    continue;
+                int kvh = !is_v ? hs[u] - nh : hs[u] - nh - nkv;
+                dst = (!is_v ? k_cache : v_cache) + cache_at + (size_t)kvh * PAGE * hd;
+            }
+            if (!is_v && has_norm) {
+                float scale = 1.0f / sqrtf(ss / (float)hd + eps);
+                float4 wl = is_q ? qwl : kwl, wh = is_q ? qwh : kwh;
+                l.x = (l.x * scale) * wl.x; l.y = (l.y * scale) * wl.y;
+                l.z = (l.z * scale) * wl.z; l.w = (l.w * scale) * wl.w;
+                h.x = (h.x * scale) * wh.x; h.y = (h.y * scale) * wh.y;
+                h.z = (h.z * scale) * wh.z; h.w = (h.w * scale) * wh.w;
+            }
+            if (!is_v && has_rot) {
+                float4 a = l, b = h;
+                l = make_float4(a.x * co.x - b.x * si.x, a.y * co.y - b.y * si.y,
+                                a.z * co.z - b.z * si.z, a.w * co.w - b.w * si.w);
+                h = make_float4(a.x * si.x + b.x * co.x, a.y * si.y + b.y * co.y,
+                                a.z * si.z + b.z * co.z, a.w * si.w + b.w * co.w);
+            }
+            store4(dst, l);
+            store4(dst + half, h);
+        }
+    }
+}
+
 }  // namespace jb
 
 using namespace jb;
@@ -299,11 +410,21 @@ extern "C" int jb_qk_norm_rope_append(const float *qkv, int S, long long split_s
         if (tasks > 0xffffffffu)
             return JB_EINVAL;
         unsigned grid = (unsigned)std::min<size_t>((tasks + 3) / 4, (size_t)sm_count() * 16);
+        // from 256 rows on a block per row: fewer instructions; below, more warps per row
+        bool by_row = n >= 256;
 #define JB_ROPE_V(TC, TW, L)                                                                   \
-    launch(qk_norm_rope_append_vec_kernel<TC, TW, L>, grid, block, 0, st,                      \
-        qkv, S, (size_t)split_stride, (const TW *)q_w, (const TW *)k_w, eps, cs, sn, rot_half, \
-        row_pos, row_seq, block_table, bt_stride, (TC *)q_out, (TC *)k_cache, (TC *)v_cache, n, \
-        nh, nkv)
+    do {                                                                                       \
+        if (by_row)                                                                            \
+            launch(qk_norm_rope_append_row_kernel<TC, TW, L>, (unsigned)n, block, 0, st,       \
+                qkv, S, (size_t)split_stride, (const TW *)q_w, (const TW *)k_w, eps, cs, sn,   \
+                rot_half, row_pos, row_seq, block_table, bt_stride, (TC *)q_out,               \
+                (TC *)k_cache, (TC *)v_cache, n, nh, nkv);                                     \
+        else                                                                                   \
+            launch(qk_norm_rope_append_vec_kernel<TC, TW, L>, grid, block, 0, st,              \
+                qkv, S, (size_t)split_stride, (const TW *)q_w, (const TW *)k_w, eps, cs, sn,   \
+                rot_half, row_pos, row_seq, block_table, bt_stride, (TC *)q_out,               \
+                (TC *)k_cache, (TC *)v_cache, n, nh, nkv);                                     \
+    } while (0)
 #define JB_ROPE_VL(TC, TW)                                                                     \
     do {                                                                                       \
         if (hd == 32)                                                                          \

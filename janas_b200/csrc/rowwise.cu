@@ -103,54 +103,90 @@ __global__ void rmsnorm_kernel(float *__restrict__ x, const float *__restrict__ 
 // block, four values per lane and load.  Its sums run in another order than
 // rmsnorm_kernel's, so it serves the bfloat16 path only (the 32-bit path keeps one
 // order for every batch); dm must be a multiple of 4.
-template <typename TW>
+template <typename TW, int WPR>
 __global__ void __launch_bounds__(256)
 rmsnorm_rows_kernel(float *__restrict__ x, const float *__restrict__ delta, int S,
                     size_t delta_stride, const TW *__restrict__ w, bf16 *__restrict__ out,
                     int n, int dm, float eps)
 {
+    // What keeps the memory busy is how much is in flight: WPR warps share a row
+    // (more of them when there are fewer rows), and each lane fetches B values of the
+    // row and B of every partial sum at a time.
+    constexpr int B = 4, STEP = 32 * WPR;
+    __shared__ float red[8];
     pdl_trigger();
     pdl_wait();
-    int lane = threadIdx.x & 31;
-    size_t row = (size_t)blockIdx.x * 8 + (threadIdx.x >> 5);
-    if (row >= (size_t)n)
+    int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    size_t row = (size_t)blockIdx.x * (8 / WPR) + warp / WPR;
+    bool live = row < (size_t)n;
+    if (WPR == 1 && !live)
         return;
-    float4 *xr = reinterpret_cast<float4 *>(x + row * dm);
-    int nv = dm / 4;
+    if (!live)
+        row = (size_t)n - 1;                       // reads only; it stores nothing
+    float *xr = x + row * dm;
+    const float *dr = delta ? delta + row * dm : nullptr;
+    int nv = dm / 4, first = (warp % WPR) * 32 + lane;
     float ss = 0.0f;
-    for (int i = lane; i < nv; i += 32) {
-        float4 v = xr[i];
-        if (delta) {
-            const float *d = delta + row * dm + 4 * i;
-            for (int s0 = 0; s0 < S; s0 += 4) {      // four partial sums are fetched together
-                float4 t[4];
+    for (int i0 = first; i0 < nv; i0 += STEP * B) {
+        float4 v[B];
 #pragma unroll
-                for (int b = 0; b < 4; b++)
-                    if (s0 + b < S)
-                        t[b] = load4(d + (size_t)(s0 + b) * delta_stride);
+        for (int b = 0; b < B; b++)
+            v[b] = i0 + STEP * b < nv ? load4(xr + 4 * (i0 + STEP * b))
+                                      : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (dr) {
+            for (int s = 0; s < S; s++) {
+                const float *d = dr + (size_t)s * delta_stride;
+                float4 t[B];
 #pragma unroll
-                for (int b = 0; b < 4; b++)
-                    if (s0 + b < S) {
-                        v.x += t[b].x; v.y += t[b].y; v.z += t[b].z; v.w += t[b].w;
-                    }
+                for (int b = 0; b < B; b++)
+                    t[b] = i0 + STEP * b < nv ? load4(d + 4 * (i0 + STEP * b))
+                                              : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+                for (int b = 0; b < B; b++) {
+                    v[b].x += t[b].x; v[b].y += t[b].y; v[b].z += t[b].z; v[b].w += t[b].w;
+                }
             }
-            xr[i] = v;
+#pragma unroll
+            for (int b = 0; b < B; b++)
+                if (live && i0 + STEP * b < nv)
+                    store4(xr + 4 * (i0 + STEP * b), v[b]);
         }
-        ss = fmaf(v.x, v.x, ss);
-        ss = fmaf(v.y, v.y, ss);
-        ss = fmaf(v.z, v.z, ss);
-        ss = fmaf(v.w, v.w, ss);
+#pragma unroll
+        for (int b = 0; b < B; b++) {
+            ss = fmaf(v[b].x, v[b].x, ss);
+            ss = fmaf(v[b].y, v[b].y, ss);
+            ss = fmaf(v[b].z, v[b].z, ss);
+            ss = fmaf(v[b].w, v[b].w, ss);
+        }
     }
     ss = warp_sum(ss);
+    if (WPR > 1) {
+        if (lane == 0)
+            red[warp] = ss;
+        __syncthreads();
+        ss = 0.0f;
+#pragma unroll
+        for (int u = 0; u < WPR; u++)
+            ss += red[warp / WPR * WPR + u];
+        if (!live)
+            return;
+    }
     float scale = 1.0f / sqrtf(ss / (float)dm + eps);
-    uint2 *o = reinterpret_cast<uint2 *>(out + row * dm);
-    for (int i = lane; i < nv; i += 32) {
-        float4 v = xr[i];                       // this lane wrote it: a cache hit
-        float w0 = to_f(w[4 * i]), w1 = to_f(w[4 * i + 1]), w2 = to_f(w[4 * i + 2]),
-              w3 = to_f(w[4 * i + 3]);
-        __nv_bfloat162 lo = __floats2bfloat162_rn((v.x * scale) * w0, (v.y * scale) * w1);
-        __nv_bfloat162 hi = __floats2bfloat162_rn((v.z * scale) * w2, (v.w * scale) * w3);
-        o[i] = make_uint2(*reinterpret_cast<uint32_t *>(&lo), *reinterpret_cast<uint32_t *>(&hi));
+    bf16 *o = out + row * dm;
+    for (int i0 = first; i0 < nv; i0 += STEP * B) {
+        float4 v[B], wv[B];
+#pragma unroll
+        for (int b = 0; b < B; b++) {
+            int c = i0 + STEP * b < nv ? 4 * (i0 + STEP * b) : 0;
+            v[b] = load4(xr + c);                   // this lane wrote it: a cache hit
+            wv[b] = load4(w + c);
+        }
+#pragma unroll
+        for (int b = 0; b < B; b++)
+            if (i0 + STEP * b < nv)
+                store4(o + 4 * (i0 + STEP * b),
+                       make_float4((v[b].x * scale) * wv[b].x, (v[b].y * scale) * wv[b].y,
+                                   (v[b].z * scale) * wv[b].z, (v[b].w * scale) * wv[b].w));
     }
 }
 
@@ -351,16 +387,32 @@ extern "C" int jb_rmsnorm(float *x, const float *delta, int S, long long delta_s
     // many rows of the bfloat16 path: the kernel that takes eight rows a block
     if (out != nullptr && out_dt == JB_BF16 && row_idx == nullptr && n_out >= 256 && dm % 4 == 0 &&
         (uintptr_t)x % 16 == 0 && (uintptr_t)delta % 16 == 0 && (uintptr_t)out % 8 == 0 &&
+        (uintptr_t)w % (w_dt == JB_F32 ? 16 : 8) == 0 &&
         (delta == nullptr || delta_stride % 4 == 0)) {
-        unsigned blocks = (unsigned)((n_out + 7) / 8);
+        // enough warps to keep every SM's memory pipeline full: four per row below
+        // 4,096 rows, two below 8,192, else one
+        int wpr = n_out < 4096 ? 4 : n_out < 8192 ? 2 : 1;
+        unsigned blocks = (unsigned)((n_out + 8 / wpr - 1) / (8 / wpr));
+#define JB_NORM_R(TW, W)                                                                      \
+    launch(rmsnorm_rows_kernel<TW, W>, blocks, 256, 0, st, x, delta, S, (size_t)delta_stride,  \
+           (const TW *)w, (bf16 *)out, n_out, dm, eps)
+#define JB_NORM_RW(TW)                                                                        \
+    do {                                                                                       \
+        if (wpr == 4)                                                                          \
+            JB_NORM_R(TW, 4);                                                                  \
+        else if (wpr == 2)                                                                     \
+            JB_NORM_R(TW, 2);                                                                  \
+        else                                                                                   \
+            JB_NORM_R(TW, 1);                                                                  \
+    } while (0)
         if (w_dt == JB_F32)
-            launch(rmsnorm_rows_kernel<float>, blocks, 256, 0, st, x, delta, S,
-                   (size_t)delta_stride, (const float *)w, (bf16 *)out, n_out, dm, eps);
+            JB_NORM_RW(float);
         else if (w_dt == JB_BF16)
-            launch(rmsnorm_rows_kernel<bf16>, blocks, 256, 0, st, x, delta, S,
-                   (size_t)delta_stride, (const bf16 *)w, (bf16 *)out, n_out, dm, eps);
+            JB_NORM_RW(bf16);
         else
             return JB_EINVAL;
+#undef JB_NORM_R
+#undef JB_NORM_RW
         return launch_status();
     }
     // few rows of the bfloat16 path: a cluster of eight CTAs per row (measured: faster

@@ -196,10 +196,13 @@ def test_attention_finds_a_far_key_and_the_window_s_edge(dtype):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("n0,n1,hd,nh,nkv", [(25, 15, 48, 6, 2), (300, 58, 128, 6, 2), (3, 1, 16, 6, 2),
                                              (40, 9, 32, 5, 1), (17, 30, 64, 9, 3),
-                                             (9, 11, 256, 3, 3), (6, 3, 80, 4, 2)])
+                                             (9, 11, 256, 3, 3), (6, 3, 80, 4, 2),
+                                             (260, 20, 32, 5, 1), (250, 30, 64, 9, 3),
+                                             (270, 10, 256, 3, 3), (310, 64, 128, 32, 8)])
 def test_qk_norm_rope_append(dtype, n0, n1, hd, nh, nkv):
-    """The kernel for any even head size (48, 16, 80) and the 16-byte one for head
-    sizes 32, 64, 128 and 256, with head counts that leave a warp partly empty."""
+    """The kernel for any even head size (48, 16, 80) and the 16-byte ones for head
+    sizes 32, 64, 128 and 256 (a block per row from 256 rows on), with head counts
+    that leave a warp partly empty."""
     n = n0 + n1
     width = (nh + 2 * nkv) * hd
     qkv = rnd(2, n, width, scale=2.0)
@@ -238,6 +241,33 @@ def test_qk_norm_rope_append(dtype, n0, n1, hd, nh, nkv):
         written[bt[seq[r], pos[r] // 64], pos[r] % 64] = True
     kc, vc = kc.permute(0, 2, 1, 3), vc.permute(0, 2, 1, 3)      # [page, position, head, value]
     assert float(kc[~written].abs().sum()) == 0.0 and float(vc[~written].abs().sum()) == 0.0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hd,nh,nkv", [(128, 6, 2), (32, 5, 1), (64, 9, 3), (256, 3, 3)])
+def test_qk_norm_rope_append_same_bits_for_few_and_many_rows(dtype, hd, nh, nkv):
+    """From 256 rows on another kernel runs; a row's values must be the same bits
+    whether it comes among 300 rows or among 100."""
+    n = 300
+    qkv = rnd(3, n, (nh + 2 * nkv) * hd, scale=2.0).to(DEV)
+    qw, kw = (1 + 0.1 * rnd(hd)).to(dtype).to(DEV), (1 + 0.1 * rnd(hd, seed=1)).to(dtype).to(DEV)
+    pos = torch.arange(5, 5 + n).int().to(DEV)
+    seq = torch.zeros(n).int().to(DEV)
+    bt = torch.tensor([[4, 2, 0, 3, 5, 7, -1, -1]], dtype=torch.int32).to(DEV)
+    half = hd // 2
+    expo = np.float32(-2.0) * np.arange(half, dtype=np.float32) / np.float32(hd)
+    inv = np.power(np.float64(np.float32(1e4)), expo.astype(np.float64)).astype(np.float32)
+    cs, sn = ops().rope_table(torch.from_numpy(inv).to(DEV), 512)
+    res = []
+    for cuts in ([(0, n)], [(0, 100), (100, 200), (200, n)]):
+        kc = torch.zeros(8, nkv, 64, hd, dtype=dtype, device=DEV)
+        vc = torch.zeros_like(kc)
+        q = torch.cat([ops().qk_norm_rope_append(qkv[:, a:b].contiguous(), qw, kw, 1e-6, cs, sn,
+                                                 pos[a:b].contiguous(), seq[a:b].contiguous(), bt,
+                                                 kc, vc, nh, nkv, hd, dtype) for a, b in cuts])
+        res.append((q, kc, vc))
+    for a, b in zip(res[0], res[1]):
+        assert torch.equal(a, b)
 
 
 def test_argmax_is_the_first_maximum():
