@@ -74,7 +74,7 @@ template <int BN, int MT> struct TileCfg {
     static constexpr int A_TILE_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = MT * W_TILE_BYTES + A_TILE_BYTES;
     // 2 CTAs per SM for the small tiles that stream weights, 1 for the large ones
-    static constexpr int RING_BYTES = (BN <= 64 && MT == 1) ? 100 * 1024 : 196 * 1024;
+    static constexpr int RING_BYTES = (BN <= 64 && MT == 1) ? 100 * 1024 : 225 * 1024;
     static constexpr int STAGES = RING_BYTES / STAGE_BYTES < 2 ? 2 : (RING_BYTES / STAGE_BYTES > 8 ? 8 : RING_BYTES / STAGE_BYTES);
     static constexpr int TMEM_COLS = MT * BN <= 32 ? 32 : MT * BN <= 64 ? 64 : MT * BN <= 128 ? 128 : MT * BN <= 256 ? 256 : 512;
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment */ + 256 /* barriers */;
@@ -471,6 +471,10 @@ static int many_tokens_tile(int n, int m, int k, int splits, double *time_us = n
         long tiles = m_tiles * ((n + bn - 1) / bn) * splits;
         long rounds = (tiles + sms - 1) / sms;
         double mma = 0.55 * bn / 256.0, load = (32768.0 + bn * 128.0) / 116000.0;
+        // tiles above 192 tokens have room for three stages only, two of them in
+        // flight: measured, a block of k then takes a fifth longer than its bytes do
+        if (bn > 192)
+            load *= 1.2;
         double t = rounds * (8.0 + kbps * (mma > load ? mma : load)) +
                    (splits - 1) * (double)n * m * 8.0 / 5e6;
         if (t < best_t * 0.98) {
