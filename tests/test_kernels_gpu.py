@@ -84,6 +84,32 @@ def test_rmsnorm_few_rows(wdt, n, dm, S):
     assert (got - want).abs().max() <= 2 ** -8 * want.abs().max()
 
 
+@pytest.mark.parametrize("wdt", DTYPES)
+@pytest.mark.parametrize("n,dm,S", [(257, 2560, 1), (1001, 516, 3), (4097, 260, 2), (5003, 1000, 1),
+                                    (8193, 132, 1), (9001, 260, 2)])
+def test_rmsnorm_many_rows(wdt, n, dm, S):
+    """Many rows with bfloat16 output: four, two or one warp per row by the number
+    of rows, row counts that leave a block's last rows empty, widths that leave
+    lanes without values.  One value of each row is large, so that a warp's share
+    missing from the row's sum would show."""
+    x = rnd(n, dm, scale=3.0)
+    x[:, dm - 3] = 200.0
+    x[:, 1] = -150.0
+    w = (1 + 0.1 * rnd(dm)).to(wdt)
+    delta = rnd(S, n, dm, seed=1)
+    xd = x.to(DEV).clone()
+    got = ops().rmsnorm(xd, w.to(DEV), 1e-5, torch.bfloat16, delta=delta.to(DEV)).cpu().float()
+    x2 = x.clone()
+    for s in range(S):
+        x2 = x2 + delta[s]
+    assert torch.equal(xd.cpu(), x2)
+    want = plain.rms_norm(x2, w.float(), 1e-5)
+    assert ((got - want).abs().max(dim=1).values <= 2 ** -8 * want.abs().max(dim=1).values).all()
+    got = ops().rmsnorm(x.to(DEV), w.to(DEV), 1e-5, torch.bfloat16).cpu().float()
+    want = plain.rms_norm(x, w.float(), 1e-5)
+    assert ((got - want).abs().max(dim=1).values <= 2 ** -8 * want.abs().max(dim=1).values).all()
+
+
 @pytest.mark.parametrize("odt", DTYPES)
 def test_swiglu(odt):
     n, ff = 7, 300
