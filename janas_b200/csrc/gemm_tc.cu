@@ -40,6 +40,10 @@ constexpr int TILE_M = 128;         // features per MMA
 constexpr int W_TILE_BYTES = TILE_M * BK * 2;
 constexpr int EPI_PARTIAL = 0;      // store float partial sums
 constexpr int EPI_SWIGLU = 1;       // two tiles: gate and up; store SiLU(gate) * up as bfloat16
+// one tile whose rows are 64 gate features and the 64 up features that pair with
+// them: as many CTAs as the plain product has, for the few tokens of a decode step
+constexpr int EPI_SWIGLU_HALF = 2;
+constexpr int HALF_M = TILE_M / 2;
 // warp 0 loads, warp 1 issues the MMAs, warps 2..9 read the accumulator back: a
 // warp may read the 32 TMEM lanes of its index modulo 4, so two warps share each
 // quarter of the features and take the 32-column groups in turn
@@ -187,6 +191,48 @@ __device__ __forceinline__ void store_swiglu(uint32_t taddr, int hgrp, bf16 *__r
     }
 }
 
+// The same for a tile whose TMEM lanes [0, 64) are gate features and [64, 128) the
+// up features of the same indices: the warps of the upper lanes hand their values
+// to the lower ones through shared memory (xch, 64 rows of BN + 1 floats: the ring's
+// first stage, which nothing reads any more).  All eight epilogue warps meet at the
+// barrier, whether their wait for the accumulator ran out or not.
+template <int BN>
+__device__ __forceinline__ void store_swiglu_half(uint32_t taddr, int q, int lane, int hgrp,
+                                                  bool ok, float *xch,
+                                                  bf16 *__restrict__ out_act, int m0, int ff,
+                                                  int n0, int n)
+{
+    constexpr int LD = BN + 1;
+    float v[16];
+    if (ok && q >= 2) {
+        float *row = xch + ((q - 2) * 32 + lane) * LD;
+        for (int c = 16 * hgrp; c < BN; c += 32) {
+            tc_ld16(taddr + c, v);
+#pragma unroll
+            for (int j = 0; j < 16; j++)
+                row[c + j] = v[j];
+        }
+    }
+    named_barrier(1, GEMM_THREADS - 64);
+    if (ok && q < 2) {
+        int j0 = q * 32 + lane, f = m0 + j0;
+        const float *row = xch + j0 * LD;
+        for (int c = 16 * hgrp; c < BN; c += 32) {
+            tc_ld16(taddr + c, v);
+            if (f < ff) {
+                bf16 *p = out_act + (size_t)(n0 + c) * ff + f;
+#pragma unroll
+                for (int j = 0; j < 16; j++, p += ff)
+                    if (n0 + c + j < n) {
+                        float gv = v[j], uv = row[c + j];
+                        float e = fast_exp2(gv * -1.4426950408889634f);
+                        *p = __float2bfloat16_rn(__fdividef(gv * uv, 1.0f + e));
+                    }
+            }
+        }
+    }
+}
+
 template <int BN, int MT, int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
@@ -210,7 +256,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     // token tiles vary fastest: the CTAs that run at the same time share weight
     // tiles, which then come from memory once, and the (small) activations come
     // from the L2
-    int m0 = blockIdx.y * (EPI == EPI_SWIGLU ? TILE_M : TILE_M * MT);
+    int m0 = blockIdx.y * (EPI == EPI_SWIGLU ? TILE_M : EPI == EPI_SWIGLU_HALF ? HALF_M
+                                                                                : TILE_M * MT);
     int n0 = blockIdx.x * BN;
     int total_kb = (k + BK - 1) / BK;
     int kb0 = blockIdx.z * kb_per_split;
@@ -244,15 +291,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         // stages are on their way before that kernel has finished.  The
         // activations do: they are loaded after the dependency wait.
         uint32_t armed = 0, last_parity = 0;
+        // a stage's weight tiles: MT boxes of 128 rows, or (EPI_SWIGLU_HALF) two boxes
+        // of 64 rows, the gate's and the up projection's, that make one tile
+        auto load_w = [&](uint32_t dst, uint32_t bar, int kx) {
+            if (EPI == EPI_SWIGLU_HALF) {
+                tma_load_2d(dst, &map_w, bar, kx, m0);
+                tma_load_2d(dst + W_TILE_BYTES / 2, &map_w, bar, kx, m0 + second_off);
+            } else {
+#pragma unroll
+                for (int t = 0; t < MT; t++)
+                    tma_load_2d(dst + t * W_TILE_BYTES, &map_w, bar, kx, m0 + t * second_off);
+            }
+        };
         int pre = min(nkb, STAGES);
         for (int i = 0; i < pre; i++) {
             uint32_t dst = smem_u32(smem + i * Cfg::STAGE_BYTES);
             uint32_t bar = full0 + 8 * i;
             mbar_expect_tx(bar, Cfg::STAGE_BYTES);
-#pragma unroll
-            for (int t = 0; t < MT; t++)
-                tma_load_2d(dst + t * W_TILE_BYTES, &map_w, bar, (kb0 + i) * BK,
-                            m0 + t * second_off);
+            load_w(dst, bar, (kb0 + i) * BK);
             armed |= 1u << i;
         }
         pdl_wait();
@@ -268,9 +324,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             uint32_t bar = full0 + 8 * s;
             mbar_expect_tx(bar, Cfg::STAGE_BYTES);
             int kx = (kb0 + i) * BK;
-#pragma unroll
-            for (int t = 0; t < MT; t++)
-                tma_load_2d(dst + t * W_TILE_BYTES, &map_w, bar, kx, m0 + t * second_off);
+            load_w(dst, bar, kx);
             tma_load_2d(dst + MT * W_TILE_BYTES, &map_a, bar, kx, n0);
             armed |= 1u << s;
             last_parity = (last_parity & ~(1u << s)) | (ph << s);
@@ -317,7 +371,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         // The accumulator is read 32 columns (tokens) at a time; the read of the
         // next 32 is in flight while the last 32 are stored.
         int hgrp = (warp - 2) >> 2;             // which of the two warps of this quarter
-        if (ok) {
+        if (EPI == EPI_SWIGLU_HALF) {
+            if constexpr (MT == 1 && BN <= 64)
+                store_swiglu_half<BN>(taddr, q, lane, hgrp, ok, (float *)smem, out_act, m0,
+                                      second_off, n0, n);
+        } else if (ok) {
             if (EPI == EPI_PARTIAL)
                 store_partial<BN, MT>(taddr, hgrp, out + (size_t)blockIdx.z * n * m, f, n0, n, m,
                                       second_off);
@@ -388,7 +446,8 @@ static int launch_tc(const void *A, const void *W, float *out, bf16 *out_act, in
 {
     using Cfg = TileCfg<BN, MT>;
     CUtensorMap map_w, map_a;
-    if (!tensor_map(W, w_rows, k, TILE_M, &map_w) || !tensor_map(A, n, k, BN, &map_a))
+    if (!tensor_map(W, w_rows, k, EPI == EPI_SWIGLU_HALF ? HALF_M : TILE_M, &map_w) ||
+        !tensor_map(A, n, k, BN, &map_a))
         return JB_EINVAL;
     auto kern = gemm_tc_kernel<BN, MT, EPI>;
     static unsigned long long smem_allowed = 0;
@@ -398,8 +457,8 @@ static int launch_tc(const void *A, const void *W, float *out, bf16 *out_act, in
     int kbps = (total_kb + splits - 1) / splits;
     if ((splits - 1) * kbps >= total_kb)
         return JB_EINVAL;   // a part without work
-    int feats = EPI == EPI_SWIGLU ? second_off : m;
-    int tile_feats = EPI == EPI_SWIGLU ? TILE_M : TILE_M * MT;
+    int feats = EPI == EPI_PARTIAL ? m : second_off;
+    int tile_feats = EPI == EPI_SWIGLU ? TILE_M : EPI == EPI_SWIGLU_HALF ? HALF_M : TILE_M * MT;
     dim3 grid((n + BN - 1) / BN, (feats + tile_feats - 1) / tile_feats, splits);
     if (grid.y > 65535 || grid.z > 65535)
         return JB_EINVAL;
@@ -553,6 +612,16 @@ extern "C" int jb_gemm_tc_swiglu(const void *A, const void *W, void *out_act, in
         }
 #undef JB_SWIGLU
     }
+    // few tokens: as many CTAs as the plain product has (64 gate and 64 up features each)
+#define JB_SWIGLU_HALF(B)                                                                      \
+    launch_tc<B, 1, EPI_SWIGLU_HALF>(A, W, nullptr, (bf16 *)out_act, n, 2 * ff, k, 2 * ff, ff, 1, st)
+    if (n <= 16)
+        return JB_SWIGLU_HALF(16);
+    if (n <= 32)
+        return JB_SWIGLU_HALF(32);
+    if (n <= 64)
+        return JB_SWIGLU_HALF(64);
+#undef JB_SWIGLU_HALF
     return launch_tc<128, 2, EPI_SWIGLU>(A, W, nullptr, (bf16 *)out_act, n, 2 * ff, k, 2 * ff, ff,
                                          1, st);
 }

@@ -409,6 +409,12 @@ def linear_swiglu(a: torch.Tensor, gate_up: torch.Tensor) -> Optional[torch.Tens
     return out
 
 
+def linear_parts(n: int, m: int, k: int) -> int:
+    """Into how many parts of k the tensor-core product of n rows with a weight
+    [m, k] is cut when the caller leaves it open (see ``linear``)."""
+    return int(lib().jb_gemm_tc_splits(n, m, k))
+
+
 def gemm_tc_error() -> int:
     """0, or which bounded wait of a tensor-core product ran out since the last
     call (the product's output is then not valid).  Synchronizes the device."""

@@ -24,6 +24,10 @@ class SwiGLU(FeedForward):
     # microseconds at 2,048 rows, 103 against 109 at 1,024, even at 512; with few rows
     # the one kernel cannot cut k into parts and loses (29 against 20 at 8 rows).
     FUSED_FROM = 512
+    # Rows up to which the one kernel runs too, in tiles of 64 gate and 64 up
+    # features, if the plain product would not cut k either (a wide feed-forward:
+    # the tiles alone fill the SMs).  It saves the activation kernel of a decode step.
+    FUSED_UP_TO = 64
 
     def __init__(self, spec, dtype, device):
         super().__init__(spec, dtype, device)
@@ -48,9 +52,12 @@ class SwiGLU(FeedForward):
 
     def forward(self, ctx: StepContext, h: torch.Tensor) -> torch.Tensor:
         act = None
-        if ctx.n_rows >= self.FUSED_FROM and ctx.dtype == torch.bfloat16:
-            # enough rows to fill the SMs without cutting k: gate, up and the
-            # activation in one kernel
+        if ctx.dtype == torch.bfloat16 and (
+                ctx.n_rows >= self.FUSED_FROM or
+                (ctx.n_rows <= self.FUSED_UP_TO and
+                 ops.linear_parts(ctx.n_rows, 2 * self.inter, self.hidden) == 1)):
+            # enough rows, or enough features, to fill the SMs without cutting k:
+            # gate, up and the activation in one kernel
             act = ops.linear_swiglu(h, self.w_gate_up)
         if act is None:
             act = ops.swiglu(product(h, self.w_gate_up), ctx.dtype)

@@ -386,11 +386,15 @@ def test_gemm_tensor_core_finds_one_large_product():
     assert torch.equal(got, want)
 
 
-@pytest.mark.parametrize("n,ff,k", [(5, 100, 64), (128, 224, 96), (129, 136, 80), (600, 300, 2560)])
+@pytest.mark.parametrize("n,ff,k", [(5, 100, 64), (128, 224, 96), (129, 136, 80), (600, 300, 2560),
+                                    (1, 64, 64), (16, 136, 80), (17, 200, 256), (33, 72, 1000),
+                                    (64, 1000, 2560), (8, 1984, 512), (65, 100, 128)])
 def test_gemm_tensor_core_swiglu(n, ff, k):
+    """Up to 64 rows in tiles of 64 gate and 64 up features, above in tiles of 128
+    and 128; feature counts that leave the last tile partly empty."""
     a = rnd(n, k, dtype=torch.bfloat16)
     w = rnd(2 * ff, k, dtype=torch.bfloat16, seed=5, scale=0.3)
-    a[1] *= 60.0                          # gates of a few hundred, of both signs
+    a[n - 1] *= 60.0                      # gates of a few hundred, of both signs
     got = ops().linear_swiglu(a.to(DEV), w.to(DEV))
     assert ops().gemm_tc_error() == 0
     gu = a.double() @ w.double().T

@@ -80,24 +80,28 @@ def test_swiglu_part():
     assert (got - want).abs().max() <= 3e-6 * want.abs().max()
 
 
-@pytest.mark.parametrize("rows", [40, 700])
-def test_swiglu_part_bfloat16(rows, monkeypatch):
-    """Few rows: product, then the activation kernel; many rows: gate, up and the
-    activation in one tensor-core kernel.  Both against the plain feed-forward
-    with the activation rounded to bfloat16."""
+@pytest.mark.parametrize("rows,hidden,inter", [(40, 72, 200), (100, 72, 200), (700, 72, 200),
+                                               (8, 1024, 136)])
+def test_swiglu_part_bfloat16(rows, hidden, inter, monkeypatch):
+    """Many rows, or few rows whose product would not be cut along k: gate, up and
+    the activation in one tensor-core kernel; else the product, then the activation
+    kernel.  All against the plain feed-forward with the activation rounded to
+    bfloat16."""
     from janas_b200.config import PartSpec
     from janas_b200.csrc import ops
     fused_calls = []
     real = ops.linear_swiglu
     monkeypatch.setattr(ops, "linear_swiglu", lambda a, w: fused_calls.append(1) or real(a, w))
-    ffn = build("feed_forward", PartSpec("swiglu", {"hidden_size": 72, "intermediate_size": 200}),
-                torch.bfloat16)
+    ffn = build("feed_forward", PartSpec("swiglu", {"hidden_size": hidden,
+                                                    "intermediate_size": inter}), torch.bfloat16)
     w = give(ffn, "mlp", seed=3, dtype=torch.bfloat16)
-    h = torch.randn(rows, 72).bfloat16()
+    h = torch.randn(rows, hidden).bfloat16()
     h[3] *= 40.0                          # gates far from zero on both sides
     got = ffn.forward(context([0], [rows], torch.bfloat16), h.to(DEV)).sum(0).cpu()
     assert ops.gemm_tc_error() == 0
-    assert bool(fused_calls) == (rows >= ffn.FUSED_FROM)
+    uncut = ops.linear_parts(rows, 2 * inter, hidden) == 1
+    assert bool(fused_calls) == (rows >= ffn.FUSED_FROM or (rows <= ffn.FUSED_UP_TO and uncut))
+    assert uncut == (hidden == 72)          # the cases cover both
     want = plain.swiglu(h.float(), w, "mlp.", "bfloat16")
     err = (got - want).abs().max(dim=1).values                    # row by row: row 3 is large
     assert bool((err <= 2 ** -7 * want.abs().max(dim=1).values).all())
