@@ -153,25 +153,41 @@ def fill(eng, batch, context, rng):
     return slots, rng.integers(0, vocab, size=batch).tolist()
 
 
+def drive(eng, slots, tokens, n):
+    """n decode steps of the same sequences, one step ahead where the engine allows
+    it; every step's tokens are read on the host.  Returns the last ones."""
+    if n <= 0:
+        return tokens
+    if not getattr(eng, "decodes_ahead", False):
+        for _ in range(n):
+            tokens = eng.decode(slots, tokens).tolist()
+        return tokens
+    cur = eng.decode_begin(slots, tokens)
+    for i in range(n):
+        nxt = eng.decode_begin(slots, None) if i + 1 < n else None
+        tokens = eng.decode_end(cur).tolist()
+        cur = nxt
+    return tokens
+
+
 def decode_device_timed(eng, slots, tokens, steps, warmup):
     """K decode steps of the whole batch (the engine's decode step: the step
     function's kernels and the choice of the next token, replayed from a CUDA
-    graph), timed on the device; the chosen tokens are read back every step."""
+    graph), timed on the device.  The steps are driven as the generation loop
+    drives them: each step's inputs are copied from pinned host memory, its chosen
+    tokens are read back on the host every step, and where the engine can feed a
+    step the tokens of the step before it, the next step is queued while this one
+    runs."""
     import torch
     from janas_b200.csrc import ops
-    from janas_b200.engine import StepEntry
 
-    def one(tokens):
-        return eng.decode(slots, tokens).tolist()
-
-    for _ in range(warmup):
-        tokens = one(tokens)
+    run = lambda n, tokens: drive(eng, slots, tokens, n)
+    tokens = run(warmup, tokens)
     torch.cuda.synchronize()
     l0 = ops.COUNTERS["launches"]
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     a.record()
-    for _ in range(steps):
-        tokens = one(tokens)
+    tokens = run(steps, tokens)
     b.record()
     torch.cuda.synchronize()
     return a.elapsed_time(b) / steps, ops.COUNTERS["launches"] - l0, tokens
@@ -185,12 +201,10 @@ def decode_timeline(eng, slots, tokens, warmup):
     cost on the step's critical path is the last column, not its duration."""
     import torch
     from torch.profiler import ProfilerActivity, profile
-    for _ in range(warmup + 2):
-        tokens = eng.decode(slots, tokens).tolist()
+    tokens = drive(eng, slots, tokens, warmup + 2)
     torch.cuda.synchronize()
     with profile(activities=[ProfilerActivity.CUDA]) as prof:
-        for _ in range(3):
-            tokens = eng.decode(slots, tokens).tolist()
+        tokens = drive(eng, slots, tokens, 3)
         torch.cuda.synchronize()
     evs = [e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA]
     evs.sort(key=lambda e: e.time_range.start)

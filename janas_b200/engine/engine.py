@@ -82,6 +82,7 @@ class Engine:
         self._graph_pool = None
         self._capture_stream = None
         self._sampler_scratch = None
+        self._last_decode = None     # (graph, slots) of the decode step begun last
         # run-order entry -> (group, index within the group) of the cache it uses
         self._cache_entry: List[Optional[int]] = []
         for e, entry in enumerate(model.spec.run_order):
@@ -111,6 +112,8 @@ class Engine:
 
     def free_sequence(self, slot: int) -> None:
         self.cache.free_sequence(slot)
+        if self._last_decode is not None and slot in self._last_decode[1]:
+            self._last_decode = None    # no step can go on from that step's tokens any more
 
     def length(self, slot: int) -> int:
         return int(self.cache.length[slot])
@@ -220,13 +223,35 @@ class Engine:
         host.  The step's kernels are the step function's; when every mixer allows
         it they are replayed from a CUDA graph captured for this batch size and
         context bound, else they are launched one by one."""
-        from ..csrc import ops
-        entries = [StepEntry(s, [int(t)], [0]) for s, t in zip(slots, tokens)]
+        return self.decode_end(self.decode_begin(slots, tokens, sampled, big))
+
+    @property
+    def decodes_ahead(self) -> bool:
+        """Whether ``decode_begin`` takes ``tokens=None``: the step is then fed the
+        tokens that the step before it chose, which never leave the device, so it
+        can be launched while that step still runs."""
+        return self.use_graphs
+
+    def decode_begin(self, slots: Sequence[int], tokens: Optional[Sequence[int]],
+                     sampled: bool = False, big=None) -> "PendingDecode":
+        """Launches a decode step and returns at once; ``decode_end`` waits for it
+        and gives the chosen tokens.  With ``tokens=None`` the sequences go on from
+        the tokens chosen by the step begun last, which must have had the same
+        slots in the same order.  Steps end in the order in which they began, and
+        at most two may be under way."""
+        slots = list(slots)
+        if tokens is None:
+            if not self.use_graphs or self._last_decode is None or self._last_decode[1] != slots:
+                raise StepError("a step can go on from the device's own tokens only right "
+                                "after a decode step of the same sequences")
+            feed = [0] * len(slots)
+        else:
+            feed = [int(t) for t in tokens]
+        entries = [StepEntry(s, [t], [0]) for s, t in zip(slots, feed)]
         if not self.use_graphs:
             logits = self.step(entries)
-            return self._sample(logits, list(slots), sampled, big)
+            return PendingDecode(None, 0, self._sample(logits, slots, sampled, big))
         kind, toks, pos0, lens = self.plan(entries)
-        slots = list(slots)
         self.cache.reserve(slots, lens.tolist())
         # launch sizes are fixed for positions below ``bound``: a new graph every
         # 256 positions keeps them close to what the step needs
@@ -239,13 +264,21 @@ class Engine:
         if g is None:
             g = DecodeGraph(self, len(slots), bound, bool(sampled), key[3])
             while len(self._graphs) >= max(self.max_graphs, 1):
+                # a step of the graph that goes may still be under way
+                torch.cuda.current_stream(self.device).synchronize()
                 del self._graphs[next(iter(self._graphs))]
             if not self._graphs:
                 self._graph_pool = None     # a pool ends with its last graph: take a new one
         self._graphs[key] = g
-        out = g.run(slots, toks, pos0)
+        before = self._last_decode[0] if tokens is None else None
+        pending = g.begin(slots, None if tokens is None else toks, pos0, before)
+        self._last_decode = (g, slots)
         self.cache.advance(slots, lens.tolist())
-        return out
+        return pending
+
+    def decode_end(self, pending: "PendingDecode") -> np.ndarray:
+        """Waits for a step begun with ``decode_begin``; its chosen tokens."""
+        return pending.result()
 
     def sampler_scratch(self, rows: int):
         """Room for every logit of ``rows`` rows as a sort key and as a probability:
@@ -274,15 +307,34 @@ class Engine:
         return toks.cpu().numpy()
 
 
+class PendingDecode:
+    """A decode step under way: ``result()`` waits for it and gives its tokens."""
+
+    def __init__(self, event, n: int, tokens=None):
+        self.event, self.n, self.tokens = event, n, tokens
+        self.out_host = None
+
+    def result(self) -> np.ndarray:
+        if self.tokens is None:
+            self.event.synchronize()
+            self.tokens = self.out_host.numpy()[:self.n].copy()
+        return self.tokens
+
+
 class DecodeGraph:
     """The decode step of ``batch`` sequences at positions below ``bound``,
     captured once and replayed.
 
     All that changes from step to step (tokens, positions, slots, block tables)
-    lies in one pinned host buffer that the graph copies to the device first; the
-    chosen tokens come back through another pinned buffer.  Launch sizes that
-    depend on the context (the attention's chunk count) are fixed at ``bound``;
-    rows whose range is shorter leave those chunks at once."""
+    lies in a pinned host buffer that is copied to the device before the graph
+    runs; the chosen tokens are written where the next step's tokens are read, so
+    a step that goes on from them needs nothing from the host but positions and
+    block tables, and can be launched while the step before it runs.  There are
+    two pinned buffers each way, used in turn: with at most two steps under way,
+    the host never writes what a copy still reads, nor reads what a later step
+    may already have written.  Launch sizes that depend on the context (the
+    attention's chunk count) are fixed at ``bound``; rows whose range is shorter
+    leave those chunks at once."""
 
     def __init__(self, engine: "Engine", batch: int, bound: int, sampled: bool,
                  long_way: bool = False):
@@ -292,17 +344,17 @@ class DecodeGraph:
         self.width = (pages_for(bound) + 7) // 8 * 8
         n_groups = len(engine.cache.groups)
         total = 4 * batch + n_groups * batch * self.width
-        self.host = torch.zeros(total, dtype=torch.int32).pin_memory()
-        self.host_np = self.host.numpy()
+        self.host = [torch.zeros(total, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self.out_host = [torch.zeros(batch, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self.events = [torch.cuda.Event() for _ in range(2)]
+        self.pending: List[Optional[PendingDecode]] = [None, None]
+        self.turn = 0
         self.dev = torch.zeros(total, dtype=torch.int32, device=engine.device)
-        self.out_dev = torch.zeros(batch, dtype=torch.int32, device=engine.device)
-        self.out_host = torch.zeros(batch, dtype=torch.int32).pin_memory()
         self.graph: Optional[torch.cuda.CUDAGraph] = None
 
     def _launch(self) -> None:
         from ..csrc import ops
         eng, B = self.engine, self.batch
-        self.dev.copy_(self.host, non_blocking=True)
         v = lambda i: self.dev[i * B:(i + 1) * B]
         bt = {}
         for gi, g in enumerate(eng.cache.groups):
@@ -313,19 +365,31 @@ class DecodeGraph:
                           seq_pos0=None, seq_len=None, seq_row0=None, max_pos=self.bound - 1)
         logits = eng.model.forward(ctx, v(0), eng._layer_caches(bt), None)
         c = eng.cache
+        # the chosen tokens take the place of the tokens the step was fed
         if self.sampled:
             big = eng.sampler_scratch(B) if self.long_way else (None, None)
-            ops.sample(logits, out=self.out_dev, row_slot=v(3), temperature=c.temperature,
+            ops.sample(logits, out=v(0), row_slot=v(3), temperature=c.temperature,
                        top_k=c.top_k, top_p=c.top_p, min_p=c.min_p, rng=c.rng,
                        big_keys=big[0], big_probs=big[1])
         else:
-            ops.sample(logits, out=self.out_dev)
-        self.out_host.copy_(self.out_dev, non_blocking=True)
+            ops.sample(logits, out=v(0))
 
-    def run(self, slots: List[int], tokens: np.ndarray, pos0: np.ndarray) -> np.ndarray:
+    def begin(self, slots: List[int], tokens: Optional[np.ndarray], pos0: np.ndarray,
+              before: Optional["DecodeGraph"]) -> PendingDecode:
+        """Copies the step's inputs, runs the step and copies its tokens back,
+        all on the current stream, without waiting.  ``tokens`` None: the step is
+        fed what the step begun last chose (``before`` is its graph)."""
         eng, B = self.engine, self.batch
-        h = self.host_np
-        h[0:B] = tokens
+        turn = self.turn
+        self.turn = 1 - turn
+        # the buffers of this turn were last used two steps ago: that step has to be
+        # over, and its tokens taken, before they are written again
+        if self.pending[turn] is not None:
+            self.pending[turn].result()
+        host = self.host[turn]
+        h = host.numpy()
+        if tokens is not None:
+            h[0:B] = tokens
         h[B:2 * B] = pos0
         h[2 * B:3 * B] = np.arange(B, dtype=np.int32)
         h[3 * B:4 * B] = slots
@@ -336,26 +400,35 @@ class DecodeGraph:
             for i, s in enumerate(slots):
                 pg = g.pages[s]
                 tab[i, :len(pg)] = pg
-        eng.h2d_bytes += self.host.numel() * 4
+        from ..csrc import ops
         with torch.cuda.device(eng.device):
+            if tokens is not None:
+                self.dev.copy_(host, non_blocking=True)
+                eng.h2d_bytes += host.numel() * 4
+            else:
+                if before is not self:
+                    self.dev[:B].copy_(before.dev[:B], non_blocking=True)
+                self.dev[B:].copy_(host[B:], non_blocking=True)
+                eng.h2d_bytes += (host.numel() - B) * 4
             if self.graph is None:
                 # the first step runs eagerly (it sizes every scratch buffer and is a
                 # real step); the capture that follows records without running
                 self._launch()
+                self.out_host[turn].copy_(self.dev[:B], non_blocking=True)
+                self.events[turn].record()
                 torch.cuda.current_stream().synchronize()
-                out = self.out_host.numpy().copy()
                 graph = torch.cuda.CUDAGraph()
                 if eng._graph_pool is None:
                     eng._graph_pool = torch.cuda.graph_pool_handle()
                 if eng._capture_stream is None:
                     eng._capture_stream = torch.cuda.Stream(eng.device)
-                from ..csrc import ops
-                before = ops.COUNTERS["launches"]
+                before_n = ops.COUNTERS["launches"]
                 # capture_begin/capture_end on a stream of the engine's own, not the
                 # torch.cuda.graph context: that one collects garbage and empties the
                 # allocator's cache first, which gives the last prefill's blocks back
                 # to the driver (0.3 s and more after a long prompt, and the next
-                # prefill pays for getting them again)
+                # prefill pays for getting them again).  The capture records the
+                # kernels without running them, so the tokens just chosen stay.
                 side = eng._capture_stream
                 side.wait_stream(torch.cuda.current_stream())
                 with torch.cuda.stream(side):
@@ -365,12 +438,15 @@ class DecodeGraph:
                     finally:
                         graph.capture_end()
                 torch.cuda.current_stream().wait_stream(side)
-                self.kernels = ops.COUNTERS["launches"] - before   # kernels per replay
-                ops.COUNTERS["launches"] = before
+                self.kernels = ops.COUNTERS["launches"] - before_n   # kernels per replay
+                ops.COUNTERS["launches"] = before_n
                 self.graph = graph
-                return out
-            self.graph.replay()
-            from ..csrc import ops
-            ops.COUNTERS["launches"] += self.kernels
-            torch.cuda.current_stream().synchronize()
-        return self.out_host.numpy().copy()
+            else:
+                self.graph.replay()
+                ops.COUNTERS["launches"] += self.kernels
+                self.out_host[turn].copy_(self.dev[:B], non_blocking=True)
+                self.events[turn].record()
+        pending = PendingDecode(self.events[turn], B)
+        pending.out_host = self.out_host[turn]
+        self.pending[turn] = pending
+        return pending

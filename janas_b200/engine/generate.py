@@ -133,6 +133,15 @@ def finish_reason(token: int, n_generated: int, max_new: int, length: int, max_p
     return None
 
 
+def goes_on_unless_stopped(n_generated: int, max_new: int, length: int, max_positions: int
+                           ) -> bool:
+    """Whether a sequence goes on after its ``n_generated``-th new token if that is
+    no stop token (``finish_reason`` with the token left open): the next step may
+    then be launched before the token is known.  ``length`` is what the cache
+    holds of the sequence before that token is fed."""
+    return n_generated < max_new and length + 1 <= max_positions
+
+
 # ----------------------------------------------------------------------- loop
 def generate(engine, requests: Sequence[Request], max_batch: int = 64,
              stats: Optional[GenStats] = None) -> List[Result]:
@@ -190,26 +199,65 @@ def generate(engine, requests: Sequence[Request], max_batch: int = 64,
             now = time.perf_counter()
             st.prefill_seconds += now - t0
             active = list(live)
+            # Decode steps are launched one ahead where the engine can feed a step
+            # the tokens of the step before it on the device: while step t runs,
+            # step t + 1 is already queued behind it, and the host reads t's tokens
+            # meanwhile.  That is done only when every sequence is sure to go on
+            # unless it draws a stop token; one that does has run one step too many,
+            # which changes nothing for the others, and the loop then takes the
+            # remaining sequences' tokens from that step before it goes on.
+            ahead_ok = bool(getattr(engine, "decodes_ahead", False))
+            ahead = None            # the step under way beyond ``toks``, and its rows
+            ahead_rows: List[int] = []
             while True:
                 st.forced_tokens += forced
+                forced = 0
                 nxt, feed = [], []
                 for i, tok in zip(active, toks):
                     out[i].append(int(tok))
                     st.new_tokens += 1
-                    why = finish_reason(int(tok), len(out[i]), requests[i].max_new,
-                                        engine.length(slots[i]), engine.max_positions, stops[i])
+                    held = engine.length(slots[i]) - (1 if ahead is not None else 0)
+                    why = finish_reason(int(tok), len(out[i]), requests[i].max_new, held,
+                                        engine.max_positions, stops[i])
                     if why is None:
                         nxt.append(i)
                         feed.append(int(tok))
                     else:
                         results[i] = Result(out[i], why)
                         engine.free_sequence(slots.pop(i))
+                ended = len(nxt) != len(active)
                 active = nxt
+                t0 = time.perf_counter()
+                if ahead is not None and (ended or not active):
+                    # the step under way ran with sequences that have ended: the
+                    # others' tokens are good
+                    got = engine.decode_end(ahead)
+                    st.passes += 1
+                    st.d2h_bytes += 4 * len(ahead_rows)
+                    st.decode_seconds += time.perf_counter() - t0
+                    toks = [got[ahead_rows.index(i)] for i in active]
+                    ahead = None
+                    if not active:
+                        break
+                    continue
                 if not active:
                     break
-                t0 = time.perf_counter()
                 h2d0 = getattr(engine, "h2d_bytes", 0)
-                toks, forced = _decode(engine, [slots[i] for i in active], feed, sampled, big)
+                cur_slots = [slots[i] for i in active]
+                if ahead is not None:
+                    cur, ahead = ahead, None
+                elif ahead_ok:
+                    cur = engine.decode_begin(cur_slots, feed, sampled, big)
+                else:
+                    cur = None
+                    toks, forced = _decode(engine, cur_slots, feed, sampled, big)
+                if cur is not None:
+                    if all(goes_on_unless_stopped(len(out[i]) + 1, requests[i].max_new,
+                                                  engine.length(slots[i]), engine.max_positions)
+                           for i in active):
+                        ahead = engine.decode_begin(cur_slots, None, sampled, big)
+                        ahead_rows = list(active)
+                    toks = engine.decode_end(cur)
                 st.passes += 1
                 st.decode_seconds += time.perf_counter() - t0
                 st.h2d_bytes += getattr(engine, "h2d_bytes", 0) - h2d0

@@ -126,3 +126,70 @@ def test_loop_refuses_bad_requests(monkeypatch):
     with pytest.raises(ValueError, match="context"):
         run(monkeypatch, eng, [Request([1] * 41, 3)])
     assert eng.pool.n_free == 3
+
+
+class AheadEngine(FakeEngine):
+    """A stand-in that also takes steps fed by the step before them, as the real
+    engine does from its device buffer; it checks the rules of that way."""
+    decodes_ahead = True
+
+    def __init__(self, *a, **kw):
+        super().__init__(*a, **kw)
+        self.last = None            # (slots, tokens) of the step begun last
+        self.under_way = 0
+        self.begun = []             # (slots, fed by the host?)
+
+    def free_sequence(self, s):
+        super().free_sequence(s)
+        if self.last is not None and s in self.last[0]:
+            self.last = None
+
+    def decode_begin(self, slots, tokens, sampled=False, big=None):
+        assert self.under_way < 2
+        if tokens is None:
+            assert self.last is not None and self.last[0] == list(slots)
+            tokens = self.last[1]
+        self.begun.append((list(slots), self.last is None or tokens is not self.last[1]))
+        out = []
+        for s, t in zip(slots, tokens):
+            assert self.pool.live(s)
+            assert self.len[s] + 1 <= self.max_positions
+            self.len[s] += 1
+            out.append((t + 1) % 50)
+        self.last = (list(slots), out)
+        self.under_way += 1
+        return out
+
+    def decode_end(self, pending):
+        self.under_way -= 1
+        return np.asarray(pending)
+
+
+def test_goes_on_unless_stopped_is_finish_reason_with_the_token_left_open():
+    for n in range(1, 6):
+        for max_new in range(1, 6):
+            for length in range(36, 42):
+                want = G.finish_reason(7, n, max_new, length, 40, frozenset()) is None
+                assert G.goes_on_unless_stopped(n, max_new, length, 40) == want
+
+
+def test_loop_one_step_ahead_gives_the_same_results(monkeypatch):
+    """With an engine that can feed a step the tokens of the step before it, the
+    loop launches one step ahead; results, reasons and counts are those of the
+    step-by-step loop, and only a stop token costs a step that was not needed."""
+    reqs = [Request([1, 2, 3], 5), Request([10], 3, GenOptions(eos=12)),
+            Request([20, 21], 0), Request([30] * 38, 10), Request([5], 2, GenOptions(stop=[6])),
+            Request([7], 9, GenOptions(stop=[11])), Request([8, 9], 9)]
+    plain_eng, eng = FakeEngine(), AheadEngine()
+    st0, st = G.GenStats(), G.GenStats()
+    want = run(monkeypatch, plain_eng, reqs, max_batch=3, stats=st0)
+    res = run(monkeypatch, eng, reqs, max_batch=3, stats=st)
+    assert [(r.tokens, r.finish) for r in res] == [(r.tokens, r.finish) for r in want]
+    assert eng.pool.n_free == 3 and not eng.len and eng.under_way == 0
+    assert (st.new_tokens, st.batches, st.prompt_tokens) == \
+        (st0.new_tokens, st0.batches, st0.prompt_tokens)
+    # request 5, the last of its batch by then, draws its stop token while the step
+    # after it is under way: that one step was not needed.  Where others go on, a
+    # stopped sequence costs a row of a step that runs anyway.
+    assert st.passes == len(eng.begun) == st0.passes + 1
+    assert any(not from_host for _, from_host in eng.begun)      # steps were fed on the device

@@ -208,3 +208,55 @@ def test_old_decode_graphs_are_dropped_and_captured_again():
     third, _ = m.generate_batch(ps, news)       # the first shapes were dropped meanwhile
     assert third == first
     m.engine.cache.check()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_steps_fed_on_the_device_equal_steps_fed_by_the_host(dtype):
+    """A decode step that goes on from the tokens the step before it chose, launched
+    while that step runs, chooses what a step fed from the host chooses: greedy
+    and sampled, across a page's end and across the context bound at which another
+    captured graph takes over (position 256)."""
+    import janas_b200
+    from janas_b200.engine import Engine, StepEntry
+    from janas_b200.engine.engine import StepError
+    from janas_b200.engine.generate import GenOptions
+    rng = np.random.default_rng(41)
+    v = TINY["C"]["vocab_size"]
+    ps = [tokens(rng, n, v) for n in (250, 61, 5)]
+    runs = {}
+    for way in ("host", "device"):
+        for sampled in (False, True):
+            eng = Engine.open(model_dir("C"), dtype=dtype, max_tokens=1024, max_seqs=4)
+            assert eng.decodes_ahead
+            slots = [eng.new_sequence() for _ in ps]
+            if sampled:
+                eng.cache.set_samplers(slots, [GenOptions(temperature=0.8, top_k=20, seed=3 + i)
+                                               for i in range(len(ps))])
+            logits = eng.step([StepEntry(s, p, [len(p) - 1]) for s, p in zip(slots, ps)])
+            toks = logits.argmax(dim=1).cpu().tolist()
+            got = []
+            if way == "host":
+                for _ in range(12):
+                    toks = eng.decode(slots, toks, sampled).tolist()
+                    got.append(toks)
+            else:
+                cur = eng.decode_begin(slots, toks, sampled)
+                for i in range(12):
+                    nxt = eng.decode_begin(slots, None, sampled) if i < 11 else None
+                    got.append(eng.decode_end(cur).tolist())
+                    cur = nxt
+                assert len(eng._graphs) == 2        # positions below 256, then from 256 on
+                with pytest.raises(StepError):      # other sequences than the last step's
+                    eng.decode_begin(slots[:2], None, sampled)
+                eng.free_sequence(slots[2])
+                with pytest.raises(StepError):      # one of them has ended
+                    eng.decode_begin(slots, None, sampled)
+                slots = slots[:2]
+            assert [eng.length(s) for s in slots] == [len(p) + 12 for p in ps[:len(slots)]]
+            runs[way, sampled] = got
+            for s in slots:
+                eng.free_sequence(s)
+            eng.cache.check()
+    assert runs["device", False] == runs["host", False]
+    assert runs["device", True] == runs["host", True]
+    assert runs["host", True] != runs["host", False]
