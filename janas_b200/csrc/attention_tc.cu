@@ -719,6 +719,27 @@ constexpr int DQ_UNITS = 3;
 constexpr int DQ_UNIT = 2 * BLK_BYTES;       // K (or V) of one chunk, 128 values each
 constexpr int DQ_SMEM = 2 * DQ_BLK + 4 * DQ_BLK + DQ_UNITS * DQ_UNIT + 1024 + 1024;
 
+// What the kernel needs to make q, and the new position's key and value, itself
+// from the q,k,v product's partial sums (qkv != nullptr): then no kernel stands
+// between that product and the attention.  Row r of qkv holds the heads of q, then
+// of k, then of v, as float sums to be added in the order 0 .. S-1.
+struct DecodeQkv {
+    const float *qkv;            // nullptr: q is read through map_q and the cache is complete
+    int S;
+    long long split_stride;
+    const void *q_w, *k_w;       // per-head RMSNorm weights of HD values, or nullptr
+    int w_f32;                   // the weights are float (else bfloat16)
+    float eps;
+    const float *cs, *sn;        // rotation tables [positions][HD / 2], or nullptr
+    bf16 *k_cache, *v_cache;     // where the new key and value go, or nullptr (a layer that
+                                 // reads another layer's cache)
+};
+
+__device__ __forceinline__ float4 load_w4(const void *w, int w_f32, int at)
+{
+    return w_f32 ? load4((const float *)w + at) : load4((const bf16 *)w + at);
+}
+
 // GP: the group's heads rounded up to a power of two (the row threads' loops).
 template <int GP>
 __global__ void __launch_bounds__(192)
@@ -728,7 +749,7 @@ attn_tc_decode_kernel(const __grid_constant__ CUtensorMap map_q,
                       const int32_t *__restrict__ row_pos, const int32_t *__restrict__ row_seq,
                       const int32_t *__restrict__ block_table, int bt_stride,
                       float *__restrict__ part, int nh, int nkv, int G, int window, float scale,
-                      int max_chunks, int chunks_per_cta, int row0)
+                      int max_chunks, int chunks_per_cta, int row0, const DecodeQkv f)
 {
     constexpr int HD = 128;
     extern __shared__ uint8_t smem_raw[];
@@ -738,8 +759,8 @@ attn_tc_decode_kernel(const __grid_constant__ CUtensorMap map_q,
     uint8_t *kv_s = p_s + 4 * DQ_BLK;
     uint64_t *bars = (uint64_t *)(kv_s + DQ_UNITS * DQ_UNIT);
     // bars: 0 q_full | 1..3 unit full | 4..6 unit free | 7,8 s_full | 9,10 p_full | 11 o_full |
-    //       12 pv_free
-    uint32_t *tmem_slot = (uint32_t *)(bars + 13);
+    //       12 pv_free | 13 the new key and value are in the cache
+    uint32_t *tmem_slot = (uint32_t *)(bars + 14);
     volatile int *abort = (volatile int *)(tmem_slot + 1);
     float *red_m = (float *)(tmem_slot + 4);   // [4 warps][16 heads]
     float *red_l = red_m + 4 * DQ_N;
@@ -767,8 +788,11 @@ attn_tc_decode_kernel(const __grid_constant__ CUtensorMap map_q,
 
     uint32_t bar0 = smem_u32(bars);
     auto bar = [&](int i) { return bar0 + 8 * i; };
+    const bool fused = f.qkv != nullptr;
+    // this CTA's run holds the chunk of the new position: it appends the key and value
+    const bool appends = fused && f.k_cache != nullptr && c_last == q_pos / AT_KEYS;
     if (threadIdx.x == 0) {
-        mbar_init(bar(0), 1);
+        mbar_init(bar(0), fused ? AT_ROWS : 1);
         for (int s = 0; s < DQ_UNITS; s++) {
             mbar_init(bar(1 + s), 1);
             mbar_init(bar(4 + s), 1);
@@ -779,6 +803,7 @@ attn_tc_decode_kernel(const __grid_constant__ CUtensorMap map_q,
         }
         mbar_init(bar(11), 1);
         mbar_init(bar(12), AT_ROWS);
+        mbar_init(bar(13), AT_ROWS);
         *abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -798,21 +823,125 @@ attn_tc_decode_kernel(const __grid_constant__ CUtensorMap map_q,
     // thread that loads fetches those without waiting for that kernel
     pdl_trigger();
     bool loader = warp == 0 && lane == 0;
+    // The row threads make q (and the new key and value) themselves when the product's
+    // sums are given: sixteen lanes share a head, each with four values of its low half
+    // and the four that pair with them in the high half, a warp two heads at a time
+    // (the arrangement and the order of every sum are those of rope.cu's kernel for
+    // few rows, so the two give the same bits).  Rotation and norm weights were
+    // written long before the kernel before this one: fetched before the wait.
+    const int at4 = 4 * (lane & 15);
+    float4 co = make_float4(1.0f, 1.0f, 1.0f, 1.0f), si = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    float4 wql = co, wqh = co, wkl = co, wkh = co;
+    int new_page = 0;
+    if (fused && warp >= 2) {
+        if (f.cs != nullptr) {
+            co = load4(f.cs + (size_t)q_pos * (HD / 2) + at4);
+            si = load4(f.sn + (size_t)q_pos * (HD / 2) + at4);
+        }
+        if (f.q_w != nullptr) {
+            wql = load_w4(f.q_w, f.w_f32, at4);
+            wqh = load_w4(f.q_w, f.w_f32, HD / 2 + at4);
+            wkl = load_w4(f.k_w, f.w_f32, at4);
+            wkh = load_w4(f.k_w, f.w_f32, HD / 2 + at4);
+        }
+        if (appends)
+            new_page = block_table[(size_t)seq * bt_stride + q_pos / PAGE];
+    }
     // The other lanes of the loader's warp do not wait either (they touch no memory):
     // a wait in one branch of a warp holds the whole warp, the loader with it.
     if (warp != 0)
         pdl_wait();
+
+    if (fused && warp >= 2) {
+        int n_slots = G + (appends ? 2 : 0);        // q heads, then the key, then the value
+        int all_slots = nh + 2 * nkv;
+        const float *src_row = f.qkv + (size_t)q_row * all_slots * HD;
+        for (int base = 0; base < n_slots; base += 8) {
+            int slot = base + (warp - 2) * 2 + (lane >> 4);
+            bool live = slot < n_slots;
+            bool is_q = slot < G, is_v = slot == G + 1;
+            int hs = is_q ? kvh * G + slot : is_v ? nh + nkv + kvh : nh + kvh;
+            float4 lo = make_float4(0.0f, 0.0f, 0.0f, 0.0f), hi = lo;
+            if (live) {
+                const float *src = src_row + (size_t)hs * HD + at4;
+                for (int s0 = 0; s0 < f.S; s0 += 4) {
+                    float4 a[4], b[4];
+#pragma unroll
+                    for (int u = 0; u < 4; u++)
+                        if (s0 + u < f.S) {
+                            a[u] = load4(src + (size_t)(s0 + u) * f.split_stride);
+                            b[u] = load4(src + (size_t)(s0 + u) * f.split_stride + HD / 2);
+                        }
+#pragma unroll
+                    for (int u = 0; u < 4; u++)
+                        if (s0 + u < f.S) {
+                            lo.x += a[u].x; lo.y += a[u].y; lo.z += a[u].z; lo.w += a[u].w;
+                            hi.x += b[u].x; hi.y += b[u].y; hi.z += b[u].z; hi.w += b[u].w;
+                        }
+                }
+            }
+            float ss = lo.x * lo.x;
+            ss = fmaf(lo.y, lo.y, ss); ss = fmaf(lo.z, lo.z, ss); ss = fmaf(lo.w, lo.w, ss);
+            ss = fmaf(hi.x, hi.x, ss); ss = fmaf(hi.y, hi.y, ss);
+            ss = fmaf(hi.z, hi.z, ss); ss = fmaf(hi.w, hi.w, ss);
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1)
+                ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            if (!live)
+                continue;
+            if (!is_v && f.q_w != nullptr) {
+                float4 wl = is_q ? wql : wkl, wh = is_q ? wqh : wkh;
+                float sc = 1.0f / sqrtf(ss / (float)HD + f.eps);
+                lo.x = (lo.x * sc) * wl.x; lo.y = (lo.y * sc) * wl.y;
+                lo.z = (lo.z * sc) * wl.z; lo.w = (lo.w * sc) * wl.w;
+                hi.x = (hi.x * sc) * wh.x; hi.y = (hi.y * sc) * wh.y;
+                hi.z = (hi.z * sc) * wh.z; hi.w = (hi.w * sc) * wh.w;
+            }
+            if (!is_v && f.cs != nullptr) {
+                float4 a = lo, b = hi;
+                lo = make_float4(a.x * co.x - b.x * si.x, a.y * co.y - b.y * si.y,
+                                 a.z * co.z - b.z * si.z, a.w * co.w - b.w * si.w);
+                hi = make_float4(a.x * si.x + b.x * co.x, a.y * si.y + b.y * co.y,
+                                 a.z * si.z + b.z * co.z, a.w * si.w + b.w * co.w);
+            }
+            if (is_q) {
+                // where the TMA load would have put it: block of the half, row of the
+                // head, 16-byte chunk at4 / 8 of the row in the 128-byte swizzle
+                uint8_t *at = q_s + swz(slot, at4 / 8) + (at4 % 8) * 2;
+                store4(reinterpret_cast<bf16 *>(at), lo);
+                store4(reinterpret_cast<bf16 *>(at + DQ_BLK), hi);
+            } else {
+                bf16 *dst = (is_v ? f.v_cache : f.k_cache) +
+                            (((size_t)new_page * nkv + kvh) * PAGE + (q_pos % PAGE)) * HD;
+                store4(dst + at4, lo);
+                store4(dst + HD / 2 + at4, hi);
+            }
+        }
+        fence_async_smem();              // q is read by the tensor core
+        tc_fence_before();
+        mbar_arrive(bar(0));
+        if (appends) {
+            // the key and value are read back by TMA: written, made visible to that
+            // proxy, then the loader is told
+            __threadfence();
+            asm volatile("fence.proxy.async;" ::: "memory");
+            mbar_arrive(bar(13));
+        }
+    }
 
     if (loader) {
         // ---------------------------------------------------------- TMA loads
         bool waited = false;
         auto wait_and_load_q = [&]() {
             pdl_wait();
-            mbar_expect_tx(bar(0), (uint32_t)(G * HD * 2));
-            tma_load_3d(smem_u32(q_s), &map_q, bar(0), 0, kvh * G, q_row);
-            tma_load_3d(smem_u32(q_s + DQ_BLK), &map_q, bar(0), 64, kvh * G, q_row);
+            if (!fused) {
+                mbar_expect_tx(bar(0), (uint32_t)(G * HD * 2));
+                tma_load_3d(smem_u32(q_s), &map_q, bar(0), 0, kvh * G, q_row);
+                tma_load_3d(smem_u32(q_s + DQ_BLK), &map_q, bar(0), 64, kvh * G, q_row);
+            }
             waited = true;
         };
+        bool appended = !appends;
         const int32_t *bt = block_table + (size_t)seq * bt_stride;
         uint32_t armed = 0, last_parity = 0;
         for (int u = 0; u < 2 * n_chunks; u++) {        // unit u: K (even) or V (odd) of chunk u / 2
@@ -820,6 +949,13 @@ attn_tc_decode_kernel(const __grid_constant__ CUtensorMap map_q,
             uint32_t ph = (u / DQ_UNITS) & 1;
             if (!waited && (u >= DQ_UNITS || c_first + u / 2 >= q_pos / AT_KEYS))
                 wait_and_load_q();
+            if (!appended && c_first + u / 2 >= q_pos / AT_KEYS) {
+                // the chunk of the new position: its key and value come from this CTA's
+                // row threads
+                if (!mbar_wait(bar(13), 0, abort, err, 20))
+                    break;
+                appended = true;
+            }
             if (!mbar_wait(bar(4 + s), ph ^ 1, abort, err, 11))
                 break;
             mbar_expect_tx(bar(1 + s), DQ_UNIT);
@@ -1151,20 +1287,26 @@ extern "C" int jb_attn_tc_prefill(const void *q, const void *k_cache, const void
 
 // Decode rows row0 .. row0 + n_rows - 1 (one token each): writes the per-chunk
 // partials of attention.cu's layout into `part`; jb_attention_merge joins them.
-extern "C" int jb_attn_tc_decode(const void *q, const void *k_cache, const void *v_cache,
-                                 long long n_pages, const int32_t *row_pos, const int32_t *row_seq,
-                                 const int32_t *block_table, int bt_stride, float *part, int n,
-                                 int row0, int n_rows, int nh, int nkv, int hd, int window,
-                                 float scale, int max_chunks, int chunks_per_cta, cudaStream_t st)
+static int attn_tc_decode(const void *q, const void *k_cache, const void *v_cache,
+                          long long n_pages, const int32_t *row_pos, const int32_t *row_seq,
+                          const int32_t *block_table, int bt_stride, float *part, int n,
+                          int row0, int n_rows, int nh, int nkv, int hd, int window,
+                          float scale, int max_chunks, int chunks_per_cta, const DecodeQkv &f,
+                          cudaStream_t st)
 {
     if (!jb_attn_tc_ok(nh, nkv, hd) || n_rows <= 0 || max_chunks <= 0 || chunks_per_cta <= 0)
+        return JB_EINVAL;
+    if (f.qkv != nullptr && !(hd == 128 && nh / nkv <= DQ_N))
         return JB_EINVAL;
     if (hd == 128 && nh / nkv <= DQ_N) {
         int G = nh / nkv;
         CUtensorMap mq, mk, mv;
-        if (!attn_tensor_map(q, hd, nh, n, G, 1, &mq) ||
-            !attn_tensor_map(k_cache, hd, n_pages * nkv * PAGE, 0, PAGE, 0, &mk) ||
+        if (!attn_tensor_map(k_cache, hd, n_pages * nkv * PAGE, 0, PAGE, 0, &mk) ||
             !attn_tensor_map(v_cache, hd, n_pages * nkv * PAGE, 0, PAGE, 0, &mv))
+            return JB_EINVAL;
+        if (f.qkv != nullptr)
+            mq = mk;            // not used: the kernel makes q itself
+        else if (!attn_tensor_map(q, hd, nh, n, G, 1, &mq))
             return JB_EINVAL;
         unsigned gx = (unsigned)n_rows * ((max_chunks + chunks_per_cta - 1) / chunks_per_cta);
 #define JB_DQ(GP)                                                                              \
@@ -1174,7 +1316,7 @@ extern "C" int jb_attn_tc_decode(const void *q, const void *k_cache, const void 
             return JB_ELAUNCH;                                                                 \
         launch(attn_tc_decode_kernel<GP>, dim3(gx, nkv), 192, DQ_SMEM, st,                     \
                mq, mk, mv, row_pos, row_seq, block_table, bt_stride, part, nh, nkv, G, window, \
-               scale, max_chunks, chunks_per_cta, row0);                                       \
+               scale, max_chunks, chunks_per_cta, row0, f);                                    \
     } while (0)
         if (G <= 1)
             JB_DQ(1);
@@ -1196,6 +1338,49 @@ extern "C" int jb_attn_tc_decode(const void *q, const void *k_cache, const void 
     return launch_attn_rows<64>(q, k_cache, v_cache, n_pages, row_pos, row_seq, block_table,
                                 bt_stride, part, n, nh, nkv, window, scale, max_chunks,
                                 chunks_per_cta, row0, n_rows, st);
+}
+
+extern "C" int jb_attn_tc_decode(const void *q, const void *k_cache, const void *v_cache,
+                                 long long n_pages, const int32_t *row_pos, const int32_t *row_seq,
+                                 const int32_t *block_table, int bt_stride, float *part, int n,
+                                 int row0, int n_rows, int nh, int nkv, int hd, int window,
+                                 float scale, int max_chunks, int chunks_per_cta, cudaStream_t st)
+{
+    DecodeQkv f = {};
+    return attn_tc_decode(q, k_cache, v_cache, n_pages, row_pos, row_seq, block_table, bt_stride,
+                          part, n, row0, n_rows, nh, nkv, hd, window, scale, max_chunks,
+                          chunks_per_cta, f, st);
+}
+
+// The same, with q and the new position's key and value made by the attention kernel
+// itself from the q,k,v product's partial sums (see DecodeQkv): per-head RMSNorm with
+// q_w / k_w (or none), rotation by cs / sn at the row's position (or none), key and
+// value written to the row's place in the cache when append is set.  Heads of 128
+// values in groups of up to 16 only (jb_attn_tc_decode_runs); everything 16-byte
+// aligned (8 for bfloat16 weights).
+extern "C" int jb_attn_tc_decode_qkv(const float *qkv, int S, long long split_stride,
+                                     const void *q_w, const void *k_w, int w_dt, float eps,
+                                     const float *cs, const float *sn, void *k_cache,
+                                     void *v_cache, int append, long long n_pages,
+                                     const int32_t *row_pos, const int32_t *row_seq,
+                                     const int32_t *block_table, int bt_stride, float *part, int n,
+                                     int row0, int n_rows, int nh, int nkv, int hd, int window,
+                                     float scale, int max_chunks, int chunks_per_cta,
+                                     cudaStream_t st)
+{
+    auto aligned = [](const void *p, size_t to) { return (uintptr_t)p % to == 0; };
+    if (qkv == nullptr || S <= 0 || split_stride % 4 != 0 || !aligned(qkv, 16) ||
+        (q_w == nullptr) != (k_w == nullptr) || (cs == nullptr) != (sn == nullptr) ||
+        (w_dt != JB_F32 && w_dt != JB_BF16))
+        return JB_EINVAL;
+    size_t w_to = w_dt == JB_F32 ? 16 : 8;
+    if (!aligned(q_w, w_to) || !aligned(k_w, w_to) || !aligned(cs, 16) || !aligned(sn, 16))
+        return JB_EINVAL;
+    DecodeQkv f = {qkv, S, split_stride, q_w, k_w, w_dt == JB_F32, eps, cs, sn,
+                   append ? (bf16 *)k_cache : nullptr, append ? (bf16 *)v_cache : nullptr};
+    return attn_tc_decode(nullptr, k_cache, v_cache, n_pages, row_pos, row_seq, block_table,
+                          bt_stride, part, n, row0, n_rows, nh, nkv, hd, window, scale, max_chunks,
+                          chunks_per_cta, f, st);
 }
 
 // Whether the decode kernel for these sizes runs over several chunks per CTA and

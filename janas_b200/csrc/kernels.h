@@ -53,6 +53,13 @@ int jb_attn_tc_decode(const void *q, const void *k_cache, const void *v_cache, l
                       int bt_stride, float *part, int n, int row0, int n_rows, int nh, int nkv,
                       int hd, int window, float scale, int max_chunks, int chunks_per_cta,
                       cudaStream_t st);
+int jb_attn_tc_decode_qkv(const float *qkv, int S, long long split_stride, const void *q_w,
+                          const void *k_w, int w_dt, float eps, const float *cs, const float *sn,
+                          void *k_cache, void *v_cache, int append, long long n_pages,
+                          const int32_t *row_pos, const int32_t *row_seq,
+                          const int32_t *block_table, int bt_stride, float *part, int n, int row0,
+                          int n_rows, int nh, int nkv, int hd, int window, float scale,
+                          int max_chunks, int chunks_per_cta, cudaStream_t st);
 int jb_attn_tc_error(void);
 int jb_gemm_simt(const void *A, int a_dt, const void *W, int w_dt, float *out, int n, int m, int k,
                  cudaStream_t st);

@@ -327,6 +327,67 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
     return out
 
 
+def attention_decode_qkv(qkv: torch.Tensor, q_weight: Optional[torch.Tensor],
+                         k_weight: Optional[torch.Tensor], eps: float,
+                         cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
+                         k_cache: torch.Tensor, v_cache: torch.Tensor, append: bool,
+                         row_pos: torch.Tensor, row_seq: torch.Tensor, block_table: torch.Tensor,
+                         window: int, scale: float, max_chunks: int,
+                         num_heads: int) -> Optional[torch.Tensor]:
+    """``qk_norm_rope_append`` and ``attention(decode=True)`` in one kernel: the
+    attention's CTAs make q, and the one that holds the new position's chunk makes
+    that position's key and value and writes them to the cache (``append``), from
+    the q,k,v product's partial sums ``qkv`` [S, n, (heads + 2 kv_heads) 128].
+    Returns the attention's output [n, heads, 128] in bfloat16, or None where the
+    kernel does not take these sizes and types (bfloat16 caches, heads of 128
+    values in groups of at most 16): the caller then goes the two-kernel way."""
+    L = lib()
+    if k_cache.dtype != torch.bfloat16 or k_cache.dim() != 4:
+        return None
+    nkv, hd = k_cache.shape[1], k_cache.shape[3]
+    if not L.jb_attn_tc_decode_runs(num_heads, nkv, hd):
+        return None
+    qkv = stack(qkv)
+    width = (num_heads + 2 * nkv) * hd
+    _need(qkv, "qkv", torch.float32, (None, None, width))
+    S, n, _ = qkv.shape
+    _need(k_cache, "k_cache", torch.bfloat16, (None, nkv, PAGE, hd))
+    _need(v_cache, "v_cache", torch.bfloat16, tuple(k_cache.shape))
+    _need(row_pos, "row_pos", torch.int32, (n,))
+    _need(row_seq, "row_seq", torch.int32, (n,))
+    _need(block_table, "block_table", torch.int32, (None, None))
+    w_dt = 0
+    if q_weight is not None:
+        _need(q_weight, "q_norm weight", _FLOATS, (hd,))
+        _need(k_weight, "k_norm weight", q_weight.dtype, (hd,))
+        w_dt = _DT[q_weight.dtype]
+    if cos is not None:
+        _need(cos, "cos", torch.float32, (None, hd // 2))
+        _need(sin, "sin", torch.float32, tuple(cos.shape))
+    parts = _decode_parts(min(n, 4096) * nkv, max_chunks, 2 * _sm_count(qkv.device))
+    per_cta = (max_chunks + parts - 1) // parts
+    parts = (max_chunks + per_cta - 1) // per_cta
+    per_row = int(L.jb_attention_scratch(1, num_heads, hd, parts))
+    rows_per_call = max(1, min(n, (_ATT_SCRATCH_BYTES // 4) // max(per_row, 1)))
+    scratch = _scratch(qkv.device, per_row * rows_per_call)
+    out = torch.empty((n, num_heads, hd), dtype=torch.bfloat16, device=qkv.device)
+    for row0 in range(0, n, rows_per_call):
+        cnt = min(rows_per_call, n - row0)
+        code = L.jb_attn_tc_decode_qkv(
+            _p(qkv), S, ctypes.c_longlong(n * width), _p(q_weight), _p(k_weight), w_dt,
+            ctypes.c_float(eps), _p(cos), _p(sin), _p(k_cache), _p(v_cache), int(bool(append)),
+            ctypes.c_longlong(k_cache.shape[0]), _p(row_pos), _p(row_seq), _p(block_table),
+            block_table.shape[1], _p(scratch), n, row0, cnt, num_heads, nkv, hd, window,
+            ctypes.c_float(scale), max_chunks, per_cta, _stream())
+        if code == -1 and row0 == 0:
+            return None             # an address the kernel's 16-byte loads cannot take
+        _check(code, "attention (tcgen05, decode, from the product's sums)")
+        _check(L.jb_attention_merge(_p(scratch), _p(row_pos), _p(out), _DT[out.dtype], row0, cnt,
+                                    num_heads, hd, window, parts, per_cta, _stream()),
+               "attention merge")
+    return out
+
+
 _SM_COUNT = {}
 
 

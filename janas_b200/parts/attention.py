@@ -103,14 +103,23 @@ class GQAAttention(Mixer):
             raise ValueError(f"position {ctx.max_pos} is beyond the {self.position.n_positions} "
                              f"positions the encoding was prepared for")
         qkv = product(h, self.w_qkv)
+        max_chunks = ctx.max_pos // self.chunk + 1
+        if self.window:
+            max_chunks = min(max_chunks, (self.window - 1) // self.chunk + 2)
+        if ctx.kind == DECODE and ctx.dtype == torch.bfloat16:
+            # one new token per sequence: the attention kernel makes q and the new
+            # key and value from the product's sums itself, where it takes the sizes
+            a = ops.attention_decode_qkv(
+                qkv, self.q_norm, self.k_norm, float(self.qk_eps or 0.0), self.position.cos,
+                self.position.sin, cache.k, cache.v, cache.writes, ctx.row_pos, ctx.row_seq,
+                cache.block_table, self.window, self.scale, max_chunks, self.nh)
+            if a is not None:
+                return product(a.view(ctx.n_rows, self.nh * self.hd), self.w_o)
         q = ops.qk_norm_rope_append(
             qkv, self.q_norm, self.k_norm, float(self.qk_eps or 0.0), self.position.cos,
             self.position.sin, ctx.row_pos, ctx.row_seq, cache.block_table,
             cache.k if cache.writes else None, cache.v if cache.writes else None,
             self.nh, self.nkv, self.hd, ctx.dtype)
-        max_chunks = ctx.max_pos // self.chunk + 1
-        if self.window:
-            max_chunks = min(max_chunks, (self.window - 1) // self.chunk + 2)
         decode = ctx.kind == DECODE
         blocks = None
         if not decode and ctx.dtype == torch.bfloat16 and self.hd in (64, 128):

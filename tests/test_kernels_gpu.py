@@ -493,6 +493,57 @@ def test_attention_tensor_core_decode(nh, nkv, hd, window):
         assert err <= 2 ** -7, (mc, err)
 
 
+@pytest.mark.parametrize("nh,nkv,window,S,normed,rotated,w_dtype", [
+    (32, 8, 0, 6, True, True, torch.bfloat16), (8, 1, 0, 1, True, True, torch.float32),
+    (5, 1, 70, 3, True, False, torch.bfloat16), (64, 4, 300, 2, False, True, torch.bfloat16),
+    (12, 2, 0, 5, False, False, torch.float32)])
+def test_attention_decode_makes_q_and_the_new_key_itself(nh, nkv, window, S, normed, rotated,
+                                                         w_dtype):
+    """The decode kernel that is given the q,k,v product's partial sums makes q and,
+    in the CTA that holds the new position's chunk, that position's key and value,
+    and writes them to the cache: output and caches equal, bit for bit, those of the
+    rope kernel followed by the attention kernel.  New positions at a page's first
+    and last place, at a chunk's first place and alone in the sequence; with and
+    without norm and rotation; a layer that only reads its cache."""
+    o = ops()
+    hd = 128
+    lens = [1, 64, 65, 128, 129, 700, 2050, 333]
+    n = len(lens)
+    ks = [rnd(m, nkv, hd, dtype=torch.bfloat16, seed=9 * i + 1) for i, m in enumerate(lens)]
+    vs = [rnd(m, nkv, hd, dtype=torch.bfloat16, seed=9 * i + 2) for i, m in enumerate(lens)]
+    kc, vc, bt = _paged_many(ks, vs, 70, seed=4)        # the last positions will be overwritten
+    width = (nh + 2 * nkv) * hd
+    qkv = rnd(S, n, width, seed=77, scale=2.0)
+    qw = (1 + 0.2 * rnd(hd, seed=5)).to(w_dtype) if normed else None
+    kw = (1 + 0.2 * rnd(hd, seed=6)).to(w_dtype) if normed else None
+    if rotated:
+        ang = torch.arange(4096)[:, None] * (10000.0 ** (-torch.arange(hd // 2) / (hd // 2)))[None]
+        cos, sin = ang.cos().float().to(DEV), ang.sin().float().to(DEV)
+    else:
+        cos = sin = None
+    row_pos = torch.tensor([m - 1 for m in lens], dtype=torch.int32).to(DEV)
+    row_seq = torch.arange(n, dtype=torch.int32).to(DEV)
+    dev = lambda t: None if t is None else t.to(DEV)
+    chunk = o.attention_chunk()
+    mc = 2049 // chunk + 1
+    if window:
+        mc = min(mc, (window - 1) // chunk + 2)
+    scale = 1 / math.sqrt(hd)
+    for append in (True, False):
+        k1, v1, k2, v2 = kc.to(DEV), vc.to(DEV), kc.to(DEV), vc.to(DEV)
+        q = o.qk_norm_rope_append(qkv.to(DEV), dev(qw), dev(kw), 1e-6, cos, sin, row_pos, row_seq,
+                                  bt.to(DEV), k1 if append else None, v1 if append else None,
+                                  nh, nkv, hd, torch.bfloat16)
+        want = o.attention(q, k1, v1, row_pos, row_seq, bt.to(DEV), window, scale, mc, decode=True)
+        got = o.attention_decode_qkv(qkv.to(DEV), dev(qw), dev(kw), 1e-6, cos, sin, k2, v2, append,
+                                     row_pos, row_seq, bt.to(DEV), window, scale, mc, nh)
+        assert got is not None and o.attn_tc_error() == 0
+        assert torch.equal(k1, k2) and torch.equal(v1, v2)
+        assert torch.equal(k1, kc.to(DEV)) != append        # the key was written, or it was not
+        assert torch.equal(got, want)
+        assert float(want.float().abs().max()) > 0.1
+
+
 def test_attention_tensor_core_prefill_moves_its_reference():
     """The prefill kernel keeps a row's exponent reference until a chunk's maximum
     runs more than 2^8 ahead, then scales the row's output, which lies in tensor
