@@ -2,6 +2,7 @@
 
     llm = janas_b200.open(model_dir, params)           # janas_llm_open
     tokens, stats = llm.generate(prompt, max_new, options)   # janas_llm_generate
+    s = llm.session(options); s.append(prompt); status, token = s.next()   # janas_llm_session_*
     llm.close()                                        # janas_llm_close
 
 Names follow include/janas/llm.h and src/llm/generate.h: ``params_default``
@@ -98,6 +99,58 @@ class LLM:
             raise LLMError(EINVAL, str(e)) from None
         self.last_finish = [r.finish for r in res]
         return [r.tokens for r in res], stats
+
+    # ------------------------------------------------------------- sessions
+    def session(self, options=None) -> "Session":
+        """A sequence of its own on this model, which grows by appended tokens and
+        by tokens generated on request (janas_llm_session_create,
+        src/llm/generate.h:101-103); see ``janas_b200.engine.session``.  As many
+        sessions as ``max_batch`` can be open at one time; ``close`` gives a
+        session's place and cache pages back."""
+        from .cache import CacheFull
+        from .engine.session import Session, SessionError
+        try:
+            return Session(self.engine, options)
+        except (SessionError, ValueError) as e:
+            raise LLMError(EINVAL, str(e)) from None
+        except (CacheFull, RuntimeError) as e:
+            raise LLMError(EFULL, str(e)) from None
+
+    def sessions_step(self, sessions):
+        """Moves several sessions on together in one pass
+        (janas_llm_sessions_step, src/llm/generate.h:155-158): returns
+        (tokens, status), status 0 with a token, 1 when that session's context is
+        full."""
+        from .cache import CacheFull
+        from .engine.session import SessionError, sessions_step
+        try:
+            return sessions_step(self.engine, list(sessions))
+        except SessionError as e:
+            raise LLMError(EINVAL, str(e)) from None
+        except CacheFull as e:
+            raise LLMError(EFULL, str(e)) from None
+
+    # ------------------------------------------------- the step function itself
+    def slot_new(self) -> int:
+        """A place for a sequence in the cache, for callers that drive ``step``
+        themselves."""
+        return self.engine.new_sequence()
+
+    def slot_free(self, slot: int) -> None:
+        self.engine.free_sequence(slot)
+
+    def step(self, entries):
+        """One step of the engine: ``entries`` are (slot, tokens, wanted places);
+        returns the float32 logits [wanted, vocab] on the device, or None."""
+        from .engine import StepEntry, StepError
+        from .cache import CacheFull
+        try:
+            return self.engine.step([e if isinstance(e, StepEntry) else StepEntry(*e)
+                                     for e in entries])
+        except StepError as e:
+            raise LLMError(EINVAL, str(e)) from None
+        except CacheFull as e:
+            raise LLMError(EFULL, str(e)) from None
 
     def close(self) -> None:
         self.engine = None

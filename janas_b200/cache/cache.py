@@ -157,6 +157,44 @@ class Cache:
         self.slots.give_back(slot)
         self.length[slot] = 0
 
+    def can_truncate(self, slot: int, n: int) -> bool:
+        """Whether the sequence can go back to its first ``n`` tokens: always to
+        none; else only if no mixer keeps a state of its own (which has seen
+        everything) and every window group still holds the pages that a token at
+        position ``n`` can see."""
+        if not self.slots.live(slot) or not 0 <= n <= int(self.length[slot]):
+            return False
+        if n == 0 or n == int(self.length[slot]):
+            return True
+        if self.mixer_state:
+            return False
+        for g in self.groups:
+            have = g.pages[slot]
+            if any(have[i] < 0 for i in range(g.first_needed_page(n), pages_for(n))):
+                return False
+        return True
+
+    def truncate(self, slot: int, n: int) -> bool:
+        """Keeps the first ``n`` tokens of the sequence and gives back the pages
+        beyond them (src/llm/generate.h:160-167: janas_llm_session_truncate).
+        False, with nothing changed, where ``can_truncate`` says no."""
+        if not self.can_truncate(slot, n):
+            return False
+        if n == int(self.length[slot]):
+            return True
+        for g in self.groups:
+            have = g.pages[slot]
+            keep = pages_for(n)
+            gone = [p for p in have[keep:] if p >= 0]
+            if gone:
+                g.pool.give_back(gone)
+            del have[keep:]
+        self.length[slot] = n
+        if n == 0:
+            for st in self.mixer_state.values():
+                st[slot].zero_()
+        return True
+
     def set_samplers(self, slots: Sequence[int], options: Sequence) -> None:
         """The sequences' sampling settings (objects with temperature, top_k,
         top_p, min_p and seed); each random sequence starts at its seed

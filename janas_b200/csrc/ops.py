@@ -31,6 +31,44 @@ class KernelError(RuntimeError):
     pass
 
 
+_C_TYPES = {"int": ctypes.c_int, "int32_t": ctypes.c_int32, "unsigned": ctypes.c_uint,
+            "long long": ctypes.c_longlong, "unsigned long long": ctypes.c_ulonglong,
+            "float": ctypes.c_float, "double": ctypes.c_double, "size_t": ctypes.c_size_t,
+            "cudaStream_t": ctypes.c_void_p}
+
+
+def _c_type(decl: str, with_name: bool):
+    """The ctypes type of a parameter (or return type) as kernels.h writes it."""
+    decl = decl.strip()
+    if "*" in decl:
+        return ctypes.c_void_p
+    words = [w for w in decl.split() if w != "const"]     # also folds runs of blanks
+    if with_name:
+        words = words[:-1]
+    return _C_TYPES[" ".join(words)]
+
+
+def declare(library: ctypes.CDLL, header: str) -> int:
+    """Gives every function that ``header`` (the text of kernels.h) declares its
+    argument and return types, so that a call converts plain Python numbers (and
+    None for a null pointer) by the declared type instead of guessing it from each
+    argument: a wrong guess would pass a 64-bit size as 32 bits.  Returns how many
+    functions were declared; one that the header has and the library lacks, or a
+    type the table above does not know, raises."""
+    import re
+    text = re.sub(r"//[^\n]*", "", header)
+    count = 0
+    for ret, name, params in re.findall(
+            r"\b((?:unsigned\s+)?(?:long\s+long|int|float|double))\s+(jb_\w+)\s*\(([^)]*)\)\s*;", text):
+        fn = getattr(library, name)
+        params = params.strip()
+        fn.argtypes = [] if params in ("", "void") else [_c_type(p, True)
+                                                         for p in params.split(",")]
+        fn.restype = _c_type(ret, False)
+        count += 1
+    return count
+
+
 def lib() -> ctypes.CDLL:
     global _lib
     if _lib is None:
@@ -38,11 +76,14 @@ def lib() -> ctypes.CDLL:
             if _lib is None:
                 path = build.library_path()
                 try:
-                    _lib = ctypes.CDLL(path)
+                    loaded = ctypes.CDLL(path)
                 except OSError as e:
                     raise KernelError(f"janas_b200: cannot load {path}: {e}") from None
-                for name in ("jb_attention_scratch", "jb_sample_scratch"):
-                    getattr(_lib, name).restype = ctypes.c_longlong
+                import os
+                with open(os.path.join(os.path.dirname(os.path.abspath(__file__)),
+                                       "kernels.h")) as f:
+                    declare(loaded, f.read())
+                _lib = loaded
     return _lib
 
 
@@ -53,16 +94,17 @@ def loaded_library_path() -> Optional[str]:
 _raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
 
 
-def _stream() -> ctypes.c_void_p:
+def _stream() -> int:
     """The current CUDA stream's handle.  Asked on every launch, so by the short
     way when this PyTorch has it (the Stream object costs several microseconds)."""
     if _raw_stream is not None:
-        return ctypes.c_void_p(_raw_stream(torch.cuda.current_device()))
-    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        return _raw_stream(torch.cuda.current_device())
+    return torch.cuda.current_stream().cuda_stream
 
 
-def _p(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
-    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+def _p(t: Optional[torch.Tensor]) -> Optional[int]:
+    """A tensor's address for a pointer argument (None: a null pointer)."""
+    return None if t is None else t.data_ptr()
 
 
 def _need(t: torch.Tensor, name: str, dtype=None, shape=None) -> None:
@@ -135,9 +177,9 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.
         _need(rows, "rows", torch.int32)
         n_out = rows.numel()
     out = torch.empty((n_out, dm), dtype=out_dtype, device=x.device)
-    _check(lib().jb_rmsnorm(_p(x), _p(delta), S, ctypes.c_longlong(stride), _p(rows),
+    _check(lib().jb_rmsnorm(_p(x), _p(delta), S, int(stride), _p(rows),
                             _p(weight), _DT[weight.dtype], _p(out), _DT[out_dtype], n_out, dm,
-                            ctypes.c_float(eps), _stream()), "rmsnorm")
+                            float(eps), _stream()), "rmsnorm")
     return out
 
 
@@ -147,8 +189,8 @@ def add_(x: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
     n, dm = x.shape
     delta = stack(delta)
     _need(delta, "delta", torch.float32, (None, n, dm))
-    _check(lib().jb_rmsnorm(_p(x), _p(delta), delta.shape[0], ctypes.c_longlong(n * dm),
-                            _p(None), _p(None), 0, _p(None), 0, n, dm, ctypes.c_float(0.0),
+    _check(lib().jb_rmsnorm(_p(x), _p(delta), delta.shape[0], int(n * dm),
+                            _p(None), _p(None), 0, _p(None), 0, n, dm, float(0.0),
                             _stream()), "add")
     return x
 
@@ -162,7 +204,7 @@ def swiglu(gate_up: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
         raise KernelError("swiglu: the gate_up width must be even")
     ff = two_ff // 2
     out = torch.empty((n, ff), dtype=out_dtype, device=gate_up.device)
-    _check(lib().jb_swiglu(_p(gate_up), S, ctypes.c_longlong(n * two_ff), _p(out),
+    _check(lib().jb_swiglu(_p(gate_up), S, int(n * two_ff), _p(out),
                            _DT[out_dtype], n, ff, _stream()), "swiglu")
     return out
 
@@ -214,8 +256,8 @@ def qk_norm_rope_append(qkv: torch.Tensor, q_weight: Optional[torch.Tensor],
         _need(v_cache, "v_cache", out_dtype, tuple(k_cache.shape))
     q = torch.empty((n, num_heads, head_dim), dtype=out_dtype, device=qkv.device)
     _check(lib().jb_qk_norm_rope_append(
-        _p(qkv), S, ctypes.c_longlong(n * width), _p(q_weight), _p(k_weight), w_dt,
-        ctypes.c_float(eps), _p(cos), _p(sin), rot_half, _p(row_pos), _p(row_seq),
+        _p(qkv), S, int(n * width), _p(q_weight), _p(k_weight), w_dt,
+        float(eps), _p(cos), _p(sin), rot_half, _p(row_pos), _p(row_seq),
         _p(block_table), block_table.shape[1], _p(q), _p(k_cache), _p(v_cache), _DT[out_dtype],
         n, num_heads, num_kv_heads, head_dim, _stream()), "qk_norm_rope_append")
     return q
@@ -289,9 +331,9 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
     if tc and not decode:
         _need(blocks, "blocks", torch.int32, (None, 4))
         _check(L.jb_attn_tc_prefill(_p(q), _p(k_cache), _p(v_cache),
-                                    ctypes.c_longlong(k_cache.shape[0]), _p(blocks),
+                                    int(k_cache.shape[0]), _p(blocks),
                                     blocks.shape[0], _p(block_table), block_table.shape[1],
-                                    _p(out), n, nh, nkv, hd, window, ctypes.c_float(scale),
+                                    _p(out), n, nh, nkv, hd, window, float(scale),
                                     _stream()), "attention (tcgen05, prefill)")
         return out
     if tc:
@@ -311,10 +353,10 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
         cnt = min(rows_per_call, n - row0)
         if tc:
             _check(L.jb_attn_tc_decode(_p(q), _p(k_cache), _p(v_cache),
-                                       ctypes.c_longlong(k_cache.shape[0]), _p(row_pos),
+                                       int(k_cache.shape[0]), _p(row_pos),
                                        _p(row_seq), _p(block_table), block_table.shape[1],
                                        _p(scratch), n, row0, cnt, nh, nkv, hd, window,
-                                       ctypes.c_float(scale), max_chunks, per_cta, _stream()),
+                                       float(scale), max_chunks, per_cta, _stream()),
                    "attention (tcgen05, decode)")
             _check(L.jb_attention_merge(_p(scratch), _p(row_pos), _p(out), _DT[q.dtype], row0, cnt,
                                         nh, hd, window, parts, per_cta, _stream()),
@@ -322,7 +364,7 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
         else:
             _check(L.jb_attention(_p(q), _p(k_cache), _p(v_cache), _DT[q.dtype], _p(row_pos),
                                   _p(row_seq), _p(block_table), block_table.shape[1], _p(scratch),
-                                  _p(out), row0, cnt, nh, nkv, hd, window, ctypes.c_float(scale),
+                                  _p(out), row0, cnt, nh, nkv, hd, window, float(scale),
                                   max_chunks, _stream()), "attention", kernels=2)
     return out
 
@@ -374,11 +416,11 @@ def attention_decode_qkv(qkv: torch.Tensor, q_weight: Optional[torch.Tensor],
     for row0 in range(0, n, rows_per_call):
         cnt = min(rows_per_call, n - row0)
         code = L.jb_attn_tc_decode_qkv(
-            _p(qkv), S, ctypes.c_longlong(n * width), _p(q_weight), _p(k_weight), w_dt,
-            ctypes.c_float(eps), _p(cos), _p(sin), _p(k_cache), _p(v_cache), int(bool(append)),
-            ctypes.c_longlong(k_cache.shape[0]), _p(row_pos), _p(row_seq), _p(block_table),
+            _p(qkv), S, int(n * width), _p(q_weight), _p(k_weight), w_dt,
+            float(eps), _p(cos), _p(sin), _p(k_cache), _p(v_cache), int(bool(append)),
+            int(k_cache.shape[0]), _p(row_pos), _p(row_seq), _p(block_table),
             block_table.shape[1], _p(scratch), n, row0, cnt, num_heads, nkv, hd, window,
-            ctypes.c_float(scale), max_chunks, per_cta, _stream())
+            float(scale), max_chunks, per_cta, _stream())
         if code == -1 and row0 == 0:
             return None             # an address the kernel's 16-byte loads cannot take
         _check(code, "attention (tcgen05, decode, from the product's sums)")
@@ -519,10 +561,10 @@ def sample(logits: torch.Tensor, out: Optional[torch.Tensor] = None,
     L = lib()
     chunk_keys = torch.empty((int(L.jb_sample_scratch(rows, V)),), dtype=torch.int64,
                              device=logits.device)
-    launches = int(L.jb_sample_launches(V, ctypes.c_longlong(big_cap), int(temperature is not None)))
+    launches = int(L.jb_sample_launches(V, int(big_cap), int(temperature is not None)))
     _check(L.jb_sample(_p(logits), rows, V, _p(row_slot), _p(temperature), _p(top_k),
                        _p(top_p), _p(min_p), _p(rng), _p(big_keys), _p(big_probs),
-                       ctypes.c_longlong(big_cap), _p(chunk_keys), _p(out), _p(forced), _stream()),
+                       int(big_cap), _p(chunk_keys), _p(out), _p(forced), _stream()),
            "sample", kernels=launches)
     return out
 

@@ -2,5 +2,7 @@
 from .model import DecoderModel, expected_tensors
 from .engine import Engine, StepEntry, StepError, parse_dtype
 from .replay import Replayer
+from .session import Session, SessionError, sessions_step
 
-__all__ = ["DecoderModel", "expected_tensors", "Engine", "StepEntry", "StepError", "parse_dtype", "Replayer"]
+__all__ = ["DecoderModel", "expected_tensors", "Engine", "StepEntry", "StepError", "parse_dtype", "Replayer",
+           "Session", "SessionError", "sessions_step"]

@@ -118,6 +118,15 @@ class Engine:
     def length(self, slot: int) -> int:
         return int(self.cache.length[slot])
 
+    def truncate_sequence(self, slot: int, n: int) -> bool:
+        """Keeps the first ``n`` computed tokens of a sequence; False where the
+        cache cannot go back there (see ``Cache.truncate``)."""
+        if not self.cache.truncate(slot, n):
+            return False
+        if self._last_decode is not None and slot in self._last_decode[1]:
+            self._last_decode = None
+        return True
+
     # ------------------------------------------------------------------ step
     def plan(self, entries: Sequence[StepEntry]):
         """Checks a step and lays out its rows; touches nothing."""

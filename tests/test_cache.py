@@ -145,3 +145,43 @@ def test_many_sequences_come_and_go():
         c.free_sequence(s)
     c.check()
     assert c.tokens_held() == 0
+
+
+def test_truncate_gives_pages_back_and_knows_what_cannot_be_undone():
+    c = make(max_tokens=1024, window=100)
+    full, win = c.groups
+    s = c.new_sequence()
+    c.reserve([s], [300]); c.advance([s], [300])
+    assert not c.truncate(s, 301) and not c.truncate(s, -1)
+    assert c.truncate(s, 300)                           # nothing to do
+    # a token at 250 would see 151..250: page 2, which the window group gave back
+    assert not c.can_truncate(s, 250) and not c.truncate(s, 250)
+    assert int(c.length[s]) == 300 and full.held(s) == 5
+    # a token at 290 sees 191..290, which begins in page 2 as well
+    assert not c.truncate(s, 290)
+    # a token at 299 sees 200..299: pages 3 and 4, both held
+    assert c.truncate(s, 299) and int(c.length[s]) == 299
+    c.check()
+    assert c.truncate(s, 0)
+    assert int(c.length[s]) == 0 and full.held(s) == 0 and win.held(s) == 0
+    c.check()
+    c.reserve([s], [70]); c.advance([s], [70])
+    assert c.truncate(s, 10) and full.held(s) == 1 and win.held(s) == 1
+    c.reserve([s], [200]); c.advance([s], [200])
+    c.check()
+    c.free_sequence(s)
+    c.check()
+    assert win.pool.n_free == win.pool.n_pages and full.pool.n_free == full.pool.n_pages
+
+
+def test_truncate_with_a_state_of_fixed_size_goes_back_to_nothing_only():
+    c = make(state=True)
+    s = c.new_sequence()
+    c.reserve([s], [20]); c.advance([s], [20])
+    c.mixer_state[1][s] += 5.0
+    assert not c.truncate(s, 10) and int(c.length[s]) == 20
+    assert float(c.mixer_state[1][s].abs().sum()) > 0
+    assert c.truncate(s, 0)
+    assert float(c.mixer_state[1][s].abs().sum()) == 0.0      # as for a new sequence
+    c.free_sequence(s)
+    c.check()

@@ -1,0 +1,173 @@
+"""Sessions on a stand-in engine: what is fed when, what a full context and a
+truncation do, and that several sessions move on together."""
+import numpy as np
+import pytest
+
+from janas_b200.cache import SlotPool
+from janas_b200.engine import generate as G
+from janas_b200.engine import session as S
+from janas_b200.engine.generate import GenOptions
+
+
+class FakeEngine:
+    """The "model" answers token t at position p with (t + p) % 50.  It records the
+    steps and checks that every position is fed exactly once, in order."""
+
+    class _Spec:
+        vocab_size = 50
+
+    def __init__(self, max_positions=40, extend=True, can_go_back=True):
+        eng = self
+
+        class _Model:
+            spec = self._Spec()
+
+            def supports(self, kind):
+                return kind != "extend" or extend
+
+        class _Cache:
+            def set_samplers(self, slots, options):
+                eng.seeds = {s: o.seed for s, o in zip(slots, options)}
+
+        self.model, self.cache = _Model(), _Cache()
+        self.max_positions = max_positions
+        self.pool = SlotPool(4)
+        self.len, self.fed, self.steps = {}, {}, []
+        self.can_go_back = can_go_back
+
+    def new_sequence(self):
+        s = self.pool.take()
+        self.len[s], self.fed[s] = 0, []
+        return s
+
+    def free_sequence(self, s):
+        self.pool.give_back(s)
+        del self.len[s]
+
+    def length(self, s):
+        return self.len[s]
+
+    def truncate_sequence(self, s, n):
+        if n != 0 and n != self.len[s] and not self.can_go_back:
+            return False
+        self.len[s] = n
+        del self.fed[s][n:]
+        return True
+
+    def step(self, entries):
+        lens = [len(e.tokens) for e in entries]
+        pos0 = [self.len[e.slot] for e in entries]
+        kind = ("prefill" if not any(pos0) else "decode" if all(n == 1 for n in lens)
+                else "extend")
+        assert self.model.supports(kind)
+        self.steps.append((kind, lens))
+        out = []
+        for e in entries:
+            assert self.len[e.slot] + len(e.tokens) <= self.max_positions
+            for t in e.tokens:
+                self.fed[e.slot].append(t)
+            self.len[e.slot] += len(e.tokens)
+            for w in e.want:
+                out.append((e.tokens[w] + self.len[e.slot] - len(e.tokens) + w) % 50)
+        return out or None
+
+
+@pytest.fixture(autouse=True)
+def pick(monkeypatch):
+    monkeypatch.setattr(S, "_pick", lambda engine, logits, slots, sampled, big:
+                        (np.asarray(logits), 0))
+
+
+def expected(hist):
+    return (hist[-1] + len(hist) - 1) % 50
+
+
+def test_turns_feed_every_token_once():
+    eng = FakeEngine()
+    s = S.Session(eng, GenOptions(seed=9))
+    assert eng.seeds == {s.slot: 9}
+    with pytest.raises(S.SessionError, match="empty"):
+        s.next()
+    s.append([3, 4, 5])
+    assert (s.length, s.computed) == (3, 0)
+    s.prefill()
+    assert (s.length, s.computed) == (3, 2) and eng.steps == [("prefill", [2])]
+    for _ in range(3):
+        want = expected(s.tokens())
+        assert s.next() == (S.OK, want)
+    assert (s.length, s.computed) == (6, 5)
+    s.append([7, 8])                       # a new turn: the last reply token and the turn
+    want = expected(s.tokens())
+    assert s.next() == (S.OK, want)
+    assert eng.steps[-1] == ("extend", [3])
+    assert eng.fed[s.slot] == s.tokens()[:-1]           # every token once, in order
+    assert s.stats.new_tokens == 4 and s.stats.prompt_tokens == 2 + 2
+    s.close()
+    assert eng.pool.n_free == 4
+    with pytest.raises(S.SessionError, match="closed"):
+        s.next()
+
+
+def test_a_model_that_cannot_extend_goes_token_by_token():
+    eng = FakeEngine(extend=False)
+    s = S.Session(eng)
+    s.append([1, 2, 3])
+    s.next()
+    s.append([9, 9, 9])
+    want = expected(s.tokens())
+    assert s.next() == (S.OK, want)
+    assert eng.steps[-4:] == [("decode", [1])] * 4
+    assert eng.fed[s.slot] == s.tokens()[:-1]
+
+
+def test_context_full_and_append_limits():
+    eng = FakeEngine(max_positions=6)
+    s = S.Session(eng)
+    with pytest.raises(S.SessionError, match="vocabulary"):
+        s.append([50])
+    with pytest.raises(S.SessionError, match="fit"):
+        s.append([1] * 8)
+    assert s.length == 0
+    s.append([1] * 4)
+    out = [s.next() for _ in range(4)]
+    # fed at 4 and 5 after the prompt; the third token has no place to be fed
+    assert [st for st, _ in out] == [S.OK, S.OK, S.OK, S.FULL] and out[3][1] is None
+    assert s.length == 7 and s.computed == 6
+
+
+def test_truncate_computes_the_last_kept_token_again():
+    for can in (True, False):
+        eng = FakeEngine(can_go_back=can)
+        s = S.Session(eng)
+        s.append([5, 6, 7, 8])
+        first = [s.next()[1] for _ in range(3)]
+        s.truncate(5)                      # the prompt and the first reply token
+        assert s.length == 5 and s.computed == (4 if can else 0)
+        assert [s.next()[1] for _ in range(2)] == first[1:]
+        assert eng.fed[s.slot] == s.tokens()[:-1]
+        s.reset()
+        assert (s.length, s.computed) == (0, 0)
+        with pytest.raises(S.SessionError):
+            s.truncate(1)
+
+
+def test_sessions_move_on_together():
+    eng = FakeEngine()
+    a, b, c = S.Session(eng), S.Session(eng), S.Session(eng)
+    a.append([1, 2, 3]); b.append([4]); c.append([9] * 39 + [1, 2])
+    toks, st = S.sessions_step(eng, [a, b, c])
+    assert st == [S.OK, S.OK, S.FULL] and toks[2] is None
+    assert toks[:2] == [expected([1, 2, 3]), expected([4])]
+    assert eng.steps == [("prefill", [3, 1])]
+    a.append([6, 6])                       # a goes on with a turn, b by one token
+    toks, st = S.sessions_step(eng, [a, b])
+    assert eng.steps[-1] == ("extend", [3, 1])
+    assert toks == [expected(a.tokens()[:-1]), expected(b.tokens()[:-1])]
+    toks, st = S.sessions_step(eng, [b, a])
+    assert eng.steps[-1] == ("decode", [1, 1])
+    with pytest.raises(S.SessionError, match="twice"):
+        S.sessions_step(eng, [a, a])
+    other = S.Session(FakeEngine())
+    other.append([1])
+    with pytest.raises(S.SessionError, match="another engine"):
+        S.sessions_step(eng, [a, other])
