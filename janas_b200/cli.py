@@ -4,6 +4,7 @@
                [--ctx N] [--temp T] [--top-k K] [--top-p P] [--min-p P] [--seed S]
                [--max N] [--eos ID] [--stop ID ...] [--batch B] [--dtype bfloat16|float32]
                [--stats]
+    janas-b200 <model-dir> --chat [the sampling options, --ctx, --max]     (turns on standard input)
     janas-b200 <model-dir> --bench [--prompt N] [--gen N] [--rounds N] [--ctx N] [--batch B]
     janas-b200 --random-weights <config.json> --out <model-dir> [--seed S] [--store bfloat16|float32]
 
@@ -12,7 +13,11 @@ janas-chat (src/chat/main.c:1346-1427); ``--prompt --gen --rounds`` what they
 mean for janas-bench (src/bench/main.c:10-30: tokens of prompt, tokens
 generated, rounds, prefill timed apart from decoding: :140-169).  There is no
 tokenizer: prompts are token ids (as tests/llm_gen.c:10-15 takes them from an
-int32 file) and the output is token ids, one request a line.
+int32 file) and the output is token ids, one request a line.  ``--chat`` is a
+conversation as janas-chat holds one (src/chat/main.c: every turn goes on from
+what the model has computed): each line of standard input is a turn's token
+ids, the reply's ids come back as a line (it ends after a stop token, at
+``--max`` tokens or when the context is full), until the input ends.
 """
 from __future__ import annotations
 
@@ -37,6 +42,47 @@ def _read_prompts(args, vocab: int) -> List[List[int]]:
     return [rng.integers(0, vocab, size=args.prompt_len).tolist() for _ in range(args.batch)]
 
 
+def _chat(llm, options, args) -> int:
+    """One session; a turn a line.  A line that cannot be taken (no ids, an id
+    outside the vocabulary, more than the context holds) is answered on standard
+    error and the conversation goes on."""
+    from . import api
+    stops = options.stop_set()
+    s = llm.session(options)
+    try:
+        for line in sys.stdin:
+            try:
+                turn = [int(t) for t in line.replace(",", " ").split()]
+                if not turn:
+                    continue
+                s.append(turn)
+            except ValueError as e:
+                print(f"janas-b200: {e}", file=sys.stderr)
+                continue
+            reply: List[int] = []
+            while len(reply) < args.max:
+                try:
+                    status, tok = s.next()
+                except (api.LLMError, ValueError, RuntimeError) as e:
+                    print(f"janas-b200: {e}", file=sys.stderr)
+                    return 2
+                if status != 0:
+                    print("janas-b200: the context is full", file=sys.stderr)
+                    break
+                reply.append(tok)
+                if tok in stops:
+                    break
+            print(" ".join(str(t) for t in reply), flush=True)
+        if args.stats:
+            st = s.stats
+            print(f"{s.length} tokens in the conversation; prompt {st.prompt_tokens} tokens in "
+                  f"{st.prefill_seconds:.3f} s; {st.new_tokens} new tokens in "
+                  f"{st.decode_seconds:.3f} s", file=sys.stderr)
+    finally:
+        s.close()
+    return 0
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="janas-b200", description=__doc__,
                                  formatter_class=argparse.RawDescriptionHelpFormatter)
@@ -57,6 +103,8 @@ def main(argv=None) -> int:
     ap.add_argument("--batch", type=int, default=1, help="sequences that run together")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--stats", action="store_true")
+    ap.add_argument("--chat", action="store_true", help="turns of token ids on standard input, "
+                                                        "one a line; replies as lines of ids")
     ap.add_argument("--bench", action="store_true", help="measure prefill and decoding speed")
     ap.add_argument("--prompt", type=int, default=256, help="bench: tokens of prompt")
     ap.add_argument("--gen", type=int, default=64, help="bench: tokens generated")
@@ -113,6 +161,11 @@ def main(argv=None) -> int:
         print(f"prompt {args.prompt} x {args.batch}: {best_p:.1f} tok/s; "
               f"gen {args.gen} x {args.batch}: {best_d:.1f} tok/s")
         return 0
+
+    if args.chat:
+        return _chat(llm, GenOptions(eos=eos, temperature=args.temp, top_k=args.top_k,
+                                     top_p=args.top_p, min_p=args.min_p, seed=args.seed,
+                                     stop=stops[:4]), args)
 
     prompts = _read_prompts(args, llm.n_vocab)
     opts = [GenOptions(eos=eos, temperature=args.temp, top_k=args.top_k, top_p=args.top_p,

@@ -171,3 +171,22 @@ def test_step_and_slots_through_the_entry_point():
     assert e.value.code == janas_b200.EINVAL
     m.slot_free(a)
     m.engine.cache.check()
+
+
+def test_cli_chat_goes_on_from_turn_to_turn():
+    """``janas-b200 --chat``: two turns on standard input, each reply the plain
+    model's continuation of the whole conversation so far."""
+    import os, subprocess, sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    c, w = plain_model("A")
+    t1, t2 = [5, 17, 3, 200], [9, 1]
+    r = subprocess.run([sys.executable, os.path.join(root, "bin", "janas-b200"), model_dir("A"),
+                        "--chat", "--max", "5", "--dtype", "float32", "--ctx", "128", "--eos", "-1"],
+                       input=" ".join(map(str, t1)) + "\n\nnot ids\n" + " ".join(map(str, t2)) + "\n",
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr
+    lines = [[int(t) for t in ln.split()] for ln in r.stdout.splitlines()]
+    assert len(lines) == 2 and "invalid literal" in r.stderr
+    r1 = plain.generate(c, w, t1, 5)
+    assert lines[0] == r1
+    assert lines[1] == plain.generate(c, w, t1 + r1 + t2, 5)
