@@ -193,3 +193,28 @@ def test_loop_one_step_ahead_gives_the_same_results(monkeypatch):
     # stopped sequence costs a row of a step that runs anyway.
     assert st.passes == len(eng.begun) == st0.passes + 1
     assert any(not from_host for _, from_host in eng.begun)      # steps were fed on the device
+
+
+def test_loop_one_step_ahead_on_requests_drawn_at_random(monkeypatch):
+    """Many small workloads (prompt lengths, limits, stop tokens, contexts that
+    fill up, batches that shrink): with and without steps launched ahead, the same
+    tokens and reasons; every slot comes back; at most one step more per batch."""
+    rng = np.random.default_rng(2026)
+    for case in range(150):
+        ctx = int(rng.integers(8, 41))
+        reqs = []
+        for _ in range(int(rng.integers(1, 8))):
+            n = int(rng.integers(1, ctx + 1))
+            stop = [int(t) for t in rng.integers(0, 50, size=int(rng.integers(0, 4)))]
+            eos = int(rng.integers(0, 50)) if rng.random() < 0.5 else -1
+            reqs.append(Request([int(t) for t in rng.integers(0, 50, size=n)],
+                                int(rng.integers(0, 12)), GenOptions(eos=eos, stop=stop)))
+        max_batch = int(rng.integers(1, 4))
+        a, b = FakeEngine(max_positions=ctx), AheadEngine(max_positions=ctx)
+        sa, sb = G.GenStats(), G.GenStats()
+        want = run(monkeypatch, a, reqs, max_batch=max_batch, stats=sa)
+        got = run(monkeypatch, b, reqs, max_batch=max_batch, stats=sb)
+        assert [(r.tokens, r.finish) for r in got] == [(r.tokens, r.finish) for r in want], case
+        assert b.pool.n_free == 3 and not b.len and b.under_way == 0
+        assert sb.new_tokens == sa.new_tokens and sb.batches == sa.batches
+        assert sa.passes <= sb.passes <= sa.passes + sa.batches
