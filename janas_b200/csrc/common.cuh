@@ -185,6 +185,15 @@ __device__ __forceinline__ float cluster_read(const float *mine, uint32_t rank)
     return v;
 }
 
+// A float written to the same shared-memory variable of another CTA of the cluster
+// (seen there after the cluster-wide barrier).
+__device__ __forceinline__ void cluster_write(float *mine, uint32_t rank, float v)
+{
+    uint32_t a = (uint32_t)__cvta_generic_to_shared(mine), ra;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(a), "r"(rank));
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(ra), "f"(v) : "memory");
+}
+
 // SMs of the current device (148 on a B200), asked once per device.
 inline int sm_count()
 {

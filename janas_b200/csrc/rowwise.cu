@@ -193,7 +193,8 @@ rmsnorm_rows_kernel(float *__restrict__ x, const float *__restrict__ delta, int 
 // The same for few rows, bfloat16 output: a row is shared out among the C CTAs of
 // a cluster, a value (KEEP values, for very wide rows) per thread, so that all a
 // row needs is fetched at once; the CTAs' sums of squares meet through
-// distributed shared memory and are added in rank order by everyone.  Like
+// distributed shared memory (each writes its own into every CTA) and are added
+// in rank order by everyone.  Like
 // rmsnorm_rows_kernel it serves the bfloat16 path only.  cols: columns per CTA.
 template <typename TW, int KEEP, int C>
 __global__ void __launch_bounds__(1024)
@@ -203,7 +204,7 @@ rmsnorm_cluster_kernel(float *__restrict__ x, const float *__restrict__ delta, i
 {
     constexpr int PB = 16 / KEEP;
     __shared__ float red[32];
-    __shared__ float share;
+    __shared__ float shares[C];        // shares[r]: written here by the CTA of rank r
     pdl_trigger();
     uint32_t rank = cluster_rank();
     size_t orow = blockIdx.x / C;
@@ -247,25 +248,23 @@ rmsnorm_cluster_kernel(float *__restrict__ x, const float *__restrict__ delta, i
 #pragma unroll
     for (int u = 0; u < KEEP; u++)
         ss = fmaf(xv[u], xv[u], ss);
-    ss = block_sum(ss, red);
-    if (threadIdx.x == 0)
-        share = ss;
+    ss = block_sum(ss, red);           // every thread has the CTA's sum
+    // each CTA hands its sum to all the CTAs of the cluster (itself too): one trip
+    // and one barrier, after which everything is local and nobody is read any more
+    if (threadIdx.x < C)
+        cluster_write(&shares[rank], threadIdx.x, ss);
     cluster_arrive();
     cluster_wait();
-    int lane = threadIdx.x & 31;
-    float theirs = lane < C ? cluster_read(&share, (uint32_t)lane) : 0.0f;
-    cluster_arrive();                  // every share this CTA needs has been read
     float tot = 0.0f;
 #pragma unroll
     for (int r = 0; r < C; r++)
-        tot += __shfl_sync(0xffffffffu, theirs, r);
+        tot += shares[r];
     float scale = 1.0f / sqrtf(tot / (float)dm + eps);
     bf16 *o = out + orow * dm;
 #pragma unroll
     for (int u = 0; u < KEEP; u++)
         if (col[u] >= 0)
             o[col[u]] = __float2bfloat16_rn((xv[u] * scale) * wv[u]);
-    cluster_wait();                    // nobody leaves while its share may still be read
 }
 
 // The same for a middling number of rows, bfloat16 output: a block per row, four
