@@ -74,11 +74,14 @@ __host__ __device__ constexpr uint32_t instr_desc(int n)
            ((uint32_t)(TILE_M >> 4) << 24);
 }
 
-template <int BN, int MT> struct TileCfg {
+// DEEP: a product whose CTAs are about as many as the SMs (the fused gate-up product
+// of a decode step: 152 tiles) has one CTA on most SMs, so each keeps a stage more in
+// flight; two of them still fit an SM, and one beside a CTA of the product after it.
+template <int BN, int MT, bool DEEP = false> struct TileCfg {
     static constexpr int A_TILE_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = MT * W_TILE_BYTES + A_TILE_BYTES;
     // 2 CTAs per SM for the small tiles that stream weights, 1 for the large ones
-    static constexpr int RING_BYTES = (BN <= 64 && MT == 1) ? 100 * 1024 : 225 * 1024;
+    static constexpr int RING_BYTES = (BN <= 64 && MT == 1) ? (DEEP ? 110 : 100) * 1024 : 225 * 1024;
     static constexpr int STAGES = RING_BYTES / STAGE_BYTES < 2 ? 2 : (RING_BYTES / STAGE_BYTES > 8 ? 8 : RING_BYTES / STAGE_BYTES);
     static constexpr int TMEM_COLS = MT * BN <= 32 ? 32 : MT * BN <= 64 ? 64 : MT * BN <= 128 ? 128 : MT * BN <= 256 ? 256 : 512;
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment */ + 256 /* barriers */;
@@ -239,7 +242,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                float *__restrict__ out, bf16 *__restrict__ out_act, int n, int m, int k,
                int second_off, int kb_per_split)
 {
-    using Cfg = TileCfg<BN, MT>;
+    using Cfg = TileCfg<BN, MT, EPI == EPI_SWIGLU_HALF>;
     constexpr int STAGES = Cfg::STAGES;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -444,7 +447,7 @@ template <int BN, int MT, int EPI>
 static int launch_tc(const void *A, const void *W, float *out, bf16 *out_act, int n, int m, int k,
                      int w_rows, int second_off, int splits, cudaStream_t st)
 {
-    using Cfg = TileCfg<BN, MT>;
+    using Cfg = TileCfg<BN, MT, EPI == EPI_SWIGLU_HALF>;
     CUtensorMap map_w, map_a;
     if (!tensor_map(W, w_rows, k, EPI == EPI_SWIGLU_HALF ? HALF_M : TILE_M, &map_w) ||
         !tensor_map(A, n, k, BN, &map_a))
