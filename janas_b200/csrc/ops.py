@@ -108,17 +108,31 @@ def _p(t: Optional[torch.Tensor]) -> Optional[int]:
 
 
 def _need(t: torch.Tensor, name: str, dtype=None, shape=None) -> None:
-    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+    """A contiguous CUDA tensor of the given dtype (one, or a tuple of allowed ones)
+    and shape (None: any size there).  Called several times per launch, so written
+    for speed: dtypes are compared by identity, sizes in a plain loop."""
+    try:
+        ok = t.is_cuda
+    except AttributeError:
+        ok = False
+    if not ok:
         raise KernelError(f"{name}: a CUDA tensor is needed (there is no CPU path)")
     if not t.is_contiguous():
         raise KernelError(f"{name}: must be contiguous")
     if dtype is not None:
-        ok = t.dtype in dtype if isinstance(dtype, (tuple, list)) else t.dtype == dtype
-        if not ok:
-            raise KernelError(f"{name}: dtype {t.dtype}, expected {dtype}")
+        td = t.dtype
+        if td is not dtype and (dtype.__class__ is torch.dtype or td not in dtype):
+            raise KernelError(f"{name}: dtype {td}, expected {dtype}")
     if shape is not None:
-        if len(shape) != t.dim() or any(s is not None and s != d for s, d in zip(shape, t.shape)):
-            raise KernelError(f"{name}: shape {tuple(t.shape)}, expected {tuple(shape)}")
+        ts = t.shape
+        bad = len(shape) != len(ts)
+        if not bad:
+            for s, d in zip(shape, ts):
+                if s is not None and s != d:
+                    bad = True
+                    break
+        if bad:
+            raise KernelError(f"{name}: shape {tuple(ts)}, expected {tuple(shape)}")
 
 
 # how many of the library's kernels have been launched (for measurements)
@@ -463,9 +477,28 @@ def attn_tc_error() -> int:
 
 # ------------------------------------------------------------------ products
 def _tensor_core_ok(a: torch.Tensor, weight: torch.Tensor) -> bool:
-    if a.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
+    """What jb_gemm_tc_ok asks (bfloat16 rows of a multiple of 8 values, 16-byte
+    aligned bases), asked here: it is on the path of every product."""
+    if a.dtype is not torch.bfloat16 or weight.dtype is not torch.bfloat16:
         return False
-    return bool(lib().jb_gemm_tc_ok(_p(a), _p(weight), a.shape[0], weight.shape[0], a.shape[1]))
+    k = a.shape[1]
+    return (a.shape[0] > 0 and weight.shape[0] > 0 and k >= 8 and k % 8 == 0
+            and a.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
+
+
+_SPLITS: dict = {}
+
+
+def _splits(n: int, m: int, k: int, device=None) -> int:
+    """jb_gemm_tc_splits, remembered per shape and device (it depends on nothing
+    else but the device's SM count)."""
+    key = (n, m, k, device)
+    s = _SPLITS.get(key)
+    if s is None:
+        if len(_SPLITS) > 4096:
+            _SPLITS.clear()
+        s = _SPLITS[key] = int(lib().jb_gemm_tc_splits(n, m, k))
+    return s
 
 
 def linear(a: torch.Tensor, weight: torch.Tensor, force_simt: bool = False,
@@ -486,7 +519,7 @@ def linear(a: torch.Tensor, weight: torch.Tensor, force_simt: bool = False,
     m = weight.shape[0]
     L = lib()
     if not force_simt and n > 0 and _tensor_core_ok(a, weight):
-        S = 1 if whole else int(splits or L.jb_gemm_tc_splits(n, m, k))
+        S = 1 if whole else int(splits or _splits(n, m, k, a.device.index))
         out = torch.empty((S, n, m), dtype=torch.float32, device=a.device)
         _check(L.jb_gemm_tc(_p(a), _p(weight), _p(out), n, m, k, S, _stream()), "linear (tcgen05)")
         return out
@@ -515,7 +548,7 @@ def linear_swiglu(a: torch.Tensor, gate_up: torch.Tensor) -> Optional[torch.Tens
 def linear_parts(n: int, m: int, k: int) -> int:
     """Into how many parts of k the tensor-core product of n rows with a weight
     [m, k] is cut when the caller leaves it open (see ``linear``)."""
-    return int(lib().jb_gemm_tc_splits(n, m, k))
+    return _splits(n, m, k)
 
 
 def gemm_tc_error() -> int:
