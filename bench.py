@@ -301,7 +301,7 @@ def main():
     import torch
     import janas_b200
     from janas_b200.csrc import ops
-    from janas_b200.engine.generate import GenOptions, GenStats, Request, generate
+    from janas_b200.engine.generate import GenOptions
 
     pk = peaks()
     rng = np.random.default_rng(0)

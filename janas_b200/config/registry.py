@@ -11,7 +11,7 @@ from __future__ import annotations
 
 import json
 import os
-from typing import Any, Callable, Dict, Mapping, Protocol
+from typing import Any, Dict, Mapping, Protocol
 
 from .spec import ConfigError, ModelSpec
 

@@ -24,7 +24,7 @@ import os
 import numpy as np
 import torch
 
-from ..cache import Cache, CacheFull
+from ..cache import Cache
 from ..config import config_from_dir
 from ..parts import DECODE, EXTEND, PREFILL, LayerCache, StepContext
 from ..weights import load_tensors

@@ -6,7 +6,7 @@ that name in a ``PartSpec``.  Nothing else in the framework has to change.
 """
 from __future__ import annotations
 
-from typing import Callable, Dict, Type
+from typing import Callable, Dict
 
 import torch
 

@@ -14,7 +14,7 @@ is widened to float32 (exactly; nothing is rounded).
 """
 from __future__ import annotations
 
-from typing import Dict, Iterator, List, Mapping, Tuple
+from typing import Iterator, List, Mapping, Tuple
 
 import torch
 
