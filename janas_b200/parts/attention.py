@@ -20,7 +20,7 @@ from ..cache import KVSpec
 from ..config import ConfigError
 from ..csrc import ops
 from ..weights import MATRIX, NORM, TensorSpec
-from .base import DECODE, EXTEND, LayerCache, Mixer, StepContext
+from .base import DECODE, LayerCache, Mixer, StepContext
 from .linear import fuse_rows, product
 from .registry import build_part, register_mixer
 
@@ -92,10 +92,10 @@ class GQAAttention(Mixer):
         self.chunk = ops.attention_chunk()
 
     def supports(self, kind: str) -> bool:
-        # with a window, pages behind it are given back after every step, so
-        # tokens appended in bulk to a sequence that already has some would
-        # need keys that are gone
-        return not (kind == EXTEND and self.window)
+        # Every kind of step, with a window too: the pages a window group gives back
+        # after a step are those that the sequence's NEXT token cannot see, and
+        # tokens appended later see no further back than that one.
+        return True
 
     # ------------------------------------------------------------- forward
     def forward(self, ctx: StepContext, h: torch.Tensor, cache: LayerCache) -> torch.Tensor:

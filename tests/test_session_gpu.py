@@ -1,7 +1,6 @@
 """Sessions through the Python entry point against the plain implementation:
 turns that go on from the cache, several sessions in one pass, truncation, a
-full context; models with and without a window (which cannot append several
-tokens to a sequence that holds some)."""
+full context; models with and without a window."""
 import numpy as np
 import pytest
 
@@ -190,3 +189,48 @@ def test_cli_chat_goes_on_from_turn_to_turn():
     r1 = plain.generate(c, w, t1, 5)
     assert lines[0] == r1
     assert lines[1] == plain.generate(c, w, t1 + r1 + t2, 5)
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 5e-6), ("bfloat16", 2e-2)])
+@pytest.mark.parametrize("name", ["C", "E"])
+def test_several_tokens_on_top_of_a_sequence_with_a_window(name, dtype, tol):
+    """Steps that append runs of tokens to sequences which hold some, on models whose
+    upper or first layers have a window: the window groups have given pages back by
+    then, and what every new token can see is still there.  Runs that cross pages
+    and the window's width, next to a sequence that goes on by one token and one that
+    starts, against the plain model on the whole sequences."""
+    from janas_b200.engine import Engine, StepEntry
+    from helpers import rel_err
+    c, w = plain_model(name)
+    rng = np.random.default_rng(17)
+    win = c["sliding_window"]
+    total = [3 * win + 140, win + 70, 9]
+    seqs = [tokens(rng, n, c["vocab_size"]) for n in total]
+    want = [plain.forward(c, w, s).numpy() for s in seqs]
+    eng = Engine.open(model_dir(name), dtype=dtype, max_tokens=2048, max_seqs=4)
+    a, b = eng.new_sequence(), eng.new_sequence()
+    done = [0, 0, 0]
+    cuts = [[win + 3, 1, 64, win + 60, 5, total[0] - 2 * win - 133], [50, 1, 1, 1, win + 16, 1]]
+    third = None
+    for it in range(6):
+        entries, rows = [], []
+        for k, slot in ((0, a), (1, b)):
+            n = cuts[k][it]
+            entries.append(StepEntry(slot, seqs[k][done[k]:done[k] + n], list(range(n))))
+            rows.append((k, done[k], n))
+            done[k] += n
+        if it == 3:                                   # a third sequence starts meanwhile
+            third = eng.new_sequence()
+            entries.append(StepEntry(third, seqs[2], list(range(9))))
+            rows.append((2, 0, 9))
+        got = eng.step(entries).cpu().numpy()
+        at = 0
+        for k, p0, n in rows:
+            e = rel_err(got[at:at + n], want[k][p0:p0 + n])
+            assert e <= tol, (name, dtype, it, k, e)
+            at += n
+    assert done[:2] == total[:2]
+    for s in (a, b, third):
+        eng.free_sequence(s)
+    eng.cache.check()
+    assert eng.cache.tokens_held() == 0
