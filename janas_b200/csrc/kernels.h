@@ -4,6 +4,13 @@
 // nothing and returns 0 or a negative code (JB_EINVAL: a size or type the
 // kernel does not take; JB_ELAUNCH: the launch failed).  The Python side
 // (janas_b200/csrc/ops.py) checks shapes and types before it calls in here.
+//
+// The kernels are launched so that their CTAs may start while the kernel before
+// them in the stream still runs, and they read what cannot depend on it before
+// they wait for it: weights, norm weights, rotation tables, and the index arrays
+// row_pos, row_seq and block_table.  None of these may be the output of another of
+// this library's kernels launched just before (a copy, or any kernel launched in
+// the ordinary way, is fine: nothing starts before those have finished).
 #pragma once
 
 #include <cuda_runtime.h>
