@@ -130,6 +130,18 @@ def test_many_sequences_come_and_go():
                 c.reserve([s], [n]); c.advance([s], [n]); live[s] = n
             except CacheFull:
                 c.free_sequence(s)
+        elif live and rng.random() < 0.25:
+            # a sequence goes back: part of the way where the window group still holds
+            # what the token at that place sees, else not at all (and nothing changes)
+            s = list(live)[int(rng.integers(len(live)))]
+            n = int(rng.integers(0, live[s] + 1))
+            could = c.can_truncate(s, n)
+            assert c.truncate(s, n) == could
+            if could:
+                live[s] = n
+            win = c.groups[1]
+            first = win.first_needed_page(live[s])
+            assert all(p >= 0 for p in win.pages[s][first:])     # what the next token sees is held
         elif live:
             ss = list(live)
             try:
