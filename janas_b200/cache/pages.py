@@ -15,6 +15,8 @@ class CacheFull(RuntimeError):
     """No free page or slot is left (the reference's JANAS_LLM_EFULL,
     include/janas/llm.h:43-53)."""
 
+    code = -5
+
 
 def pages_for(n_tokens: int) -> int:
     return (n_tokens + PAGE - 1) // PAGE

@@ -30,7 +30,12 @@ FULL = 1        # the context is full: no further token can be fed
 
 
 class SessionError(ValueError):
-    pass
+    """A call that cannot be served; ``code`` is the reference's error code for it
+    (include/janas/llm.h:43-53): -1 an invalid argument, -5 a full context."""
+
+    def __init__(self, message: str, code: int = -1):
+        super().__init__(message)
+        self.code = code
 
 
 class Session:
@@ -84,7 +89,7 @@ class Session:
             raise SessionError(f"a token id lies outside the vocabulary of {self.vocab}")
         if len(self.hist) + len(toks) > self.engine.max_positions + 1:
             raise SessionError(f"{len(self.hist)} + {len(toks)} tokens do not fit the context "
-                               f"of {self.engine.max_positions}")
+                               f"of {self.engine.max_positions}", code=-5)
         self.hist.extend(toks)
 
     def truncate(self, n: int) -> None:

@@ -123,10 +123,12 @@ def test_a_model_that_cannot_extend_goes_token_by_token():
 def test_context_full_and_append_limits():
     eng = FakeEngine(max_positions=6)
     s = S.Session(eng)
-    with pytest.raises(S.SessionError, match="vocabulary"):
+    with pytest.raises(S.SessionError, match="vocabulary") as e:
         s.append([50])
-    with pytest.raises(S.SessionError, match="fit"):
+    assert e.value.code == -1
+    with pytest.raises(S.SessionError, match="fit") as e:
         s.append([1] * 8)
+    assert e.value.code == -5                # the reference's EFULL
     assert s.length == 0
     s.append([1] * 4)
     out = [s.next() for _ in range(4)]
