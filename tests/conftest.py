@@ -23,6 +23,13 @@ def pytest_configure(config):
 
 def pytest_collection_modifyitems(config, items):
     import torch
+    # a watchdog on every test (as the reference's tests have one,
+    # tests/test_attention.c:343): a test that hangs ends the run with the stacks of
+    # all threads instead of holding the machine.  Only where the plugin is there.
+    if config.pluginmanager.hasplugin("timeout"):
+        for item in items:
+            if item.get_closest_marker("timeout") is None:
+                item.add_marker(pytest.mark.timeout(600, method="thread"))
     if torch.cuda.is_available():
         return
     skip = pytest.mark.skip(reason="no CUDA device")
