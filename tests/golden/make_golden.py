@@ -1,9 +1,12 @@
 """Makes tests/golden/reference_vectors.json from the reference's own C code.
 
 What of prabanta-dev/janas compiles alone on a CPU is compiled here (gcc) and run
-on small inputs: its sampler (src/llm/sample.c with src/llm/jmath.c) and its
+on small inputs: its sampler (src/llm/sample.c with src/llm/jmath.c), its
 math functions for RoPE angles and the activated gate (janas_powf,
-janas_sincosf in src/llm/jmath.c; janas_silu_mul_det in src/llm/vmath.h).  The
+janas_sincosf in src/llm/jmath.c; janas_silu_mul_det in src/llm/vmath.h), and
+its attention (src/llm/attention.c: janas_attn_run with float scores) over keys
+and values that its eight-bit cache holds exactly (a byte times a scale per
+position and KV head), in blocks of 50 tokens, with and without a window.  The
 whole model cannot be run this way (it takes quantized weights only), so the
 plain implementation in tests/plain_qwen3.py rests on the formulas for the rest.
 
@@ -84,6 +87,79 @@ int main(void)
 }
 '''
 
+ATTENTION_DRIVER = r'''
+#include <stdio.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include "attention.h"
+#include "common/pool.h"
+
+static uint64_t lcg_state;
+static double lcg(void) {
+    lcg_state = lcg_state * 6364136223846793005ull + 1442695040888963407ull;
+    return (double)(lcg_state >> 11) * (1.0 / 9007199254740992.0);
+}
+
+int main(void)
+{
+    /* heads, KV heads, head size, tokens, window, seed; the rows that are printed */
+    struct { int nh, nkv, hd, n, window; uint64_t seed; int rows[6]; } C[] = {
+        {4, 2, 16, 70, 0, 11, {0, 1, 49, 50, 64, 69}},
+        {5, 1, 48, 150, 37, 12, {0, 36, 37, 63, 100, 149}},
+        {6, 3, 128, 300, 150, 13, {0, 149, 150, 255, 256, 299}}};
+    struct janas_pool *pool = janas_pool_create(1, NULL);
+    printf("{\"attention\": [");
+    for (unsigned c = 0; c < sizeof C / sizeof *C; c++) {
+        int nh = C[c].nh, nkv = C[c].nkv, hd = C[c].hd, n = C[c].n;
+        uint32_t n_ctx = 512;
+        float *q = malloc(sizeof(float) * n * nh * hd), *out = malloc(sizeof(float) * n * nh * hd);
+        int8_t *k = calloc((size_t)nkv * n_ctx * hd, 1), *v = calloc((size_t)nkv * n_ctx * hd, 1);
+        float *ks = calloc((size_t)nkv * n_ctx, sizeof(float));
+        float *vs = calloc((size_t)nkv * n_ctx, sizeof(float));
+        lcg_state = C[c].seed;
+        for (int i = 0; i < n * nh * hd; i++)
+            q[i] = (float)((lcg() - 0.5) * 4.0);
+        for (int h = 0; h < nkv; h++)
+            for (int t = 0; t < n; t++) {
+                ks[h * n_ctx + t] = (float)(0.004 + 0.008 * lcg());
+                vs[h * n_ctx + t] = (float)(0.004 + 0.008 * lcg());
+                for (int d = 0; d < hd; d++) {
+                    k[((size_t)h * n_ctx + t) * hd + d] = (int8_t)((int)(lcg() * 255.0) - 127);
+                    v[((size_t)h * n_ctx + t) * hd + d] = (int8_t)((int)(lcg() * 255.0) - 127);
+                }
+            }
+        struct janas_attn *a = janas_attn_create(nh, nkv, hd, n_ctx, 1, JANAS_ATTN_FLOAT);
+        if (!a || janas_attn_scores_mode(a) != JANAS_ATTN_FLOAT)
+            return 1;
+        if (C[c].window)
+            janas_attn_set_window(a, C[c].window);
+        for (int p0 = 0; p0 < n; p0 += 50) {      /* at most 64 tokens a call */
+            int cnt = n - p0 < 50 ? n - p0 : 50;
+            janas_attn_run(a, pool, q + (size_t)p0 * nh * hd, k, ks, v, vs, cnt, p0,
+                           out + (size_t)p0 * nh * hd);
+        }
+        printf("%s{\"nh\": %d, \"nkv\": %d, \"hd\": %d, \"n\": %d, \"window\": %d, "
+               "\"seed\": %llu, \"rows\": {", c ? ", " : "", nh, nkv, hd, n, C[c].window,
+               (unsigned long long)C[c].seed);
+        int step = hd / 16;                        /* sixteen values of every head */
+        for (int r = 0; r < 6; r++) {
+            printf("%s\"%d\": [", r ? ", " : "", C[c].rows[r]);
+            for (int h = 0; h < nh; h++)
+                for (int d = 0; d < hd; d += step)
+                    printf("%s%.9g", h + d ? ", " : "",
+                           out[((size_t)C[c].rows[r] * nh + h) * hd + d]);
+            printf("]");
+        }
+        printf("}}");
+        janas_attn_destroy(a);
+        free(q); free(out); free(k); free(v); free(ks); free(vs);
+    }
+    printf("]}\n");
+    janas_pool_destroy(pool);
+    return 0;
+}
+'''
+
 
 def main():
     if len(sys.argv) != 2:
@@ -100,7 +176,22 @@ def main():
                         os.path.join(ref, "src/llm/sample.c"),
                         os.path.join(ref, "src/llm/jmath.c"), "-lm", "-o", exe], check=True)
         out = subprocess.run([exe], check=True, capture_output=True, text=True).stdout
+        drv = os.path.join(tmp, "attention_driver.c")
+        with open(drv, "w") as f:
+            f.write(ATTENTION_DRIVER)
+        exe = os.path.join(tmp, "attention_driver")
+        llm, common = os.path.join(ref, "src/llm"), os.path.join(ref, "src/common")
+        subprocess.run(["gcc", "-O2", "-ffp-contract=off", "-I", llm, "-I", os.path.join(ref, "src"),
+                        drv] + [os.path.join(llm, f) for f in
+                                ("attention.c", "jmath.c", "quant.c", "quant_q6k.c", "tuner.c")]
+                       + [os.path.join(common, f) for f in
+                          ("pool.c", "sysinfo.c", "paths.c", "cpu_features.c")]
+                       + ["-lm", "-lpthread", "-o", exe], check=True)
+        # the reference keeps tuning notes below HOME: give it the scratch folder
+        att = subprocess.run([exe], check=True, capture_output=True, text=True,
+                             env=dict(os.environ, HOME=tmp, JANAS_ATTN="float")).stdout
     data = json.loads(out)
+    data.update(json.loads(att))
     with open(os.path.join(here, "reference_vectors.json"), "w") as f:
         json.dump(data, f)
         f.write("\n")

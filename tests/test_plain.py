@@ -71,6 +71,39 @@ def test_silu_matches_the_reference_math():
         assert abs(got - want) <= 2e-6 * max(1.0, abs(want))
 
 
+def test_attention_matches_the_reference_attention():
+    """plain.attention against the reference's own attention code (janas_attn_run
+    with float scores, compiled alone: tests/golden/make_golden.py) on keys and
+    values that its eight-bit cache holds exactly: grouped heads of 16, 48 and 128
+    values, sequences run in blocks of 50 tokens, rows at the blocks' and the
+    windows' edges."""
+    for case in GOLDEN["attention"]:
+        nh, nkv, hd, n, window = (case[k] for k in ("nh", "nkv", "hd", "n", "window"))
+        g = LCG(case["seed"])
+        q = np.array([np.float32((g.next() - 0.5) * 4.0) for _ in range(n * nh * hd)],
+                     dtype=np.float32).reshape(n, nh, hd)
+        k = np.zeros((n, nkv, hd), dtype=np.float32)
+        v = np.zeros((n, nkv, hd), dtype=np.float32)
+        for h in range(nkv):
+            for t in range(n):
+                ks = np.float32(0.004 + 0.008 * g.next())
+                vs = np.float32(0.004 + 0.008 * g.next())
+                for d in range(hd):
+                    k[t, h, d] = np.float32(int(g.next() * 255.0) - 127) * ks
+                    v[t, h, d] = np.float32(int(g.next() * 255.0) - 127) * vs
+        out = plain.attention(torch.from_numpy(q), torch.from_numpy(k), torch.from_numpy(v), window)
+        step = hd // 16
+        for row, want in case["rows"].items():
+            want = np.asarray(want, dtype=np.float64).reshape(nh, 16)
+            got = out[int(row)].double().numpy()[:, ::step]
+            err = np.abs(got - want).max() / np.abs(want).max()
+            assert err <= 2e-6, (nh, nkv, hd, window, row, err)
+        if window:      # the window does matter at the rows that were compared
+            full = plain.attention(torch.from_numpy(q), torch.from_numpy(k), torch.from_numpy(v), 0)
+            last = max(int(r) for r in case["rows"])
+            assert (full[last] - out[last]).abs().max() > 1e-3
+
+
 def test_splitmix_and_greedy():
     s, z = plain.splitmix64(0)
     assert (s, z) == (0x9E3779B97F4A7C15, 0xE220A8397B1DCDAF)     # the published first output
