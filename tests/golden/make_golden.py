@@ -6,7 +6,8 @@ math functions for RoPE angles and the activated gate (janas_powf,
 janas_sincosf in src/llm/jmath.c; janas_silu_mul_det in src/llm/vmath.h), and
 its attention (src/llm/attention.c: janas_attn_run with float scores) over keys
 and values that its eight-bit cache holds exactly (a byte times a scale per
-position and KV head), in blocks of 50 tokens, with and without a window.  The
+position and KV head), in blocks of 50 tokens, with and without a window, and
+its RMSNorm (rms_norm, an inline function of src/llm/model_impl.h).  The
 whole model cannot be run this way (it takes quantized weights only), so the
 plain implementation in tests/plain_qwen3.py rests on the formulas for the rest.
 
@@ -160,6 +161,46 @@ int main(void)
 }
 '''
 
+NORM_DRIVER = r'''
+#include <stdio.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include "model_impl.h"
+
+static uint64_t lcg_state;
+static double lcg(void) {
+    lcg_state = lcg_state * 6364136223846793005ull + 1442695040888963407ull;
+    return (double)(lcg_state >> 11) * (1.0 / 9007199254740992.0);
+}
+
+int main(void)
+{
+    struct { int n; float eps; uint64_t seed; } C[] = {
+        {16, 1e-6f, 21}, {96, 1e-5f, 22}, {104, 3e-6f, 23}, {2560, 1e-6f, 24}};
+    printf("{\"rms_norm\": [");
+    for (unsigned c = 0; c < sizeof C / sizeof *C; c++) {
+        int n = C[c].n;
+        float *x = malloc(sizeof(float) * n), *w = malloc(sizeof(float) * n);
+        float *out = malloc(sizeof(float) * n);
+        lcg_state = C[c].seed;
+        for (int i = 0; i < n; i++) {
+            x[i] = (float)((lcg() - 0.5) * 8.0);
+            w[i] = (float)(1.0 + (lcg() - 0.5) * 0.4);
+        }
+        rms_norm(out, x, w, (uint32_t)n, C[c].eps);
+        int step = n > 128 ? n / 16 : 1;
+        printf("%s{\"n\": %d, \"eps\": %.9g, \"seed\": %llu, \"step\": %d, \"out\": [",
+               c ? ", " : "", n, C[c].eps, (unsigned long long)C[c].seed, step);
+        for (int i = 0; i < n; i += step)
+            printf("%s%.9g", i ? ", " : "", out[i]);
+        printf("]}");
+        free(x); free(w); free(out);
+    }
+    printf("]}\n");
+    return 0;
+}
+'''
+
 
 def main():
     if len(sys.argv) != 2:
@@ -190,8 +231,18 @@ def main():
         # the reference keeps tuning notes below HOME: give it the scratch folder
         att = subprocess.run([exe], check=True, capture_output=True, text=True,
                              env=dict(os.environ, HOME=tmp, JANAS_ATTN="float")).stdout
+        # rms_norm is an inline function of the model's own header
+        drv = os.path.join(tmp, "norm_driver.c")
+        with open(drv, "w") as f:
+            f.write(NORM_DRIVER)
+        exe = os.path.join(tmp, "norm_driver")
+        subprocess.run(["gcc", "-O2", "-ffp-contract=off", "-I", llm, "-I", os.path.join(ref, "src"),
+                        "-I", os.path.join(ref, "include"), drv, os.path.join(llm, "jmath.c"),
+                        "-lm", "-o", exe], check=True)
+        norm = subprocess.run([exe], check=True, capture_output=True, text=True).stdout
     data = json.loads(out)
     data.update(json.loads(att))
+    data.update(json.loads(norm))
     with open(os.path.join(here, "reference_vectors.json"), "w") as f:
         json.dump(data, f)
         f.write("\n")

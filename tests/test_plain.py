@@ -71,6 +71,24 @@ def test_silu_matches_the_reference_math():
         assert abs(got - want) <= 2e-6 * max(1.0, abs(want))
 
 
+def test_rms_norm_matches_the_reference_norm():
+    """plain.rms_norm against the reference's rms_norm (an inline function of its
+    model header, compiled alone): bit for bit, or within one unit in the last
+    place where the square root's rounding differs."""
+    for case in GOLDEN["rms_norm"]:
+        n, step = case["n"], case["step"]
+        g = LCG(case["seed"])
+        x, w = np.zeros(n, dtype=np.float32), np.zeros(n, dtype=np.float32)
+        for i in range(n):
+            x[i] = np.float32((g.next() - 0.5) * 8.0)
+            w[i] = np.float32(1.0 + (g.next() - 0.5) * 0.4)
+        got = plain.rms_norm(torch.from_numpy(x), torch.from_numpy(w),
+                             float(np.float32(case["eps"]))).numpy()[::step]
+        want = np.asarray(case["out"], dtype=np.float32)
+        assert got.shape == want.shape
+        assert np.abs(got - want).max() <= 2.0 ** -23 * np.abs(want).max(), n
+
+
 def test_attention_matches_the_reference_attention():
     """plain.attention against the reference's own attention code (janas_attn_run
     with float scores, compiled alone: tests/golden/make_golden.py) on keys and
