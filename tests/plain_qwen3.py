@@ -5,15 +5,20 @@ shares no code with ``janas_b200``: it reads ``config.json`` with ``json`` and
 the weights with the ``safetensors`` package, and every function restates a
 formula of the reference, cited as file:line within prabanta-dev/janas.
 
-The whole model rests on the formulas only.  The reference's own model code
-cannot run a float32 or bfloat16 model: its loader accepts quantized weight types
-alone (src/llm/model_load.c:68-71), quantizes activations and the cache to eight
-bits (src/llm/model_attn.c:42-48,115-145) and wants sizes that are multiples of
-256 (src/llm/model_load.c:827-830).  What of the reference does compile alone
-here is compared with this file through the vectors under ``tests/golden/``: its
-sampler, its math functions, and its attention (float scores over keys and
-values that its eight-bit cache holds exactly; ``attention`` below agrees with it
-to 1e-6).
+The reference's own model code cannot run a float32 or bfloat16 model: its loader
+accepts quantized weight types alone (src/llm/model_load.c:68-71), quantizes
+activations and the cache to eight bits (src/llm/model_attn.c:42-48,115-145) and
+wants sizes that are multiples of 256 (src/llm/model_load.c:827-830).  So this
+file is compared with the reference in two ways (``tests/golden/``,
+``tests/test_plain.py``).  Part by part, exactly: what of the reference compiles
+alone here (its sampler, its math functions, its RMSNorm, and its attention with
+float scores over keys and values that its eight-bit cache holds exactly) gives
+the same tokens, the same bits or agrees to 1e-6.  And whole, loosely: a tiny
+random Qwen3 whose matrices its eight-bit weight type holds exactly went through
+its own tools (gguf2jns, llm_eval) on the CPU; ``forward`` below agrees with the
+logits it wrote to a few hundredths of the largest (what its eight-bit
+activations cost), while a wrong pairing of heads, exchanged norms or another
+rotation are off by ten times as much.
 
 ``rounding="bfloat16"`` rounds the activations to bfloat16 at the places where a
 bfloat16 engine stores them (norm outputs, q/k/v after RoPE, the attention

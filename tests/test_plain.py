@@ -122,6 +122,56 @@ def test_attention_matches_the_reference_attention():
             assert (full[last] - out[last]).abs().max() > 1e-3
 
 
+def test_whole_model_against_the_reference_model_code():
+    """plain.forward against the logits that the reference's own forward pass wrote
+    for a tiny random Qwen3 (tests/golden/make_model_golden.py: its tools, run on a
+    CPU, on weights that its eight-bit type holds exactly).  The reference rounds
+    activations and cached keys and values to eight bits, so the two agree to a few
+    hundredths of the largest logit, not more.  That is enough to tell the structure:
+    the same comparison with two norms' weights exchanged, gate and up exchanged,
+    another rotation base or the KV heads paired the other way is off by ten times
+    as much and more."""
+    golden = os.path.join(os.path.dirname(__file__), "golden")
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("tiny_q8_model",
+                                                  os.path.join(golden, "tiny_q8_model.py"))
+    tiny = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(tiny)
+    ref = json.load(open(os.path.join(golden, "reference_model_logits.json")))
+    pos = ref["positions"]
+    want = np.asarray(ref["logits"], dtype=np.float32)
+    c = dict(tiny.CONFIG)
+    w = {h: torch.from_numpy(a.copy()) for _, h, a, _, _ in tiny.tensors()}
+
+    def off(config, weights):
+        got = plain.forward(config, weights, tiny.TOKENS).numpy()[pos]
+        return got, np.abs(got - want).max(axis=1) / np.abs(want).max(axis=1)
+
+    got, err = off(c, w)
+    assert err.max() <= 6e-2 and err.mean() <= 4e-2, err
+    assert np.corrcoef(got.ravel(), want.ravel())[0, 1] >= 0.999
+    assert (got.argmax(1) == want.argmax(1)).mean() >= 0.75
+
+    def exchanged(a, b):
+        wrong = dict(w)
+        for l in range(c["num_hidden_layers"]):
+            x, y = f"model.layers.{l}.{a}", f"model.layers.{l}.{b}"
+            wrong[x], wrong[y] = w[y], w[x]
+        return off(c, wrong)[1]
+
+    late = [i for i, p in enumerate(pos) if p >= 7]        # rows that see several positions
+    assert exchanged("self_attn.q_norm.weight", "self_attn.k_norm.weight")[late].min() >= 0.2
+    assert exchanged("input_layernorm.weight", "post_attention_layernorm.weight").min() >= 0.5
+    assert exchanged("mlp.gate_proj.weight", "mlp.up_proj.weight").min() >= 0.5
+    assert off(dict(c, rope_theta=1e6), w)[1][late].min() >= 0.25
+    wrong = dict(w)
+    half = c["head_dim"]
+    for l in range(c["num_hidden_layers"]):
+        k = f"model.layers.{l}.self_attn.k_proj.weight"
+        wrong[k] = torch.cat([w[k][half:], w[k][:half]])          # the two KV heads exchanged
+    assert off(c, wrong)[1][1:].min() >= 0.5
+
+
 def test_splitmix_and_greedy():
     s, z = plain.splitmix64(0)
     assert (s, z) == (0x9E3779B97F4A7C15, 0xE220A8397B1DCDAF)     # the published first output
