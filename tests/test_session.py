@@ -173,3 +173,49 @@ def test_sessions_move_on_together():
     other.append([1])
     with pytest.raises(S.SessionError, match="another engine"):
         S.sessions_step(eng, [a, other])
+
+
+def test_sessions_driven_at_random_feed_every_position_once_and_in_order():
+    """Appends, tokens asked for alone and together, prefills, truncations and
+    resets in random order, on an engine that can append runs of tokens, one that
+    cannot, and one whose cache cannot go back part of the way: what the engine was
+    fed is always the sequence itself, up to its last token but one."""
+    rng = np.random.default_rng(5)
+    for kind in range(3):
+        eng = FakeEngine(max_positions=60, extend=kind != 1, can_go_back=kind != 2)
+        ss = [S.Session(eng) for _ in range(3)]
+        for it in range(600):
+            s = ss[int(rng.integers(3))]
+            op = rng.random()
+            if op < 0.3:
+                room = eng.max_positions + 1 - s.length
+                n = int(rng.integers(1, 9))
+                if n <= room:
+                    s.append([int(t) for t in rng.integers(0, 50, size=n)])
+                else:
+                    with pytest.raises(S.SessionError):
+                        s.append([1] * n)
+            elif op < 0.55 and s.length:
+                want = expected(s.tokens())
+                full = s.length > eng.max_positions        # the last token has no place to be fed
+                assert s.next() == ((S.FULL, None) if full else (S.OK, want))
+            elif op < 0.7:
+                live = [x for x in ss if x.length]
+                if live:
+                    wants = [expected(x.tokens()) if x.length <= eng.max_positions else None
+                             for x in live]
+                    toks, st = S.sessions_step(eng, live)
+                    assert toks == wants
+            elif op < 0.8 and s.length:
+                s.prefill()
+                assert s.computed >= s.length - 1
+            elif op < 0.95 and s.length:
+                s.truncate(int(rng.integers(0, s.length + 1)))
+            elif op >= 0.95:
+                s.reset()
+            for x in ss:
+                assert x.computed <= max(x.length - 1, 0) or x.computed == x.length == 0
+                assert eng.fed[x.slot] == x.tokens()[:x.computed]
+        for x in ss:
+            x.close()
+        assert eng.pool.n_free == 4
