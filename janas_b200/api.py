@@ -174,5 +174,9 @@ def open(path: str, params: Optional[LLMParams] = None) -> LLM:
         raise LLMError(EOPEN, str(e)) from None
     except torch.cuda.OutOfMemoryError as e:
         raise LLMError(ENOMEM, str(e)) from None
+    except RuntimeError as e:
+        # no CUDA device, or the kernel library cannot be built or loaded: there is
+        # no other path to fall back to
+        raise LLMError(EFAIL, str(e)) from None
     eng.max_positions = min(eng.max_positions, p.n_ctx)
     return LLM(eng, p)
