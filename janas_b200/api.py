@@ -1,15 +1,17 @@
-"""The Python entry point, in the manner of the reference's C interface.
+"""The Python entry point: a thin ctypes layer over the library's C interface
+(``include/janas_b200/llm.h``), which follows the reference's
+(include/janas/llm.h, src/llm/generate.h).
 
-    llm = janas_b200.open(model_dir, params)           # janas_llm_open
-    tokens, stats = llm.generate(prompt, max_new, options)   # janas_llm_generate
-    s = llm.session(options); s.append(prompt); status, token = s.next()   # janas_llm_session_*
-    llm.close()                                        # janas_llm_close
+    llm = janas_b200.open(model_dir, params)                  # jb_llm_open
+    tokens, stats = llm.generate(prompt, max_new, options)    # jb_llm_generate
+    s = llm.session(options); s.append(prompt); status, token = s.next()   # jb_llm_session_*
+    llm.close()                                               # jb_llm_close
 
-Names follow include/janas/llm.h and src/llm/generate.h: ``params_default``
-(janas_llm_params_default, include/janas/llm.h:159), ``n_ctx``
-(struct janas_llm_params, :76-78), the error codes (:43-53), ``GenOptions`` and
-``GenStats`` (struct janas_gen_options / janas_gen_stats,
-src/llm/generate.h:31-86).  Tokens go in and come out as lists of ids on the
+``params_default`` is jb_llm_params_default (janas_llm_params_default,
+include/janas/llm.h:159), ``n_ctx`` the context of one sequence (struct
+janas_llm_params, :76-78), the error codes are the reference's (:43-53),
+``GenOptions`` and ``GenStats`` its struct janas_gen_options / janas_gen_stats
+(src/llm/generate.h:31-86).  Tokens go in and come out as lists of ids on the
 host; there is no tokenizer here.
 """
 from __future__ import annotations
@@ -17,21 +19,9 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import List, Optional, Sequence, Tuple, Union
 
-ABI_VERSION = 1
-
-OK = 0
-EINVAL = -1   # invalid argument
-ENOMEM = -2   # out of memory
-EOPEN = -3    # model folder missing, unreadable, invalid
-EMODEL = -4   # model not supported (architecture)
-EFULL = -5    # the context or the cache is full
-EFAIL = -8    # internal failure
-
-
-class LLMError(RuntimeError):
-    def __init__(self, code: int, message: str):
-        super().__init__(message)
-        self.code = code
+from . import lib
+from .lib import (ABI_VERSION, EFAIL, EFULL, EINVAL, ELIMIT, EMODEL, ENOMEM, EOPEN, OK, CacheFull,
+                  LLMError)
 
 
 @dataclass
@@ -44,11 +34,15 @@ class LLMParams:
 
 
 def params_default() -> LLMParams:
-    return LLMParams()
+    import ctypes
+    p = lib.Params()
+    lib.lib().jb_llm_params_default(ctypes.byref(p))
+    return LLMParams(n_ctx=p.n_ctx, dtype="float32" if p.dtype == lib.F32 else "bfloat16",
+                     max_batch=p.max_batch, max_tokens=p.max_tokens, device=f"cuda:{p.device}")
 
 
 def abi_version() -> int:
-    return ABI_VERSION
+    return int(lib.lib().jb_llm_abi_version())
 
 
 class LLM:
@@ -57,6 +51,7 @@ class LLM:
     def __init__(self, engine, params: LLMParams):
         self.engine = engine
         self.params = params
+        self.last_finish: List[str] = []
 
     @property
     def n_ctx(self) -> int:
@@ -64,10 +59,9 @@ class LLM:
 
     @property
     def n_vocab(self) -> int:
-        return self.engine.model.spec.vocab_size
+        return self.engine.vocab_size
 
-    def generate(self, prompt: Sequence[int], max_new: int, options=None
-                 ) -> Tuple[List[int], "GenStats"]:
+    def generate(self, prompt: Sequence[int], max_new: int, options=None):
         """Runs the prompt, then generates up to ``max_new`` tokens, stopping
         after a stop token.  Returns the new tokens and the counters."""
         outs, stats = self.generate_batch([prompt], max_new, options)
@@ -93,42 +87,34 @@ class LLM:
         stats = GenStats()
         try:
             res = generate(self.engine, [Request(list(p), m, o)
-                                         for p, m, o in zip(prompts, news, opts)],
-                           max_batch=self.params.max_batch, stats=stats)
+                                         for p, m, o in zip(prompts, news, opts)], stats=stats)
         except ValueError as e:
+            if isinstance(e, LLMError):
+                raise
             raise LLMError(EINVAL, str(e)) from None
         self.last_finish = [r.finish for r in res]
         return [r.tokens for r in res], stats
 
     # ------------------------------------------------------------- sessions
-    def session(self, options=None) -> "Session":
+    def session(self, options=None):
         """A sequence of its own on this model, which grows by appended tokens and
-        by tokens generated on request (janas_llm_session_create,
-        src/llm/generate.h:101-103); see ``janas_b200.engine.session``.  As many
-        sessions as ``max_batch`` can be open at one time; ``close`` gives a
-        session's place and cache pages back."""
-        from .cache import CacheFull
-        from .engine.session import Session, SessionError
+        by tokens generated on request (jb_llm_session_create); see
+        ``janas_b200.engine.session``.  As many sessions as ``max_batch`` can be
+        open at one time; ``close`` gives a session's place and cache pages back."""
+        from .engine.session import Session
         try:
             return Session(self.engine, options)
-        except (SessionError, ValueError) as e:
+        except ValueError as e:
+            if isinstance(e, LLMError):
+                raise
             raise LLMError(EINVAL, str(e)) from None
-        except (CacheFull, RuntimeError) as e:
-            raise LLMError(EFULL, str(e)) from None
 
     def sessions_step(self, sessions):
-        """Moves several sessions on together in one pass
-        (janas_llm_sessions_step, src/llm/generate.h:155-158): returns
-        (tokens, status), status 0 with a token, 1 when that session's context is
-        full."""
-        from .cache import CacheFull
-        from .engine.session import SessionError, sessions_step
-        try:
-            return sessions_step(self.engine, list(sessions))
-        except SessionError as e:
-            raise LLMError(EINVAL, str(e)) from None
-        except CacheFull as e:
-            raise LLMError(EFULL, str(e)) from None
+        """Moves several sessions on together in one pass (jb_llm_sessions_step):
+        returns (tokens, status), status 0 with a token, 1 when that session's
+        context is full."""
+        from .engine.session import sessions_step
+        return sessions_step(self.engine, list(sessions))
 
     # ------------------------------------------------- the step function itself
     def slot_new(self) -> int:
@@ -142,41 +128,18 @@ class LLM:
     def step(self, entries):
         """One step of the engine: ``entries`` are (slot, tokens, wanted places);
         returns the float32 logits [wanted, vocab] on the device, or None."""
-        from .engine import StepEntry, StepError
-        from .cache import CacheFull
-        try:
-            return self.engine.step([e if isinstance(e, StepEntry) else StepEntry(*e)
-                                     for e in entries])
-        except StepError as e:
-            raise LLMError(EINVAL, str(e)) from None
-        except CacheFull as e:
-            raise LLMError(EFULL, str(e)) from None
+        return self.engine.step(entries)
 
     def close(self) -> None:
+        if self.engine is not None:
+            self.engine.close()
         self.engine = None
 
 
 def open(path: str, params: Optional[LLMParams] = None) -> LLM:
     """Opens a model folder (config.json, model.safetensors)."""
-    import torch
-    from .cache import CacheFull
-    from .config import ConfigError
     from .engine import Engine
-    from .weights import SafetensorsError, WeightError
     p = params or params_default()
-    try:
-        eng = Engine.open(path, dtype=p.dtype, max_tokens=p.max_tokens or p.n_ctx,
-                          max_seqs=p.max_batch, device=p.device)
-    except ConfigError as e:
-        code = EMODEL if "not supported" in str(e) else EOPEN
-        raise LLMError(code, str(e)) from None
-    except (SafetensorsError, WeightError, OSError) as e:
-        raise LLMError(EOPEN, str(e)) from None
-    except torch.cuda.OutOfMemoryError as e:
-        raise LLMError(ENOMEM, str(e)) from None
-    except RuntimeError as e:
-        # no CUDA device, or the kernel library cannot be built or loaded: there is
-        # no other path to fall back to
-        raise LLMError(EFAIL, str(e)) from None
-    eng.max_positions = min(eng.max_positions, p.n_ctx)
+    eng = Engine.open(path, dtype=p.dtype, max_tokens=p.max_tokens or p.n_ctx, max_seqs=p.max_batch,
+                      device=p.device, n_ctx=p.n_ctx)
     return LLM(eng, p)

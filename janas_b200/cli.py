@@ -117,7 +117,7 @@ def main(argv=None) -> int:
 
     if args.random_weights:
         import torch
-        from .config import config_from_dict
+        from .config import ConfigError, config_from_dict
         from .weights import write_random_model
         if not args.out:
             ap.error("--random-weights needs --out")
@@ -140,7 +140,7 @@ def main(argv=None) -> int:
     except api.LLMError as e:
         print(f"janas-b200: {e}", file=sys.stderr)
         return 2
-    eos_ids = getattr(getattr(llm.engine, "config", None), "eos_token_ids", ())
+    eos_ids = tuple(getattr(getattr(llm.engine, "config", None), "eos_token_ids", ()) or ())
     eos = args.eos if args.eos is not None else (eos_ids[0] if eos_ids else -1)
     stops = list(args.stop) + [e for e in eos_ids[1:] if args.eos is None]
 

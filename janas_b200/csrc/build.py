@@ -1,8 +1,9 @@
-"""Compiles the CUDA kernels for sm_100a into one shared library, in the tree.
+"""Compiles the library (the CUDA kernels for sm_100a and the C++ engine around
+them) into one shared library, in the tree.
 
 The library is built with nvcc alone (no PyTorch headers), so a first call in a
-fresh checkout takes well under a minute; while it compiles, a line is printed
-now and then.  A record of the sources' hashes beside the library decides
+fresh checkout takes about a minute; while it compiles, a line is printed now and
+then.  A record of the sources' hashes beside the library decides
 whether it is still current.  The library lands in ``janas_b200/csrc/_build``
 when that folder can be written and in a per-user folder under the system's
 temporary directory otherwise.
@@ -22,7 +23,10 @@ from concurrent.futures import ThreadPoolExecutor
 from typing import List, Optional
 
 CSRC = os.path.dirname(os.path.abspath(__file__))
-LIB_NAME = "libjanas_b200_kernels.so"
+PKG = os.path.dirname(CSRC)
+LIB_NAME = "libjanas_b200.so"
+# folders of the package that hold sources of the library
+SOURCE_DIRS = ("core", "config", "weights", "cache", "parts", "engine", "api", "csrc")
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ARCH_FLAGS + ["-O3", "-lineinfo", "-std=c++17", "-Xcompiler", "-fPIC",
                            "--expt-relaxed-constexpr"]
@@ -47,16 +51,26 @@ def _nvcc() -> str:
 
 
 def sources() -> List[str]:
-    return sorted(f for f in os.listdir(CSRC) if f.endswith(".cu"))
+    """Every .cu and .cpp file of the library, as paths below the package."""
+    out = []
+    for d in SOURCE_DIRS:
+        folder = os.path.join(PKG, d)
+        if os.path.isdir(folder):
+            out += [os.path.join(d, f) for f in os.listdir(folder) if f.endswith((".cu", ".cpp"))]
+    return sorted(out)
 
 
 def _fingerprint(nvcc: str) -> str:
     h = hashlib.sha256()
-    for f in sorted(os.listdir(CSRC)):
-        if f.endswith((".cu", ".cuh", ".h")):
-            h.update(f.encode())
-            with open(os.path.join(CSRC, f), "rb") as fh:
-                h.update(fh.read())
+    for d in SOURCE_DIRS + (os.path.join("include", "janas_b200"),):
+        folder = os.path.join(PKG, d)
+        if not os.path.isdir(folder):
+            continue
+        for f in sorted(os.listdir(folder)):
+            if f.endswith((".cu", ".cuh", ".h", ".cpp")):
+                h.update(os.path.join(d, f).encode())
+                with open(os.path.join(folder, f), "rb") as fh:
+                    h.update(fh.read())
     h.update(" ".join(NVCC_FLAGS).encode())
     try:
         ver = subprocess.run([nvcc, "--version"], capture_output=True, text=True).stdout
@@ -116,13 +130,13 @@ def library_path(build_if_needed: bool = True, verbose: bool = True) -> str:
         if os.path.isfile(lib):
             return lib
     if not build_if_needed:
-        raise BuildError("janas_b200: the kernel library has not been built")
+        raise BuildError("janas_b200: the library has not been built")
     if nvcc is None:
         _nvcc()  # raises with the message
     for d in _build_dirs(fp):
         if _writable_dir(d):
             return _compile(nvcc, d, fp, verbose)
-    raise BuildError("janas_b200: no folder to build the kernel library in")
+    raise BuildError("janas_b200: no folder to build the library in")
 
 
 def _compile(nvcc: str, build_dir: str, fingerprint: str, verbose: bool) -> str:
@@ -137,19 +151,20 @@ def _compile(nvcc: str, build_dir: str, fingerprint: str, verbose: bool) -> str:
 
     def ticker() -> None:
         while not stop.wait(5.0):
-            say(f"compiling kernels for sm_100a, {done[0]} of {len(srcs)} files done, "
+            say(f"compiling, {done[0]} of {len(srcs)} files done, "
                 f"{time.time() - t0:.0f} s")
 
     def one(src: str) -> str:
-        obj = os.path.join(build_dir, src[:-3] + ".o")
-        cmd = [nvcc] + NVCC_FLAGS + ["-I", CSRC, "-c", os.path.join(CSRC, src), "-o", obj]
+        obj = os.path.join(build_dir, src.replace(os.sep, "_").rsplit(".", 1)[0] + ".o")
+        cmd = [nvcc] + NVCC_FLAGS + ["-I", CSRC, "-c", os.path.join(PKG, src), "-o", obj]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise BuildError(f"janas_b200: nvcc failed on {src}:\n{r.stdout}\n{r.stderr}")
         done[0] += 1
         return obj
 
-    say(f"compiling {len(srcs)} kernel files for sm_100a into {build_dir} (first call only)")
+    say(f"compiling {len(srcs)} files (kernels for sm_100a, engine) into {build_dir} "
+        f"(first call only)")
     th = threading.Thread(target=ticker, daemon=True)
     th.start()
     try:
@@ -165,7 +180,7 @@ def _compile(nvcc: str, build_dir: str, fingerprint: str, verbose: bool) -> str:
             json.dump({"fingerprint": fingerprint, "sources": srcs, "flags": NVCC_FLAGS}, f)
     finally:
         stop.set()
-    say(f"kernels built in {time.time() - t0:.0f} s")
+    say(f"library built in {time.time() - t0:.0f} s")
     return os.path.join(build_dir, LIB_NAME)
 
 

@@ -632,6 +632,39 @@ extern "C" int jb_gemm_tc_swiglu(const void *A, const void *W, void *out_act, in
 // Reads and clears the error word: 0, or which wait ran out first (1: a free
 // stage, 2: a loaded stage, 3: the accumulator, 4: a load in flight).
 // Synchronizes the device.
+// A wait that nothing ends, to show that a bounded wait runs out as it should: one
+// warp, one mbarrier that no thread and no copy ever arrives at, the products' own
+// wait with a limit of limit_cycles.  The kernel returns when the limit has passed
+// and leaves code 9 in the products' error word (jb_gemm_tc_error reads and clears
+// it).  Nothing faults and nothing is left waiting.
+__global__ void wait_selftest_kernel(long long limit_cycles)
+{
+    __shared__ __align__(8) unsigned long long bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        mbar_init(smem_u32(&bar), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (threadIdx.x == 0)
+        mbar_wait_limit(smem_u32(&bar), 0, &abort_flag, &g_gemm_tc_error, 9, limit_cycles);
+}
+
+// Runs the kernel above and waits for it; limit_cycles is cut to 20 million (about
+// ten milliseconds).  Returns 0, or JB_ELAUNCH.
+extern "C" int jb_wait_selftest(long long limit_cycles)
+{
+    if (limit_cycles < 1000)
+        limit_cycles = 1000;
+    if (limit_cycles > 20000000ll)
+        limit_cycles = 20000000ll;
+    wait_selftest_kernel<<<1, 32>>>(limit_cycles);
+    if (cudaGetLastError() != cudaSuccess)
+        return JB_ELAUNCH;
+    return cudaDeviceSynchronize() == cudaSuccess ? JB_OK : JB_ELAUNCH;
+}
+
 extern "C" int jb_gemm_tc_error(void)
 {
     int v = 0, zero = 0;

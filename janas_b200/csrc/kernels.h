@@ -24,6 +24,7 @@
 extern "C" {
 #endif
 
+int jb_page(void);
 int jb_embed(const void *table, int table_dt, const int32_t *tokens, float *x, int n, int dm,
              cudaStream_t st);
 int jb_rmsnorm(float *x, const float *delta, int S, long long delta_stride,
@@ -77,7 +78,13 @@ int jb_gemm_tc(const void *A, const void *W, float *out, int n, int m, int k, in
 int jb_gemm_tc_swiglu(const void *A, const void *W, void *out_act, int n, int ff, int k,
                       cudaStream_t st);
 int jb_gemm_tc_error(void);
+int jb_wait_selftest(long long limit_cycles);
 int jb_sample_small_cap(void);
+int jb_sample_needs_big(int V, int top_k);
+int jb_sampler_set(const int32_t *slots, int n, const unsigned long long *seeds,
+                   const float *temperature, const int32_t *top_k, const float *top_p,
+                   const float *min_p, unsigned long long *rng_out, float *temperature_out,
+                   int32_t *top_k_out, float *top_p_out, float *min_p_out, cudaStream_t st);
 long long jb_sample_scratch(int rows, int V);
 int jb_sample_launches(int V, long long big_cap, int sampled);
 int jb_sample(const float *logits, int rows, int V, const int32_t *row_slot,

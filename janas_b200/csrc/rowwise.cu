@@ -360,6 +360,10 @@ static int norm_threads(int dm)
 
 using namespace jb;
 
+// Positions a page of the cache holds, as the kernels were compiled; the host side
+// checks its own number against it when an engine is made.
+extern "C" int jb_page(void) { return PAGE; }
+
 extern "C" int jb_embed(const void *table, int table_dt, const int32_t *tokens, float *x, int n,
                         int dm, cudaStream_t st)
 {

@@ -609,12 +609,61 @@ sample_kernel(const float *__restrict__ logits, int V, const int32_t *__restrict
                   rng + slot, out + row, forced ? forced + row : nullptr, tmp, &sh_idx, &sh_val);
 }
 
+// Writes the settings of n sequences to their slots' places in the per-slot arrays.
+__global__ void sampler_set_kernel(const int32_t *__restrict__ slots, int n,
+                                   const unsigned long long *__restrict__ seeds,
+                                   const float *__restrict__ temperature,
+                                   const int32_t *__restrict__ top_k,
+                                   const float *__restrict__ top_p, const float *__restrict__ min_p,
+                                   unsigned long long *rng_out, float *temperature_out,
+                                   int32_t *top_k_out, float *top_p_out, float *min_p_out)
+{
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n)
+        return;
+    int s = slots[i];
+    rng_out[s] = seeds[i];
+    temperature_out[s] = temperature[i];
+    top_k_out[s] = top_k[i];
+    top_p_out[s] = top_p[i];
+    min_p_out[s] = min_p[i];
+}
+
 }  // namespace jb
 
 using namespace jb;
 
 // The most candidates a row can keep without the caller's scratch.
 extern "C" int jb_sample_small_cap() { return CHUNK_KEEP; }
+
+// Whether a row with temperature > 0 and this top_k over V logits goes the long way
+// (all candidates sorted in the caller's scratch): top_k off or above what a chunk's
+// list keeps, or so many chunks that their lists do not fit the merge.  The test is
+// the kernel's own (sample_kernel); callers size their scratch by it.
+extern "C" int jb_sample_needs_big(int V, int top_k)
+{
+    int chunks = (V + CHUNK - 1) / CHUNK;
+    bool short_way = top_k > 0 && top_k <= CHUNK_KEEP && top_k < V && chunks * CHUNK_KEEP <= MERGE_CAP;
+    return short_way ? 0 : 1;
+}
+
+// The sampling settings of n sequences (arrays of n values on the device) to the
+// places of their slots in the per-slot arrays; each random sequence starts at its
+// seed (src/llm/sample.c:118).  An ordinary launch: it runs after all that is ahead
+// of it in the stream.
+extern "C" int jb_sampler_set(const int32_t *slots, int n, const unsigned long long *seeds,
+                              const float *temperature, const int32_t *top_k, const float *top_p,
+                              const float *min_p, unsigned long long *rng_out,
+                              float *temperature_out, int32_t *top_k_out, float *top_p_out,
+                              float *min_p_out, cudaStream_t st)
+{
+    if (n <= 0)
+        return JB_OK;
+    sampler_set_kernel<<<(n + 127) / 128, 128, 0, st>>>(slots, n, seeds, temperature, top_k, top_p,
+                                                        min_p, rng_out, temperature_out, top_k_out,
+                                                        top_p_out, min_p_out);
+    return launch_status();
+}
 
 // 64-bit words of scratch that jb_sample wants for rows x V logits.
 extern "C" long long jb_sample_scratch(int rows, int V)

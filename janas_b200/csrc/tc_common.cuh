@@ -46,8 +46,8 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity)
 // Waits for the phase with this parity to complete.  Gives up when another
 // thread of the CTA has given up (*abort) or after WAIT_CYCLES; then it records
 // `code` in *err (a device word the host reads), raises *abort and returns false.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort,
-                                          int *err, int code)
+__device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, volatile int *abort,
+                                                int *err, int code, long long limit_cycles)
 {
     if (mbar_try(bar, parity))
         return true;
@@ -57,12 +57,18 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
             return true;
         if (*abort)
             return false;
-        if (clock64() - t0 > WAIT_CYCLES) {
+        if (clock64() - t0 > limit_cycles) {
             *abort = 1;
             atomicCAS(err, 0, code);
             return false;
         }
     }
+}
+
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort,
+                                          int *err, int code)
+{
+    return mbar_wait_limit(bar, parity, abort, err, code, WAIT_CYCLES);
 }
 
 // Brings a tensor map (a kernel parameter) into the descriptor cache ahead of its

@@ -32,13 +32,11 @@ class Replayer:
         out = None
         if entries:
             try:
-                logits = self.engine.step(entries)
+                out = self.engine.step_numpy(entries)
             except Exception:
                 for rid in fresh:      # a refused step leaves no new request behind
                     self.engine.free_sequence(self.slots.pop(rid))
                 raise
-            if logits is not None:
-                out = logits.detach().to("cpu").numpy().astype("<f4", copy=False)
         for rid in req.get("end", []):
             if rid in self.slots:
                 self.engine.free_sequence(self.slots.pop(rid))

@@ -60,7 +60,7 @@ def write_random_model(model_dir: str, config, seed: int,
     """Writes ``config.json`` and ``model.safetensors`` for ``config`` (a
     registered architecture's typed configuration) with weights from ``seed``,
     stored as ``dtype`` (bfloat16 or float32)."""
-    from ..engine.model import expected_tensors  # the same list the loader checks
+    from . import expected_tensors  # the same list the loader checks
 
     if dtype not in (torch.bfloat16, torch.float32):
         raise ValueError("random weights are stored as bfloat16 or float32")

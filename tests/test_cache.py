@@ -1,5 +1,6 @@
-"""The cache's bookkeeping on the host: no page or slot is lost, held twice or
-freed twice; window groups give pages back; a refused step changes nothing."""
+"""The cache's bookkeeping (the library's, cache/cache.cpp) on the host: no page or
+slot is lost, held twice or freed twice; window groups give pages back; a refused
+step changes nothing.  The two tests of per-sequence state need the device."""
 import numpy as np
 import pytest
 import torch
@@ -41,7 +42,7 @@ def test_slot_pool():
 def make(max_tokens=512, max_seqs=4, window=0, state=False):
     kv = [KVSpec(2, 16), KVSpec(2, 16), KVSpec(1, 32, window) if window else KVSpec(2, 16), None]
     st = [None, StateSpec((3,)) if state else None, None, None]
-    return Cache(kv, st, max_tokens, max_seqs, torch.float32, "cpu")
+    return Cache(kv, st, max_tokens, max_seqs, torch.float32, "cuda:0" if state else "cpu")
 
 
 def test_groups_have_storage_of_their_own():
@@ -105,12 +106,14 @@ def test_window_group_gives_pages_back():
     assert win.pool.n_free == win.pool.n_pages and full.pool.n_free == full.pool.n_pages
 
 
+@pytest.mark.gpu
 def test_state_is_zero_for_a_new_sequence():
     c = make(state=True)
     s = c.new_sequence()
     c.mixer_state[1][s] += 5.0
     c.free_sequence(s)
     t = c.new_sequence()
+    torch.cuda.synchronize()
     assert t == s and float(c.mixer_state[1][t].abs().sum()) == 0.0
 
 
@@ -186,6 +189,7 @@ def test_truncate_gives_pages_back_and_knows_what_cannot_be_undone():
     assert win.pool.n_free == win.pool.n_pages and full.pool.n_free == full.pool.n_pages
 
 
+@pytest.mark.gpu
 def test_truncate_with_a_state_of_fixed_size_goes_back_to_nothing_only():
     c = make(state=True)
     s = c.new_sequence()

@@ -1,8 +1,12 @@
 """The generation loop's decisions, without a device: which requests form a
-batch, when a sequence ends, and the whole loop over a fake engine."""
+batch, when a sequence ends, and the whole loop (the library's, engine/generate.cpp)
+over a stand-in for the engine."""
 import numpy as np
 import pytest
 
+from standin import StandIn
+
+import janas_b200
 from janas_b200.engine import generate as G
 from janas_b200.engine.generate import (FINISH_CONTEXT, FINISH_LENGTH, FINISH_STOP, GenOptions,
                                         Request, finish_reason, plan_batches, tokens_needed)
@@ -19,7 +23,7 @@ def test_plan_batches():
     assert plan_batches([10] * 5, [5] * 5, 2, 10_000, 1000) == [[0, 1], [2, 3], [4]]
     # the cache holds 256 tokens: 100+30 -> 192, 10+5 -> 64, then full
     assert plan_batches([100, 10, 10, 200], [30, 5, 5, 20], 8, 256, 1000) == [[0, 1], [2], [3]]
-    with pytest.raises(ValueError, match="need"):
+    with pytest.raises(janas_b200.CacheFull, match="need"):
         plan_batches([300], [10], 8, 256, 1000)
 
 
@@ -41,63 +45,31 @@ def test_options():
         GenOptions(top_p=1.5).validate(100)
 
 
-class FakeEngine:
+class FakeEngine(StandIn):
     """Stands in for the engine: the "model" answers token t with (t + 1) % 50,
     and the bookkeeping of slots is checked as the loop goes."""
 
-    class _Spec:
-        vocab_size = 50
-
-    class _Model:
-        pass
-
-    def __init__(self, max_positions=40, max_tokens=64 * 4, max_seqs=3):
-        from janas_b200.cache import SlotPool
-        self.model = self._Model()
-        self.model.spec = self._Spec()
-        self.max_positions = max_positions
-        self.device = "cpu"
-        self.pool = SlotPool(max_seqs)
-        self.len = {}
+    def __init__(self, max_positions=40, max_tokens=64 * 4, max_seqs=3, **kw):
+        super().__init__(max_positions, max_tokens, max_seqs, **kw)
         self.steps = []
-        eng = self
 
-        class _Cache:
-            max_seqs = eng.pool.n_slots
-            max_tokens = 64 * 4
-
-            def set_samplers(self, slots, options):
-                pass
-        self.cache = _Cache()
-        self.cache.max_tokens = max_tokens
-
-    def new_sequence(self):
-        s = self.pool.take()
-        self.len[s] = 0
-        return s
-
-    def free_sequence(self, s):
-        self.pool.give_back(s)
-        del self.len[s]
-
-    def length(self, s):
-        return self.len[s]
-
-    def step(self, entries):
-        self.steps.append([(e.slot, len(e.tokens)) for e in entries])
+    def run(self, entries):
+        self.steps.append([(e["slot"], len(e["tokens"])) for e in entries])
         out = []
         for e in entries:
-            assert self.pool.live(e.slot)
-            assert self.len[e.slot] + len(e.tokens) <= self.max_positions
-            self.len[e.slot] += len(e.tokens)
-            out.append((e.tokens[-1] + 1) % 50)
+            assert self.pool.live(e["slot"])
+            assert self.len[e["slot"]] + len(e["tokens"]) <= self.max_positions
+            self.len[e["slot"]] += len(e["tokens"])
+            if e["want"]:
+                out.append((e["tokens"][-1] + 1) % 50)
         return out
 
 
-def run(monkeypatch, eng, reqs, **kw):
-    monkeypatch.setattr(G, "_pick", lambda engine, logits, slots, sampled, big:
-                        (np.asarray(logits), 0))
-    return G.generate(eng, reqs, **kw)
+def run(monkeypatch, eng, reqs, max_batch=None, **kw):
+    """The loop takes as many sequences at a time as the stand-in has free slots."""
+    res = G.generate(eng, reqs, **kw)
+    assert eng.error is None
+    return res
 
 
 def test_loop_unequal_prompts_stops_and_batches(monkeypatch):
@@ -105,7 +77,7 @@ def test_loop_unequal_prompts_stops_and_batches(monkeypatch):
     reqs = [Request([1, 2, 3], 5), Request([10], 3, GenOptions(eos=12)),
             Request([20, 21], 0), Request([30] * 38, 10), Request([5], 2, GenOptions(stop=[6]))]
     st = G.GenStats()
-    res = run(monkeypatch, eng, reqs, max_batch=3, stats=st)
+    res = run(monkeypatch, eng, reqs, stats=st)
     assert res[0].tokens == [4, 5, 6, 7, 8] and res[0].finish == FINISH_LENGTH
     assert res[1].tokens == [11, 12] and res[1].finish == FINISH_STOP      # the stop token counts
     assert res[2].tokens == [] and res[2].finish == FINISH_LENGTH
@@ -121,35 +93,38 @@ def test_loop_unequal_prompts_stops_and_batches(monkeypatch):
 
 def test_loop_refuses_bad_requests(monkeypatch):
     eng = FakeEngine()
-    with pytest.raises(ValueError, match="empty"):
+    with pytest.raises(janas_b200.LLMError, match="empty") as e:
         run(monkeypatch, eng, [Request([], 3)])
-    with pytest.raises(ValueError, match="context"):
+    assert e.value.code == janas_b200.EINVAL
+    with pytest.raises(janas_b200.LLMError, match="context") as e:
         run(monkeypatch, eng, [Request([1] * 41, 3)])
+    assert e.value.code == janas_b200.ELIMIT
     assert eng.pool.n_free == 3
 
 
 class AheadEngine(FakeEngine):
     """A stand-in that also takes steps fed by the step before them, as the real
     engine does from its device buffer; it checks the rules of that way."""
-    decodes_ahead = True
 
     def __init__(self, *a, **kw):
-        super().__init__(*a, **kw)
+        super().__init__(*a, ahead=True, **kw)
         self.last = None            # (slots, tokens) of the step begun last
         self.under_way = 0
         self.begun = []             # (slots, fed by the host?)
+        self.pending = {}
 
-    def free_sequence(self, s):
-        super().free_sequence(s)
+    def on_free(self, s):
         if self.last is not None and s in self.last[0]:
             self.last = None
 
-    def decode_begin(self, slots, tokens, sampled=False, big=None):
+    def do_decode_begin(self, a):
+        slots, tokens = a["slots"], a["tokens"]
         assert self.under_way < 2
+        from_host = tokens is not None
         if tokens is None:
             assert self.last is not None and self.last[0] == list(slots)
             tokens = self.last[1]
-        self.begun.append((list(slots), self.last is None or tokens is not self.last[1]))
+        self.begun.append((list(slots), from_host))
         out = []
         for s, t in zip(slots, tokens):
             assert self.pool.live(s)
@@ -158,11 +133,13 @@ class AheadEngine(FakeEngine):
             out.append((t + 1) % 50)
         self.last = (list(slots), out)
         self.under_way += 1
-        return out
+        key = len(self.begun)
+        self.pending[key] = out
+        return {"pending": key}
 
-    def decode_end(self, pending):
+    def do_decode_end(self, a):
         self.under_way -= 1
-        return np.asarray(pending)
+        return {"tokens": self.pending.pop(a["pending"])}
 
 
 def test_goes_on_unless_stopped_is_finish_reason_with_the_token_left_open():
@@ -182,8 +159,8 @@ def test_loop_one_step_ahead_gives_the_same_results(monkeypatch):
             Request([7], 9, GenOptions(stop=[11])), Request([8, 9], 9)]
     plain_eng, eng = FakeEngine(), AheadEngine()
     st0, st = G.GenStats(), G.GenStats()
-    want = run(monkeypatch, plain_eng, reqs, max_batch=3, stats=st0)
-    res = run(monkeypatch, eng, reqs, max_batch=3, stats=st)
+    want = run(monkeypatch, plain_eng, reqs, stats=st0)
+    res = run(monkeypatch, eng, reqs, stats=st)
     assert [(r.tokens, r.finish) for r in res] == [(r.tokens, r.finish) for r in want]
     assert eng.pool.n_free == 3 and not eng.len and eng.under_way == 0
     assert (st.new_tokens, st.batches, st.prompt_tokens) == \
@@ -210,11 +187,13 @@ def test_loop_one_step_ahead_on_requests_drawn_at_random(monkeypatch):
             reqs.append(Request([int(t) for t in rng.integers(0, 50, size=n)],
                                 int(rng.integers(0, 12)), GenOptions(eos=eos, stop=stop)))
         max_batch = int(rng.integers(1, 4))
-        a, b = FakeEngine(max_positions=ctx), AheadEngine(max_positions=ctx)
+        a = FakeEngine(max_positions=ctx, max_seqs=max_batch)
+        b = AheadEngine(max_positions=ctx, max_seqs=max_batch)
         sa, sb = G.GenStats(), G.GenStats()
-        want = run(monkeypatch, a, reqs, max_batch=max_batch, stats=sa)
-        got = run(monkeypatch, b, reqs, max_batch=max_batch, stats=sb)
+        want = run(monkeypatch, a, reqs, stats=sa)
+        got = run(monkeypatch, b, reqs, stats=sb)
         assert [(r.tokens, r.finish) for r in got] == [(r.tokens, r.finish) for r in want], case
-        assert b.pool.n_free == 3 and not b.len and b.under_way == 0
+        assert b.pool.n_free == max_batch and not b.len and b.under_way == 0
+        a.close(); b.close()
         assert sb.new_tokens == sa.new_tokens and sb.batches == sa.batches
         assert sa.passes <= sb.passes <= sa.passes + sa.batches

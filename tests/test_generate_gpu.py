@@ -180,7 +180,7 @@ def test_replayed_decode_steps_equal_launched_ones(dtype):
                                                                 max_batch=4, max_tokens=2048))
         assert m.engine.use_graphs
         a, _ = m.generate_batch(ps, news, opts)
-        assert len(m.engine._graphs) >= 3            # several batch sizes were captured
+        assert m.engine.n_graphs >= 3                # several batch sizes were captured
         m.engine.use_graphs = False
         b, _ = m.generate_batch(ps, news, opts)
         assert a == b
@@ -198,13 +198,13 @@ def test_old_decode_graphs_are_dropped_and_captured_again():
     m = janas_b200.open(model_dir("B"), janas_b200.LLMParams(n_ctx=256, dtype="bfloat16",
                                                             max_batch=4, max_tokens=1024))
     first, _ = m.generate_batch(ps, news)
-    shapes = len(m.engine._graphs)
+    shapes = m.engine.n_graphs
     assert shapes >= 3
-    m.engine._graphs.clear()
-    m.engine.max_graphs = 2
+    m.engine.drop_graphs()
+    m.engine.set_max_graphs(2)
     again, _ = m.generate_batch(ps, news)
     assert again == first
-    assert len(m.engine._graphs) == 2
+    assert m.engine.n_graphs == 2
     third, _ = m.generate_batch(ps, news)       # the first shapes were dropped meanwhile
     assert third == first
     m.engine.cache.check()
@@ -245,7 +245,7 @@ def test_steps_fed_on_the_device_equal_steps_fed_by_the_host(dtype):
                     nxt = eng.decode_begin(slots, None, sampled) if i < 11 else None
                     got.append(eng.decode_end(cur).tolist())
                     cur = nxt
-                assert len(eng._graphs) == 2        # positions below 256, then from 256 on
+                assert eng.n_graphs == 2            # positions below 256, then from 256 on
                 with pytest.raises(StepError):      # other sequences than the last step's
                     eng.decode_begin(slots[:2], None, sampled)
                 eng.free_sequence(slots[2])

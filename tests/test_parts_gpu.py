@@ -89,9 +89,6 @@ def test_swiglu_part_bfloat16(rows, hidden, inter, monkeypatch):
     bfloat16."""
     from janas_b200.config import PartSpec
     from janas_b200.csrc import ops
-    fused_calls = []
-    real = ops.linear_swiglu
-    monkeypatch.setattr(ops, "linear_swiglu", lambda a, w: fused_calls.append(1) or real(a, w))
     ffn = build("feed_forward", PartSpec("swiglu", {"hidden_size": hidden,
                                                     "intermediate_size": inter}), torch.bfloat16)
     w = give(ffn, "mlp", seed=3, dtype=torch.bfloat16)
@@ -100,7 +97,8 @@ def test_swiglu_part_bfloat16(rows, hidden, inter, monkeypatch):
     got = ffn.forward(context([0], [rows], torch.bfloat16), h.to(DEV)).sum(0).cpu()
     assert ops.gemm_tc_error() == 0
     uncut = ops.linear_parts(rows, 2 * inter, hidden) == 1
-    assert bool(fused_calls) == (rows >= ffn.FUSED_FROM or (rows <= ffn.FUSED_UP_TO and uncut))
+    assert ffn.info()["fused_last"] == (rows >= ffn.FUSED_FROM or
+                                         (rows <= ffn.FUSED_UP_TO and uncut))
     assert uncut == (hidden == 72)          # the cases cover both
     want = plain.swiglu(h.float(), w, "mlp.", "bfloat16")
     err = (got - want).abs().max(dim=1).values                    # row by row: row 3 is large
@@ -166,11 +164,14 @@ def test_a_toy_position_encoding_is_registered_and_used_by_the_attention_part():
 
     @register_position_encoding("toy_linear_angles")
     class LinearAngles(PositionEncoding):
+        last = None         # the instance the library built last, for the test to ask
+
         def __init__(self, spec, dtype, device):
             super().__init__(spec, dtype, device)
             self.rotary_dim = int(spec.params["rotary_dim"])
             self.step = float(spec.params["step"])
             self.cos = self.sin = None
+            LinearAngles.last = self
 
         def table(self, n):
             half = self.rotary_dim // 2
@@ -211,7 +212,7 @@ def test_a_toy_position_encoding_is_registered_and_used_by_the_attention_part():
     q = plain.rms_norm((x @ w["attn.q_proj.weight"].T).view(n, nh, hd), w["attn.q_norm.weight"], 1e-6)
     k = plain.rms_norm((x @ w["attn.k_proj.weight"].T).view(n, nkv, hd), w["attn.k_norm.weight"], 1e-6)
     v = (x @ w["attn.v_proj.weight"].T).view(n, nkv, hd)
-    cs, sn = att.position.table(n)
+    cs, sn = LinearAngles.last.table(n)
     q, k = plain.rope_neox(q, cs, sn), plain.rope_neox(k, cs, sn)
     want = plain.attention(q, k, v, 0).reshape(n, nh * hd) @ w["attn.o_proj.weight"].T
     assert (got - want).abs().max() <= 5e-6 * want.abs().max()
@@ -342,18 +343,18 @@ def toy_plain(w, toks):
 
 
 def test_a_model_of_toy_parts_is_registered_built_and_stepped():
-    from janas_b200.engine import DecoderModel, Engine
+    from janas_b200.engine import Engine, expected_tensors
     from janas_b200.weights import random_tensors
     from helpers import rel_err, run_trace, trace_batches, trace_tail, trace_whole
     register_toys()
     spec = toy_spec()
-    model = DecoderModel(spec, torch.float32, DEV)
-    names = model.tensors()
+    names = expected_tensors(spec)
     assert "toy.layers.0.mix.gain" in names and "toy.layers.1.self_attn.q_proj.weight" in names
     assert not any("layers.1.mlp" in n for n in names)         # the toy feed-forward has no tensors
     ts = dict(random_tensors(names, 9, torch.float32))
-    model.load(ts.items())
-    eng = Engine(model, max_tokens=1024, max_seqs=4)
+    eng = Engine.from_spec(spec, {n: t.to(DEV) for n, t in ts.items()}, dtype="float32",
+                           max_tokens=1024, max_seqs=4)
+    assert not eng.use_graphs               # the toys do not say that they can be captured
     # the cache: entries 1 and 2 share a group (same KV shape), entry 4 reads entry 1's,
     # entries 0 and 3 have a state each
     assert len(eng.cache.groups) == 1 and eng.cache.groups[0].entries == [1, 2]

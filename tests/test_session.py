@@ -3,79 +3,59 @@ truncation do, and that several sessions move on together."""
 import numpy as np
 import pytest
 
-from janas_b200.cache import SlotPool
-from janas_b200.engine import generate as G
+import janas_b200
 from janas_b200.engine import session as S
 from janas_b200.engine.generate import GenOptions
+from standin import StandIn
 
 
-class FakeEngine:
+class FakeEngine(StandIn):
     """The "model" answers token t at position p with (t + p) % 50.  It records the
     steps and checks that every position is fed exactly once, in order."""
 
-    class _Spec:
-        vocab_size = 50
-
     def __init__(self, max_positions=40, extend=True, can_go_back=True):
-        eng = self
-
-        class _Model:
-            spec = self._Spec()
-
-            def supports(self, kind):
-                return kind != "extend" or extend
-
-        class _Cache:
-            def set_samplers(self, slots, options):
-                eng.seeds = {s: o.seed for s, o in zip(slots, options)}
-
-        self.model, self.cache = _Model(), _Cache()
-        self.max_positions = max_positions
-        self.pool = SlotPool(4)
-        self.len, self.fed, self.steps = {}, {}, []
+        super().__init__(max_positions, max_seqs=4, extend=extend)
+        self.fed, self.steps = {}, []
         self.can_go_back = can_go_back
 
-    def new_sequence(self):
-        s = self.pool.take()
-        self.len[s], self.fed[s] = 0, []
-        return s
+    def on_new(self, s):
+        self.fed[s] = []
 
-    def free_sequence(self, s):
-        self.pool.give_back(s)
-        del self.len[s]
-
-    def length(self, s):
-        return self.len[s]
-
-    def truncate_sequence(self, s, n):
+    def truncate(self, s, n):
         if n != 0 and n != self.len[s] and not self.can_go_back:
             return False
         self.len[s] = n
         del self.fed[s][n:]
         return True
 
-    def step(self, entries):
-        lens = [len(e.tokens) for e in entries]
-        pos0 = [self.len[e.slot] for e in entries]
+    def run(self, entries):
+        lens = [len(e["tokens"]) for e in entries]
+        pos0 = [self.len[e["slot"]] for e in entries]
         kind = ("prefill" if not any(pos0) else "decode" if all(n == 1 for n in lens)
                 else "extend")
-        assert self.model.supports(kind)
+        assert kind != "extend" or self.extend
         self.steps.append((kind, lens))
         out = []
         for e in entries:
-            assert self.len[e.slot] + len(e.tokens) <= self.max_positions
-            for t in e.tokens:
-                self.fed[e.slot].append(t)
-            self.len[e.slot] += len(e.tokens)
-            for w in e.want:
-                out.append((e.tokens[w] + self.len[e.slot] - len(e.tokens) + w) % 50)
-        return out or None
+            slot, toks = e["slot"], e["tokens"]
+            assert self.len[slot] + len(toks) <= self.max_positions
+            self.fed[slot] += toks
+            self.len[slot] += len(toks)
+            if e["want"]:
+                out.append((toks[-1] + self.len[slot] - 1) % 50)
+        return out
 
 
-@pytest.fixture(autouse=True)
-def pick(monkeypatch):
-    monkeypatch.setattr(S, "_pick", lambda engine, logits, slots, sampled, big:
-                        (np.asarray(logits), 0))
+def slot_of(eng, session):
+    """The stand-in's slot of a session: sessions take slots in the order they were made."""
+    return session._slot
+
+
+def make(eng, options=None):
+    before = set(eng.len)
+    s = S.Session(eng, options)
+    (s._slot,) = set(eng.len) - before
+    return s
 
 
 def expected(hist):
@@ -84,8 +64,8 @@ def expected(hist):
 
 def test_turns_feed_every_token_once():
     eng = FakeEngine()
-    s = S.Session(eng, GenOptions(seed=9))
-    assert eng.seeds == {s.slot: 9}
+    s = make(eng, GenOptions(seed=9))
+    assert eng.seeds == {s._slot: 9}
     with pytest.raises(S.SessionError, match="empty"):
         s.next()
     s.append([3, 4, 5])
@@ -100,7 +80,7 @@ def test_turns_feed_every_token_once():
     want = expected(s.tokens())
     assert s.next() == (S.OK, want)
     assert eng.steps[-1] == ("extend", [3])
-    assert eng.fed[s.slot] == s.tokens()[:-1]           # every token once, in order
+    assert eng.fed[s._slot] == s.tokens()[:-1]           # every token once, in order
     assert s.stats.new_tokens == 4 and s.stats.prompt_tokens == 2 + 2
     s.close()
     assert eng.pool.n_free == 4
@@ -110,19 +90,19 @@ def test_turns_feed_every_token_once():
 
 def test_a_model_that_cannot_extend_goes_token_by_token():
     eng = FakeEngine(extend=False)
-    s = S.Session(eng)
+    s = make(eng)
     s.append([1, 2, 3])
     s.next()
     s.append([9, 9, 9])
     want = expected(s.tokens())
     assert s.next() == (S.OK, want)
     assert eng.steps[-4:] == [("decode", [1])] * 4
-    assert eng.fed[s.slot] == s.tokens()[:-1]
+    assert eng.fed[s._slot] == s.tokens()[:-1]
 
 
 def test_context_full_and_append_limits():
     eng = FakeEngine(max_positions=6)
-    s = S.Session(eng)
+    s = make(eng)
     with pytest.raises(S.SessionError, match="vocabulary") as e:
         s.append([50])
     assert e.value.code == -1
@@ -140,13 +120,13 @@ def test_context_full_and_append_limits():
 def test_truncate_computes_the_last_kept_token_again():
     for can in (True, False):
         eng = FakeEngine(can_go_back=can)
-        s = S.Session(eng)
+        s = make(eng)
         s.append([5, 6, 7, 8])
         first = [s.next()[1] for _ in range(3)]
         s.truncate(5)                      # the prompt and the first reply token
         assert s.length == 5 and s.computed == (4 if can else 0)
         assert [s.next()[1] for _ in range(2)] == first[1:]
-        assert eng.fed[s.slot] == s.tokens()[:-1]
+        assert eng.fed[s._slot] == s.tokens()[:-1]
         s.reset()
         assert (s.length, s.computed) == (0, 0)
         with pytest.raises(S.SessionError):
@@ -155,7 +135,7 @@ def test_truncate_computes_the_last_kept_token_again():
 
 def test_sessions_move_on_together():
     eng = FakeEngine()
-    a, b, c = S.Session(eng), S.Session(eng), S.Session(eng)
+    a, b, c = make(eng), make(eng), make(eng)
     a.append([1, 2, 3]); b.append([4]); c.append([9] * 39 + [1, 2])
     toks, st = S.sessions_step(eng, [a, b, c])
     assert st == [S.OK, S.OK, S.FULL] and toks[2] is None
@@ -169,7 +149,7 @@ def test_sessions_move_on_together():
     assert eng.steps[-1] == ("decode", [1, 1])
     with pytest.raises(S.SessionError, match="twice"):
         S.sessions_step(eng, [a, a])
-    other = S.Session(FakeEngine())
+    other = make(FakeEngine())
     other.append([1])
     with pytest.raises(S.SessionError, match="another engine"):
         S.sessions_step(eng, [a, other])
@@ -183,7 +163,7 @@ def test_sessions_driven_at_random_feed_every_position_once_and_in_order():
     rng = np.random.default_rng(5)
     for kind in range(3):
         eng = FakeEngine(max_positions=60, extend=kind != 1, can_go_back=kind != 2)
-        ss = [S.Session(eng) for _ in range(3)]
+        ss = [make(eng) for _ in range(3)]
         for it in range(600):
             s = ss[int(rng.integers(3))]
             op = rng.random()
@@ -215,7 +195,7 @@ def test_sessions_driven_at_random_feed_every_position_once_and_in_order():
                 s.reset()
             for x in ss:
                 assert x.computed <= max(x.length - 1, 0) or x.computed == x.length == 0
-                assert eng.fed[x.slot] == x.tokens()[:x.computed]
+                assert eng.fed[x._slot] == x.tokens()[:x.computed]
         for x in ss:
             x.close()
         assert eng.pool.n_free == 4

@@ -1,5 +1,7 @@
-"""Weights: the safetensors reader and writer, the loader's one error, the
-random-weights mode (no GPU)."""
+"""Weights (no GPU): model folders written and read back, resident dtypes, the one
+error that lists every mismatch, malformed files, shards.  The reader and the
+checks are the library's own (weights/safetensors.cpp, weights/loader.cpp), reached
+through its C interface."""
 import json
 import os
 import struct
@@ -9,11 +11,9 @@ import pytest
 import torch
 
 from janas_b200.config import config_from_dict
-from janas_b200.engine import expected_tensors
-from janas_b200.weights import (Checkpoint, SafetensorsError, WeightError, load_tensors,
-                                random_tensors, resident_dtype, write_random_model,
-                                write_safetensors)
-from janas_b200.weights.spec import INT_TABLE, MATRIX, NORM, TensorSpec
+from janas_b200.weights import (INT_TABLE, MATRIX, NORM, SafetensorsError, TensorSpec, WeightError,
+                                check_folder, expected_tensors, list_folder, random_tensors,
+                                read_tensor, resident_dtype, write_random_model, write_safetensors)
 from tiny import TINY
 
 
@@ -23,19 +23,25 @@ def folder(tmp_path, name="A", seed=0, dtype=torch.bfloat16):
     return d
 
 
+def bits(t: torch.Tensor) -> np.ndarray:
+    return t.view(torch.uint16).numpy() if t.dtype == torch.bfloat16 else t.numpy()
+
+
 def test_written_folder_reads_back_with_the_library(tmp_path):
     from safetensors.torch import load_file
     d = folder(tmp_path, "B", 1)
     ref = load_file(os.path.join(d, "model.safetensors"))
     exp = expected_tensors(config_from_dict(TINY["B"]).to_model_spec())
-    got = dict(load_tensors(d, exp, torch.bfloat16))
-    assert set(got) == set(ref)
+    check_folder(d, exp)
+    have = list_folder(d)
+    assert set(have) == set(ref) == set(exp)
     for k in ref:
-        assert got[k].dtype == torch.bfloat16
-        assert torch.equal(got[k], ref[k]), k
-    wide = dict(load_tensors(d, exp, torch.float32))
-    assert all(t.dtype == torch.float32 for t in wide.values())
-    assert torch.equal(wide["model.norm.weight"], ref["model.norm.weight"].float())
+        assert have[k] == ("BF16", tuple(ref[k].shape))
+        got = read_tensor(d, k, "bfloat16", ref[k].shape)
+        assert np.array_equal(got, bits(ref[k])), k
+    # widened exactly when the whole model is computed in 32-bit
+    wide = read_tensor(d, "model.norm.weight", "float32", ref["model.norm.weight"].shape)
+    assert np.array_equal(wide, ref["model.norm.weight"].float().numpy())
 
 
 def test_random_weights_are_deterministic_and_distributed(tmp_path):
@@ -58,14 +64,20 @@ def test_random_weights_are_deterministic_and_distributed(tmp_path):
 
 def test_a_tensor_stored_in_32_bit_stays_so(tmp_path):
     d = folder(tmp_path, "A", 0, torch.float32)
-    exp = expected_tensors(config_from_dict(TINY["A"]).to_model_spec())
-    got = dict(load_tensors(d, exp, torch.bfloat16))
-    assert all(t.dtype == torch.float32 for t in got.values())
-    assert resident_dtype("BF16", MATRIX, torch.bfloat16) == torch.bfloat16
-    assert resident_dtype("F16", NORM, torch.bfloat16) == torch.bfloat16
-    assert resident_dtype("F32", MATRIX, torch.bfloat16) == torch.float32
-    assert resident_dtype("BF16", MATRIX, torch.float32) == torch.float32
-    assert resident_dtype("I64", INT_TABLE, torch.bfloat16) == torch.int32
+    assert all(dt == "F32" for dt, _ in list_folder(d).values())
+    assert resident_dtype("BF16", MATRIX, "bfloat16") == "bfloat16"
+    assert resident_dtype("F16", NORM, "bfloat16") == "bfloat16"
+    assert resident_dtype("F32", MATRIX, "bfloat16") == "float32"
+    assert resident_dtype("BF16", MATRIX, "float32") == "float32"
+    assert resident_dtype("I64", INT_TABLE, "bfloat16") == "int32"
+
+
+def test_half_precision_is_converted_exactly_where_it_fits(tmp_path):
+    d = str(tmp_path)
+    x = torch.tensor([0.5, -1.25, 3.0e-5, 65504.0, 6.0e-8, 0.0, -0.0], dtype=torch.float16)
+    write_safetensors(os.path.join(d, "model.safetensors"), [("x", x)])
+    assert np.array_equal(read_tensor(d, "x", "float32", x.shape), x.float().numpy())
+    assert np.array_equal(read_tensor(d, "x", "bfloat16", x.shape), bits(x.float().bfloat16()))
 
 
 def test_one_error_lists_everything(tmp_path):
@@ -81,7 +93,7 @@ def test_one_error_lists_everything(tmp_path):
     ts["model.norm.weight"] = torch.zeros(64, dtype=torch.int32)
     write_safetensors(os.path.join(d, "model.safetensors"), ts.items())
     with pytest.raises(WeightError) as ei:
-        list(load_tensors(d, exp, torch.bfloat16))
+        check_folder(d, exp)
     e = ei.value
     assert e.missing == ["model.layers.0.self_attn.q_norm.weight",
                          "model.layers.1.mlp.down_proj.weight"]
@@ -103,32 +115,39 @@ def test_untied_model_needs_its_head(tmp_path):
     os.makedirs(d)
     write_safetensors(os.path.join(d, "model.safetensors"), ts.items())
     with pytest.raises(WeightError, match="lm_head.weight"):
-        list(load_tensors(d, exp, torch.bfloat16))
+        check_folder(d, exp)
 
 
 def test_malformed_files(tmp_path):
     d = str(tmp_path)
     p = os.path.join(d, "model.safetensors")
     with pytest.raises(SafetensorsError, match="no model.safetensors"):
-        Checkpoint(d)
+        list_folder(d)
     open(p, "wb").write(b"abc")
     with pytest.raises(SafetensorsError, match="too short"):
-        Checkpoint(d)
+        list_folder(d)
     open(p, "wb").write(struct.pack("<Q", 1000) + b"{}")
     with pytest.raises(SafetensorsError, match="header length"):
-        Checkpoint(d)
+        list_folder(d)
+    open(p, "wb").write(struct.pack("<Q", 5) + b"{nope")
+    with pytest.raises(SafetensorsError, match="not JSON"):
+        list_folder(d)
     hdr = json.dumps({"t": {"dtype": "F32", "shape": [4], "data_offsets": [0, 16]}}).encode()
     open(p, "wb").write(struct.pack("<Q", len(hdr)) + hdr + b"\0" * 8)      # truncated data
     with pytest.raises(SafetensorsError, match="outside the file"):
-        Checkpoint(d)
+        list_folder(d)
     hdr = json.dumps({"t": {"dtype": "F32", "shape": [5], "data_offsets": [0, 16]}}).encode()
     open(p, "wb").write(struct.pack("<Q", len(hdr)) + hdr + b"\0" * 16)
     with pytest.raises(SafetensorsError, match="does not match shape"):
-        Checkpoint(d)
+        list_folder(d)
     hdr = json.dumps({"t": {"dtype": "F8_E4M3", "shape": [16], "data_offsets": [0, 16]}}).encode()
     open(p, "wb").write(struct.pack("<Q", len(hdr)) + hdr + b"\0" * 16)
     with pytest.raises(SafetensorsError, match="not read"):
-        Checkpoint(d)
+        list_folder(d)
+    hdr = json.dumps({"t": {"dtype": "F32", "shape": [2 ** 40, 2 ** 40], "data_offsets": [0, 0]}}).encode()
+    open(p, "wb").write(struct.pack("<Q", len(hdr)) + hdr)
+    with pytest.raises(SafetensorsError, match="does not match shape"):
+        list_folder(d)
 
 
 def test_shards(tmp_path):
@@ -142,7 +161,18 @@ def test_shards(tmp_path):
                               "z": "model-00002-of-00002.safetensors"}},
               open(os.path.join(d, "model.safetensors.index.json"), "w"))
     exp = {"x": TensorSpec((2, 3)), "y": TensorSpec((4,), NORM), "z": TensorSpec((3,), INT_TABLE)}
-    got = dict(load_tensors(d, exp, torch.bfloat16))
-    assert torch.equal(got["x"], a["x"]) and got["x"].dtype == torch.float32
-    assert got["y"].dtype == torch.bfloat16
-    assert got["z"].dtype == torch.int32 and got["z"].tolist() == [1, 2, 3]
+    check_folder(d, exp)
+    assert list_folder(d) == {"x": ("F32", (2, 3)), "y": ("BF16", (4,)), "z": ("I64", (3,))}
+    assert np.array_equal(read_tensor(d, "x", "float32", (2, 3)), a["x"].numpy())
+    assert read_tensor(d, "z", "int32", (3,)).tolist() == [1, 2, 3]
+    big = {"z": torch.tensor([1, 2 ** 40], dtype=torch.int64)}
+    write_safetensors(os.path.join(d, "model-00002-of-00002.safetensors"),
+                      list(b.items())[:1] + list(big.items()))
+    with pytest.raises(SafetensorsError, match="does not fit int32"):
+        read_tensor(d, "z", "int32", (2,))
+    # a tensor that the index names and its shard lacks
+    json.dump({"weight_map": {"x": "model-00001-of-00002.safetensors",
+                              "w": "model-00002-of-00002.safetensors"}},
+              open(os.path.join(d, "model.safetensors.index.json"), "w"))
+    with pytest.raises(SafetensorsError, match="is not in"):
+        list_folder(d)
