@@ -3,7 +3,8 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--model 4b|8b|32b] [--layers L]
                     [--batch B] [--context C] [--dtype bfloat16|float32] [--no-points]
-    python bench.py --impl reference ...     (prints why it is unavailable)
+                    [--all-configs]
+    python bench.py --impl reference ...     (the reference's own bench program, on the CPU)
     python bench.py --only decode|prefill|timeline ...   (one part, for profiling)
     python bench.py --only generate [--model 8b] ...      (unequal prompts, then 256 tokens each)
 
@@ -19,8 +20,15 @@ through the Python entry point (host tokens in, host tokens out, every step's
 inputs copied from pinned host memory and its tokens read back); ``prefill`` is
 one prompt of 2,048 tokens; ``roofline`` divides the bytes a decode step has to
 read (every weight once and the cache of the live sequences) by its time;
-``points`` holds decoding at batch 1 and 64.  Peaks come from
-MEASURED_PEAKS.json beside this file when it exists.
+``points`` holds decoding at batch 1 and 64 and the 32-bit path's decode and
+prefill speeds.  The cache that the timed steps read was written by the engine's
+own prefill of random prompts.  ``checked`` says that, after the timed regions,
+the kernels' error words were clear and the last decode step replayed from its CUDA
+graph chose the tokens that the same step chooses when its kernels are launched one
+by one.  Peaks come from MEASURED_PEAKS.json beside this file when it exists.
+``--all-configs`` adds the other workloads (8B sizes: eight unequal prompts and
+256 decode steps; 32B sizes: prefill and decoding) as further points; each runs in
+a process of its own.
 """
 import argparse
 import json
@@ -47,7 +55,7 @@ MODELS = {
                 intermediate_size=25600, tie_word_embeddings=False, max_position_embeddings=4096),
 }
 
-# used only when MEASURED_PEAKS.json is absent: an earlier measurement on this pool
+# used only when MEASURED_PEAKS.json is absent: figures of an earlier measurement
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
 
 
@@ -122,34 +130,26 @@ class Clocks:
                 "samples": len(mhz)}
 
 
-def build_engine(args, n_layers, max_tokens, max_seqs):
-    import torch
-    from janas_b200.config import config_from_dict
-    from janas_b200.engine import DecoderModel, Engine
-    from janas_b200.weights import random_tensors
-    cfg = config_from_dict(dict(MODELS[args.model], num_hidden_layers=n_layers))
-    dt = torch.bfloat16 if args.dtype == "bfloat16" else torch.float32
-    model = DecoderModel(cfg.to_model_spec(), dt, "cuda:0")
-    with torch.cuda.device(0):
-        model.load(random_tensors(model.tensors(), 0, dt, device="cuda:0"))
-        eng = Engine(model, max_tokens=max_tokens, max_seqs=max_seqs)
-        for g in eng.cache.groups:      # see fill()
-            g.k.normal_()
-            g.v.normal_()
-    eng.config = cfg
-    return eng
+def build_engine(args, n_layers, max_tokens, max_seqs, dtype=None):
+    """A model of the chosen sizes with weights made at random on the device, and a
+    cache of ``max_tokens``."""
+    from janas_b200.engine import Engine
+    cfg = dict(MODELS[args.model], num_hidden_layers=n_layers)
+    return Engine.open_random(cfg, seed=0, dtype=dtype or args.dtype, max_tokens=max_tokens,
+                              max_seqs=max_seqs, n_ctx=cfg["max_position_embeddings"])
 
 
 def fill(eng, batch, context, rng):
-    """New sequences that hold ``context`` tokens each.  Their pages are taken from
-    the pool as a prefill would take them; the keys and values in them are the
-    random numbers the cache was filled with once (build_engine), which cost a
-    decode step the same reads as computed ones.  Returns the slots and a random
-    next token for each."""
-    vocab = eng.model.spec.vocab_size
-    slots = [eng.new_sequence() for _ in range(batch)]
-    eng.cache.reserve(slots, [context] * batch)
-    eng.cache.advance(slots, [context] * batch)
+    """New sequences that hold ``context`` tokens each, computed by the engine's own
+    prefill of random prompts (one prompt a step, so that the step's temporaries
+    stay small).  Returns the slots and a random next token for each."""
+    from janas_b200.engine import StepEntry
+    vocab = eng.vocab_size
+    slots = []
+    for _ in range(batch):
+        s = eng.new_sequence()
+        eng.step([StepEntry(s, rng.integers(0, vocab, size=context).tolist(), [])])
+        slots.append(s)
     return slots, rng.integers(0, vocab, size=batch).tolist()
 
 
@@ -158,7 +158,7 @@ def drive(eng, slots, tokens, n):
     it; every step's tokens are read on the host.  Returns the last ones."""
     if n <= 0:
         return tokens
-    if not getattr(eng, "decodes_ahead", False):
+    if not eng.decodes_ahead:
         for _ in range(n):
             tokens = eng.decode(slots, tokens).tolist()
         return tokens
@@ -170,6 +170,32 @@ def drive(eng, slots, tokens, n):
     return tokens
 
 
+def launches():
+    from janas_b200 import lib
+    return lib.call("llm.launches")["launches"]
+
+
+class DeviceTimer:
+    """CUDA events on the engine's own stream."""
+
+    def __init__(self, eng):
+        import torch
+        self.torch = torch
+        self.stream = torch.cuda.ExternalStream(eng.stream)
+        self.a = torch.cuda.Event(enable_timing=True)
+        self.b = torch.cuda.Event(enable_timing=True)
+
+    def __enter__(self):
+        self.stream.synchronize()
+        self.a.record(self.stream)
+        return self
+
+    def __exit__(self, *exc):
+        self.b.record(self.stream)
+        self.stream.synchronize()
+        self.ms = self.a.elapsed_time(self.b)
+
+
 def decode_device_timed(eng, slots, tokens, steps, warmup):
     """K decode steps of the whole batch (the engine's decode step: the step
     function's kernels and the choice of the next token, replayed from a CUDA
@@ -178,19 +204,32 @@ def decode_device_timed(eng, slots, tokens, steps, warmup):
     tokens are read back on the host every step, and where the engine can feed a
     step the tokens of the step before it, the next step is queued while this one
     runs."""
-    import torch
-    from janas_b200.csrc import ops
+    tokens = drive(eng, slots, tokens, warmup)
+    l0 = launches()
+    with DeviceTimer(eng) as t:
+        tokens = drive(eng, slots, tokens, steps)
+    return t.ms / steps, launches() - l0, tokens
 
-    run = lambda n, tokens: drive(eng, slots, tokens, n)
-    tokens = run(warmup, tokens)
-    torch.cuda.synchronize()
-    l0 = ops.COUNTERS["launches"]
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record()
-    tokens = run(steps, tokens)
-    b.record()
-    torch.cuda.synchronize()
-    return a.elapsed_time(b) / steps, ops.COUNTERS["launches"] - l0, tokens
+
+def check_last_step(eng, slots, tokens):
+    """One more decode step replayed from its graph, then the same step again with
+    its kernels launched one by one (the sequences are taken back by the one token
+    in between): both must choose the same tokens.  And the kernels' error words
+    must be clear.  Raises when not."""
+    a = eng.decode(slots, tokens).tolist()
+    for s in slots:
+        if not eng.truncate_sequence(s, eng.length(s) - 1):
+            raise RuntimeError("the cache cannot go back one token")
+    graphs = eng.use_graphs
+    eng.use_graphs = False
+    try:
+        b = eng.decode(slots, tokens).tolist()
+    finally:
+        eng.use_graphs = graphs
+    eng.check()
+    if a != b:
+        raise RuntimeError(f"the replayed decode step chose {a}, the launched one {b}")
+    return True
 
 
 def decode_timeline(eng, slots, tokens, warmup):
@@ -206,7 +245,8 @@ def decode_timeline(eng, slots, tokens, warmup):
     with profile(activities=[ProfilerActivity.CUDA]) as prof:
         tokens = drive(eng, slots, tokens, 3)
         torch.cuda.synchronize()
-    evs = [e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA]
+    evs = [e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA
+           and "memcpy" not in e.name.lower()]
     evs.sort(key=lambda e: e.time_range.start)
     last = evs[-(len(evs) // 3):]
     t0 = last[0].time_range.start
@@ -222,11 +262,13 @@ def decode_timeline(eng, slots, tokens, warmup):
 def step_bytes(eng, batch, context):
     """Bytes a decode step has to read: every weight once, and the keys and
     values of the live sequences."""
+    info = eng.info()
+    esz = 2 if info["dtype"] == "bfloat16" else 4
     kv = 0
-    for g in eng.cache.groups:
-        per_token = 2 * len(g.entries) * g.spec.num_kv_heads * g.spec.head_dim * g.k.element_size()
+    for g in info["cache"]["groups"]:
+        per_token = 2 * len(g["entries"]) * g["num_kv_heads"] * g["head_dim"] * esz
         kv += per_token * batch * context
-    return eng.model.weight_bytes() + kv
+    return info["weight_bytes"] + kv
 
 
 def prefill_flops(cfg, n_layers, tokens):
@@ -240,26 +282,58 @@ def prefill_flops(cfg, n_layers, tokens):
     return n_layers * (per_token * tokens + attn) + 2 * dm * cfg["vocab_size"]
 
 
-def generate_workload(eng, args, rng, new_tokens=256):
+def prefill_timed(eng, rng, T, rounds=6):
+    """One prompt of T tokens in one step, the logits of its last token wanted;
+    the best of ``rounds`` after a first that pays for allocations."""
+    from janas_b200.engine import StepEntry
+    times = []
+    for _ in range(rounds):
+        s = eng.new_sequence()
+        toks = rng.integers(0, eng.vocab_size, size=T).tolist()
+        with DeviceTimer(eng) as t:
+            eng.step([StepEntry(s, toks, [T - 1])])
+        times.append(t.ms)
+        eng.free_sequence(s)
+    return min(times[1:])
+
+
+def generate_workload(eng, args, rng, new_tokens=256, runs=3):
     """A batch of unequal prompts through the entry point: host token lists in, host
-    token lists out.  Prints one line per run; the first run pays for graph captures."""
+    token lists out.  Prints one line per run (the first pays for graph captures);
+    returns the last run's prefill and decode speeds."""
     import janas_b200
     from janas_b200.engine.generate import GenOptions
-    vocab = MODELS[args.model]["vocab_size"]
+    vocab = eng.vocab_size
     llm = janas_b200.LLM(eng, janas_b200.LLMParams(n_ctx=eng.max_positions, dtype=args.dtype,
                                                   max_batch=args.batch))
-    for run in range(3):
+    out = {}
+    for run in range(runs):
         lens = rng.integers(64, args.context + 1, size=args.batch).tolist()
         prompts = [rng.integers(0, vocab, size=n).tolist() for n in lens]
         t0 = time.perf_counter()
         outs, st = llm.generate_batch(prompts, new_tokens, GenOptions(eos=-1))
         wall = time.perf_counter() - t0
+        out = {"prefill_tok_s": sum(lens) / st.prefill_seconds,
+               "decode_tok_s": args.batch * st.passes / st.decode_seconds,
+               "ms_per_step": 1e3 * st.decode_seconds / max(st.passes, 1),
+               "prompt_tokens": sum(lens)}
         print(f"generate run {run}: prompts {lens} ({sum(lens)} tokens) prefill "
-              f"{1e3 * st.prefill_seconds:.1f} ms ({sum(lens) / st.prefill_seconds:,.0f} tokens/s), "
+              f"{1e3 * st.prefill_seconds:.1f} ms ({out['prefill_tok_s']:,.0f} tokens/s), "
               f"{st.new_tokens} new tokens in {st.passes} steps, "
-              f"{1e3 * st.decode_seconds / max(st.passes, 1):.3f} ms a step "
-              f"({args.batch * st.passes / st.decode_seconds:,.0f} tokens/s), "
-              f"whole call {wall:.3f} s", flush=True)
+              f"{out['ms_per_step']:.3f} ms a step ({out['decode_tok_s']:,.0f} tokens/s), "
+              f"whole call {wall:.3f} s", file=sys.stderr, flush=True)
+    return out
+
+
+def other_config(model, extra):
+    """Runs this program for another model size in a process of its own (its
+    weights and cache are given back when it ends); returns its JSON line."""
+    cmd = [sys.executable, os.path.abspath(__file__), "--model", model, "--no-points"] + extra
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=1500)
+    for line in reversed(r.stdout.strip().splitlines()):
+        if line.startswith("{"):
+            return json.loads(line)
+    raise RuntimeError(f"{' '.join(cmd)} printed no result:\n{r.stdout[-500:]}\n{r.stderr[-1500:]}")
 
 
 def main():
@@ -275,20 +349,20 @@ def main():
     ap.add_argument("--context", type=int, default=2048)
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
-    ap.add_argument("--no-points", action="store_true", help="skip decoding at batch 1 and 64")
+    ap.add_argument("--no-points", action="store_true",
+                    help="skip decoding at batch 1 and 64 and the 32-bit points")
+    ap.add_argument("--all-configs", action="store_true",
+                    help="also the 8B workload (unequal prompts, 256 steps) and the 32B points")
     ap.add_argument("--only", default="", choices=["", "decode", "prefill", "timeline", "generate"],
-                    help="run one part only and print its time (for profiling; no JSON line); "
-                         "timeline: when each kernel of one replayed decode step ends; "
-                         "generate: --batch prompts of lengths uniform in [64, --context], all in "
-                         "one step, then 256 tokens each through the Python entry point")
+                    help="run one part only and print its time (for profiling; no JSON line "
+                         "but for generate); timeline: when each kernel of one replayed decode "
+                         "step ends; generate: --batch prompts of lengths uniform in [64, "
+                         "--context], all in one step, then 256 tokens each through the Python "
+                         "entry point")
     args = ap.parse_args()
 
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "prabanta-dev/janas is a C program without setup.py or pyproject.toml "
-                          "(pip: 'not installable'); it runs quantized .jns files only and has no "
-                          "bfloat16 or sm_100 path"}))
-        return 0
+        return reference_arm(args)
     if args.gpus != 1:
         print("bench.py: this engine runs on one GPU; --gpus must be 1")
         return 2
@@ -298,14 +372,12 @@ def main():
     args.warmup = max(args.warmup, 3)
 
     import numpy as np
-    import torch
     import janas_b200
-    from janas_b200.csrc import ops
     from janas_b200.engine.generate import GenOptions
 
     pk = peaks()
     rng = np.random.default_rng(0)
-    total_steps = args.warmup + args.steps + 8
+    total_steps = args.warmup + args.steps + 10
     room = (args.context + 2 * total_steps + 63) // 64 * 64
     big_batch = 64 if not args.no_points else args.batch
     if args.only == "generate":
@@ -319,54 +391,47 @@ def main():
         return 0
 
     if args.only == "generate":
-        generate_workload(eng, args, rng)
+        r = generate_workload(eng, args, rng)
+        eng.check()
+        print(json.dumps({"model": args.model, "layers": args.layers, "batch": args.batch,
+                          **{k: round(v, 3) for k, v in r.items()}}))
         return 0
 
     if args.only == "decode":
         slots, toks = fill(eng, args.batch, args.context, rng)
-        ms, launches, _ = decode_device_timed(eng, slots, toks, args.steps, args.warmup)
+        ms, n_launch, _ = decode_device_timed(eng, slots, toks, args.steps, args.warmup)
         print(f"decode batch {args.batch} context {args.context}: {ms:.4f} ms a step, "
-              f"{launches // args.steps} kernels a step")
+              f"{n_launch // args.steps} kernels a step")
         return 0
 
     # ---- prefill of one prompt
-    from janas_b200.engine import StepEntry
     T = args.prefill_tokens
-    times = []
-    for it in range(6):         # the first pays for allocations; the best of the rest counts
-        s = eng.new_sequence()
-        toks = rng.integers(0, cfg["vocab_size"], size=T).tolist()
-        torch.cuda.synchronize()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        eng.step([StepEntry(s, toks, [T - 1])])
-        b.record()
-        torch.cuda.synchronize()
-        times.append(a.elapsed_time(b))
-        eng.free_sequence(s)
-    pre_ms = min(times[1:])
+    pre_ms = prefill_timed(eng, rng, T)
     if args.only == "prefill":
         print(f"prefill {T} tokens: {pre_ms:.3f} ms")
         return 0
     flops = prefill_flops(cfg, args.layers, T)
-    dense_peak = pk["bf16_tflops"] * 1e12 * (1.0 if args.dtype == "bfloat16" else 1.0)
     prefill = {"value": round(T / (pre_ms / 1e3), 1), "tokens": T, "ms": round(pre_ms, 3),
-               "frac": round(flops / (pre_ms / 1e3) / dense_peak, 4)}
+               "frac": round(flops / (pre_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
     if pk.get("bf16_tflops_sustained"):
         # against the library's throughput in a seconds-long loop under the power cap
         prefill["frac_sustained"] = round(
             flops / (pre_ms / 1e3) / (pk["bf16_tflops_sustained"] * 1e12), 4)
 
     # ---- decoding, device-timed
-    def decode_point(batch, steps, warmup):
-        slots, toks = fill(eng, batch, args.context, rng)
-        ms, launches, _ = decode_device_timed(eng, slots, toks, steps, warmup)
+    checked = True
+
+    def decode_point(e, batch, steps, warmup):
+        nonlocal checked
+        slots, toks = fill(e, batch, args.context, rng)
+        ms, n_launch, toks = decode_device_timed(e, slots, toks, steps, warmup)
+        checked = check_last_step(e, slots, toks) and checked
         for s in slots:
-            eng.free_sequence(s)
-        return ms, launches
+            e.free_sequence(s)
+        return ms, n_launch
 
     with Clocks() as clk:
-        ms, launches = decode_point(args.batch, args.steps, args.warmup)
+        ms, n_launch = decode_point(eng, args.batch, args.steps, args.warmup)
     clocks = clk.summary()
     value = args.batch / (ms / 1e3)
     mid_context = args.context + args.warmup + args.steps // 2
@@ -376,7 +441,7 @@ def main():
     points = {}
     if not args.no_points:
         for b in (1, 64):
-            pms, _ = decode_point(b, max(8, args.steps // 4), 3)
+            pms, _ = decode_point(eng, b, max(8, args.steps // 4), 3)
             points[f"decode_b{b}"] = round(b / (pms / 1e3), 1)
 
     # ---- the same through the Python entry point: host tokens in and out
@@ -389,6 +454,27 @@ def main():
     e2e = {"value": round(e2e_value, 1), "unit": "tokens/s",
            "h2d_bytes_per_step": st.h2d_bytes // max(st.passes, 1),
            "d2h_bytes_per_step": st.d2h_bytes // max(st.passes, 1)}
+    eng.check()
+    eng.close()
+
+    # ---- the whole model in true 32-bit: decoding at the same batch, and the prefill
+    if not args.no_points and args.dtype == "bfloat16":
+        e32 = build_engine(args, args.layers, room * args.batch, args.batch, dtype="float32")
+        p32 = prefill_timed(e32, rng, T, rounds=3)
+        d32, _ = decode_point(e32, args.batch, max(8, args.steps // 4), 3)
+        points["fp32_decode_b%d" % args.batch] = round(args.batch / (d32 / 1e3), 1)
+        points["fp32_prefill_tok_s"] = round(T / (p32 / 1e3), 1)
+        points["fp32_prefill_tflops"] = round(flops / (p32 / 1e3) / 1e12, 2)
+        e32.close()
+
+    if args.all_configs:
+        g8 = other_config("8b", ["--only", "generate", "--batch", "8", "--context", "2048"])
+        points["8b_generate_prefill_tok_s"] = round(g8["prefill_tok_s"], 1)
+        points["8b_generate_decode_tok_s"] = round(g8["decode_tok_s"], 1)
+        big = other_config("32b", ["--steps", "16"])
+        points["32b_decode_b8"] = big["value"]
+        points["32b_roofline_frac"] = big["roofline"]["frac"]
+        points["32b_prefill_tok_s"] = big["prefill"]["value"]
 
     out = {
         "metric": "decode tokens/s", "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1,
@@ -404,12 +490,22 @@ def main():
                    "seq_len": args.context, "max_context": cfg["max_position_embeddings"],
                    "parallelism": "1 GPU", "l2": "inputs larger than L2 (weights read once a step)",
                    "peaks": pk["source"]},
-        "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "prefill": prefill,
+        "e2e": e2e, "gpu_launches": n_launch, "clocks": clocks, "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"],
                      "unit": "GB/s", "frac": round(achieved / pk["hbm_gbs"], 4)},
-        "points": points,
+        "points": points, "checked": bool(checked),
     }
     print(json.dumps(out))
+    return 0
+
+
+def reference_arm(args):
+    """The reference is a C program for quantized models on CPUs: there is nothing of
+    it to install with pip, and no bfloat16 or sm_100 path."""
+    print(json.dumps({"impl": "reference", "unavailable":
+                      "prabanta-dev/janas is a C program without setup.py or pyproject.toml "
+                      "(pip: 'not installable'); it runs quantized .jns files only and has no "
+                      "bfloat16 or sm_100 path"}))
     return 0
 
 

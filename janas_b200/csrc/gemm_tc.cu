@@ -519,7 +519,34 @@ extern "C" int jb_gemm_tc_splits(int n, int m, int k)
 // time and the time to bring its operands in (measured: about 116 GB/s per SM),
 // which is why narrower tiles are not proportionally faster.  Every part beyond
 // the first also costs the writing and the reading back of a float partial sum.
+static int many_tokens_tile_choice(int n, int m, int k, int splits, double *time_us);
+static int g_forced_tile = 0;   // tokens per tile that the next products must take; 0: the choice below
+static int g_last_tile = 0;     // what the last product over many tokens took
+
 static int many_tokens_tile(int n, int m, int k, int splits, double *time_us = nullptr)
+{
+    if (g_forced_tile && !time_us)
+        return g_last_tile = g_forced_tile;
+    int best = many_tokens_tile_choice(n, m, k, splits, time_us);
+    if (!time_us)
+        g_last_tile = best;
+    return best;
+}
+
+// For tests: makes every product over more than 128 tokens take tiles of this many
+// tokens (128, 160, 192, 224 or 256; 0: the library's own choice again), and says
+// which width the last such product took.  Every width computes the same sums; the
+// choice is one of speed.
+extern "C" int jb_gemm_tc_force_tile(int tokens)
+{
+    if (tokens != 0 && tokens != 128 && tokens != 160 && tokens != 192 && tokens != 224 && tokens != 256)
+        return JB_EINVAL;
+    g_forced_tile = tokens;
+    return JB_OK;
+}
+extern "C" int jb_gemm_tc_last_tile(void) { return g_last_tile; }
+
+static int many_tokens_tile_choice(int n, int m, int k, int splits, double *time_us)
 {
     int sms = sm_count();
     const int choices[5] = {256, 224, 192, 160, 128};

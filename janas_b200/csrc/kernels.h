@@ -78,6 +78,8 @@ int jb_gemm_tc(const void *A, const void *W, float *out, int n, int m, int k, in
 int jb_gemm_tc_swiglu(const void *A, const void *W, void *out_act, int n, int ff, int k,
                       cudaStream_t st);
 int jb_gemm_tc_error(void);
+int jb_gemm_tc_force_tile(int tokens);
+int jb_gemm_tc_last_tile(void);
 int jb_wait_selftest(long long limit_cycles);
 int jb_sample_small_cap(void);
 int jb_sample_needs_big(int V, int top_k);

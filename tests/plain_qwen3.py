@@ -181,8 +181,10 @@ def swiglu(x: torch.Tensor, w: Dict[str, torch.Tensor], prefix: str,
 
 def forward(c: Dict, w: Dict[str, torch.Tensor], tokens: Sequence[int],
             rounding: Optional[str] = None, round_weights: bool = False,
-            trace: Optional[List[torch.Tensor]] = None) -> torch.Tensor:
-    """Logits [len(tokens), vocab] of one whole sequence from position 0.
+            trace: Optional[List[torch.Tensor]] = None,
+            rows: Optional[Sequence[int]] = None) -> torch.Tensor:
+    """Logits [len(tokens), vocab] of one whole sequence from position 0 (with
+    ``rows``: of those positions only; the layers still see every token).
 
     Pre-norm blocks: x += Attn(RMSNorm(x)); x += FFN(RMSNorm(x))
     (src/llm/model.c:743-796); then the final norm and the head, which is the
@@ -201,6 +203,8 @@ def forward(c: Dict, w: Dict[str, torch.Tensor], tokens: Sequence[int],
         x = x + swiglu(h, w, p + "mlp.", rounding)
         if trace is not None:
             trace.append(x.clone())
+    if rows is not None:
+        x = x[list(rows)]
     h = _round(rms_norm(x, w["model.norm.weight"], eps), rounding)
     head = w.get("lm_head.weight")
     if head is None:
