@@ -499,13 +499,170 @@ def main():
     return 0
 
 
+def write_q8_gguf(path, cfg, seed=0):
+    """A random model of ``cfg``'s sizes in the reference's eight-bit weight type
+    (Q8_0: blocks of 32 signed bytes and a half-precision scale), as a GGUF version 3
+    file (src/llm/gguf.c:6-9; the keys its converter wants: tools/gguf2jns.c:377-399;
+    tensor names: src/llm/model_load.c:403-503,999-1007).  Written tensor by tensor."""
+    import struct
+    import numpy as np
+    L, dm, ff, V = (cfg["num_hidden_layers"], cfg["hidden_size"], cfg["intermediate_size"],
+                    cfg["vocab_size"])
+    hd = cfg["head_dim"]
+    qd, kvd = cfg["num_attention_heads"] * hd, cfg["num_key_value_heads"] * hd
+    names = [("token_embd.weight", (V, dm)), ("output_norm.weight", (dm,))]
+    for l in range(L):
+        g = f"blk.{l}."
+        names += [(g + "attn_norm.weight", (dm,)), (g + "attn_q.weight", (qd, dm)),
+                  (g + "attn_k.weight", (kvd, dm)), (g + "attn_v.weight", (kvd, dm)),
+                  (g + "attn_output.weight", (dm, qd)), (g + "attn_q_norm.weight", (hd,)),
+                  (g + "attn_k_norm.weight", (hd,)), (g + "ffn_norm.weight", (dm,)),
+                  (g + "ffn_gate.weight", (ff, dm)), (g + "ffn_up.weight", (ff, dm)),
+                  (g + "ffn_down.weight", (dm, ff))]
+    if not cfg["tie_word_embeddings"]:
+        names.append(("output.weight", (V, dm)))
+    string = lambda t: struct.pack("<Q", len(t.encode())) + t.encode()
+    u32 = lambda k, v: string(k) + struct.pack("<II", 4, v)
+    f32 = lambda k, v: string(k) + struct.pack("<If", 6, v)
+    text = lambda k, v: string(k) + struct.pack("<I", 8) + string(v)
+    kvs = [text("general.architecture", "qwen3"), text("general.name", "random qwen3"),
+           u32("general.alignment", 32), u32("qwen3.block_count", L),
+           u32("qwen3.context_length", cfg["max_position_embeddings"]),
+           u32("qwen3.embedding_length", dm), u32("qwen3.feed_forward_length", ff),
+           u32("qwen3.attention.head_count", cfg["num_attention_heads"]),
+           u32("qwen3.attention.head_count_kv", cfg["num_key_value_heads"]),
+           u32("qwen3.attention.key_length", hd), u32("qwen3.attention.value_length", hd),
+           f32("qwen3.attention.layer_norm_rms_epsilon", cfg["rms_norm_eps"]),
+           f32("qwen3.rope.freq_base", cfg["rope_theta"])]
+    size = lambda shape: (int(np.prod(shape)) // 32 * 34) if len(shape) == 2 else shape[0] * 4
+    infos, at = b"", 0
+    for name, shape in names:
+        at = (at + 31) // 32 * 32
+        dims = list(reversed(shape))                 # the row's length first
+        infos += string(name) + struct.pack("<I", len(dims))
+        infos += b"".join(struct.pack("<Q", d) for d in dims)
+        infos += struct.pack("<IQ", 8 if len(shape) == 2 else 0, at)
+        at += size(shape)
+    head = b"GGUF" + struct.pack("<IQQ", 3, len(names), len(kvs)) + b"".join(kvs) + infos
+    head += b"\0" * ((len(head) + 31) // 32 * 32 - len(head))
+    rng = np.random.default_rng(seed)
+    with open(path, "wb") as f:
+        f.write(head)
+        at = 0
+        for name, shape in names:
+            pad = (at + 31) // 32 * 32 - at
+            f.write(b"\0" * pad)
+            at += pad
+            if len(shape) == 1:
+                raw = (1.0 + 0.1 * rng.standard_normal(shape[0])).astype("<f4").tobytes()
+            else:
+                # weights of about N(0, 0.02): uniform bytes (standard deviation 73) times a scale
+                rows, blocks = shape[0], shape[1] // 32
+                raw = np.empty((rows, blocks, 34), dtype=np.uint8)
+                raw[..., :2] = np.frombuffer(np.float16(0.02 / 73.0).tobytes(), dtype=np.uint8)
+                raw[..., 2:] = rng.integers(-127, 128, size=(rows, blocks, 32), dtype=np.int8).view(np.uint8)
+                raw = raw.tobytes()
+            f.write(raw)
+            at += len(raw)
+
+
 def reference_arm(args):
-    """The reference is a C program for quantized models on CPUs: there is nothing of
-    it to install with pip, and no bfloat16 or sm_100 path."""
-    print(json.dumps({"impl": "reference", "unavailable":
-                      "prabanta-dev/janas is a C program without setup.py or pyproject.toml "
-                      "(pip: 'not installable'); it runs quantized .jns files only and has no "
-                      "bfloat16 or sm_100 path"}))
+    """The reference's own generation program on this machine's CPU.
+
+    prabanta-dev/janas is a C program for quantized models on CPUs (and, through a
+    graphics API, on GPUs); pip has nothing of it to install, and it has no bfloat16 or
+    sm_100 path.  What can be run of it here, unmodified, is what its own build
+    (./build.sh release) makes: ``gguf2jns`` and ``llm_gen`` (tests/llm_gen.c, which
+    calls janas_llm_generate on given token ids and reports prefill and decoding
+    speed), kept under baseline/_ref/bin.  This arm writes a random model of the same
+    layer sizes in the reference's eight-bit weight type, converts it with the
+    reference's converter and lets llm_gen read a prompt of --prefill-tokens tokens and
+    write --steps tokens, one sequence, on all CPU cores.  It is not the same
+    configuration (said in the line it prints): eight-bit weights, activations and
+    cache, a CPU, batch 1."""
+    import re
+    import shutil
+    import tempfile
+    import numpy as np
+
+    def unavailable(why):
+        print(json.dumps({"impl": "reference", "unavailable": why}))
+        return 0
+
+    bin_dir = os.path.join(ROOT, "baseline", "_ref", "bin")
+    tools = {t: os.path.join(bin_dir, t) for t in ("gguf2jns", "llm_gen")}
+    if not all(os.path.isfile(p) and os.access(p, os.X_OK) for p in tools.values()):
+        return unavailable(
+            "prabanta-dev/janas is a C program without setup.py or pyproject.toml (pip: 'not "
+            "installable'); its own build's gguf2jns and llm_gen are not under baseline/_ref/bin")
+    cfg = dict(MODELS[args.model])
+    if args.layers > 0:
+        cfg["num_hidden_layers"] = args.layers
+    uid = os.getuid() if hasattr(os, "getuid") else 0
+    work = os.path.join(tempfile.gettempdir(), f"janas_b200_reference_{uid}")
+    os.makedirs(work, exist_ok=True)
+    tag = f"qwen3_{args.model}_{cfg['num_hidden_layers']}l_q8_0"
+    jns = os.path.join(work, tag + ".jns")
+    env = dict(os.environ, HOME=work)          # the reference writes tuning notes below HOME
+    try:
+        if not os.path.isfile(jns):
+            # the GGUF file and the converted copy lie side by side for a moment
+            need = 2.3 * 1.07 * (
+                cfg["vocab_size"] * cfg["hidden_size"] * (1 if cfg["tie_word_embeddings"] else 2) +
+                cfg["num_hidden_layers"] * cfg["hidden_size"] * (
+                    (cfg["num_attention_heads"] * 2 + cfg["num_key_value_heads"] * 2) * cfg["head_dim"] +
+                    3 * cfg["intermediate_size"]))
+            if shutil.disk_usage(work).free < need:
+                return unavailable(f"{work} has no room for a {need / 1e9:.0f} GB model file and its copy")
+            gguf = os.path.join(work, tag + ".gguf")
+            write_q8_gguf(gguf, cfg)
+            r = subprocess.run([tools["gguf2jns"], gguf, jns + ".tmp"], env=env, capture_output=True,
+                               text=True, timeout=1200)
+            os.remove(gguf)
+            if r.returncode != 0:
+                return unavailable("the reference's gguf2jns refused the random model: "
+                                   + (r.stderr or r.stdout).strip()[-300:])
+            os.replace(jns + ".tmp", jns)
+        T, gen = args.prefill_tokens, max(args.steps, 1)
+        if T > 8191:
+            return unavailable("the reference's llm_gen reads prompts of up to 8192 tokens")
+        rng = np.random.default_rng(0)
+        prompt = os.path.join(work, "prompt.int32")
+        rng.integers(0, cfg["vocab_size"], size=T).astype("<i4").tofile(prompt)
+        cmd = [tools["llm_gen"], jns, prompt, str(T), str(gen), "1", "threads=100000",
+               f"ctx={min(cfg['max_position_embeddings'], T + gen + 64)}"]
+        t0 = time.perf_counter()
+        r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=1500)
+        wall = time.perf_counter() - t0
+    except (OSError, subprocess.SubprocessError, MemoryError) as e:
+        return unavailable(f"the reference's tools could not be run here: {type(e).__name__}: {e}"[:400])
+    m = re.search(r"prefill (\d+) tokens ([\d.]+) s \(([\d.]+) token/s\); decode (\d+) tokens "
+                  r"([\d.]+) s \(([\d.]+) token/s\), (\d+) passes", r.stdout)
+    if r.returncode != 0 or not m:
+        return unavailable("the reference's llm_gen did not report speeds: "
+                           + ((r.stderr or "") + (r.stdout or "")).strip()[-300:])
+    n_new, dec_s = int(m.group(4)), float(m.group(5))
+    out = {
+        "impl": "reference", "metric": "decode tokens/s", "value": round(n_new / dec_s, 2),
+        "unit": "tokens/s", "n_gpus": 1, "steps": n_new, "warmup": args.warmup,
+        "ms_per_step": round(1e3 * dec_s / max(int(m.group(7)), 1), 3), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "q8_0 weights, int8 activations and cache",
+        "data": "synthetic", "same_config": False,
+        "differences": "the reference's own CPU code (it has no bfloat16 and no sm_100 path): "
+                       "eight-bit weights, activations and cache; one sequence (batch 1); all CPU "
+                       "cores of this machine; its test program llm_gen (janas_llm_generate), the "
+                       "measured run after one warm-up run",
+        "config": {"model": f"Qwen3-{args.model.upper()} sizes, random Q8_0 weights",
+                   "layers": cfg["num_hidden_layers"], "hidden": cfg["hidden_size"],
+                   "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
+                   "head_dim": cfg["head_dim"], "ffn": cfg["intermediate_size"],
+                   "vocab": cfg["vocab_size"], "global_batch": 1, "seq_len": T,
+                   "parallelism": f"{os.cpu_count()} CPU threads"},
+        "prefill": {"value": float(m.group(3)), "tokens": int(m.group(1)),
+                    "ms": round(1e3 * float(m.group(2)), 1)},
+        "wall_seconds": round(wall, 1),
+    }
+    print(json.dumps(out))
     return 0
 
 

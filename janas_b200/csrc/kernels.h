@@ -69,8 +69,9 @@ int jb_attn_tc_decode_qkv(const float *qkv, int S, long long split_stride, const
                           int n_rows, int nh, int nkv, int hd, int window, float scale,
                           int max_chunks, int chunks_per_cta, cudaStream_t st);
 int jb_attn_tc_error(void);
+long long jb_gemm_simt_scratch(int n, int m, int k);
 int jb_gemm_simt(const void *A, int a_dt, const void *W, int w_dt, float *out, int n, int m, int k,
-                 cudaStream_t st);
+                 float *scratch, cudaStream_t st);
 int jb_gemm_tc_ok(const void *A, const void *W, int n, int m, int k);
 int jb_gemm_tc_splits(int n, int m, int k);
 int jb_gemm_tc(const void *A, const void *W, float *out, int n, int m, int k, int splits,

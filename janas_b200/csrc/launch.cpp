@@ -111,7 +111,11 @@ Stack linear(Device &d, const void *a, DType a_dt, long long n, long long k, con
     }
     out.S = 1;
     out.buf = d.pool.get((size_t)n * (size_t)m * 4);
-    check(jb_gemm_simt(a, a_dt, w.ptr, w.dt, out.data(), ni, mi, ki, d.stream), "linear");
+    long long need = jb_gemm_simt_scratch(ni, mi, ki);
+    Buf scratch;
+    if (need > 0) scratch = d.pool.get((size_t)need * 4);
+    check(jb_gemm_simt(a, a_dt, w.ptr, w.dt, out.data(), ni, mi, ki, scratch.as<float>(), d.stream),
+          "linear", need > 0 ? 2 : 1);
     return out;
 }
 

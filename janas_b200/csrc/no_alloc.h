@@ -31,6 +31,10 @@
 //   that the merge step reads has been written by the same call.  Two calls
 //   whose kernels can overlap on the GPU (different streams, no ordering between
 //   them) race on the array and give wrong results; order them.
+// * Threads: the address found at a device's first call is kept in a plain static
+//   table without a lock.  Two threads that make a device's first call at the same
+//   time both look the address up and both store the same value, which is harmless;
+//   the calls themselves must be ordered anyway, as said above.
 #pragma once
 
 #include <cuda_runtime.h>

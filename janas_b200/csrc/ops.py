@@ -524,8 +524,10 @@ def linear(a: torch.Tensor, weight: torch.Tensor, force_simt: bool = False,
         _check(L.jb_gemm_tc(_p(a), _p(weight), _p(out), n, m, k, S, _stream()), "linear (tcgen05)")
         return out
     out = torch.empty((1, n, m), dtype=torch.float32, device=a.device)
+    need = int(L.jb_gemm_simt_scratch(n, m, k))
+    scratch = torch.empty((need,), dtype=torch.float32, device=a.device) if need else None
     _check(L.jb_gemm_simt(_p(a), _DT[a.dtype], _p(weight), _DT[weight.dtype], _p(out), n, m,
-                          k, _stream()), "linear")
+                          k, _p(scratch), _stream()), "linear", kernels=2 if need else 1)
     return out
 
 

@@ -197,3 +197,38 @@ def test_loop_one_step_ahead_on_requests_drawn_at_random(monkeypatch):
         a.close(); b.close()
         assert sb.new_tokens == sa.new_tokens and sb.batches == sa.batches
         assert sa.passes <= sb.passes <= sa.passes + sa.batches
+
+
+def test_batches_are_planned_against_what_is_free_now(monkeypatch):
+    """Slots and pages held by others (open sessions, a caller's own slots) are not
+    the loop's to plan with: it cuts batches by the free slots and the free tokens of
+    the moment, and with nothing free it fails as a full cache before taking anything."""
+    import ctypes
+    from janas_b200 import lib
+    eng = FakeEngine(max_seqs=3)
+    held = ctypes.c_int32()
+    lib.check(lib.lib().jb_llm_slot_new(eng._h, ctypes.byref(held)))       # someone holds a slot
+    reqs = [Request([1, 2], 3), Request([3], 3), Request([4, 5, 6], 3)]
+    st = G.GenStats()
+    res = run(monkeypatch, eng, reqs, stats=st)
+    assert [r.tokens for r in res] == [[3, 4, 5], [4, 5, 6], [7, 8, 9]]
+    assert st.batches == 2 and [len(s) for s in eng.steps[:1]] == [2]      # two at a time, not three
+    assert eng.pool.n_free == 2 and eng.pool.live(held.value)              # the held slot is untouched
+    eng.max_tokens = 64                                                    # room for one sequence
+    st = G.GenStats()
+    run(monkeypatch, eng, reqs, stats=st)
+    assert st.batches == 3
+    eng.max_tokens = 0
+    with pytest.raises(janas_b200.CacheFull):
+        run(monkeypatch, eng, reqs)
+    eng.max_tokens = 256
+    others = [ctypes.c_int32(), ctypes.c_int32()]
+    for o in others:
+        lib.check(lib.lib().jb_llm_slot_new(eng._h, ctypes.byref(o)))
+    with pytest.raises(janas_b200.CacheFull) as e:                         # no slot is free
+        run(monkeypatch, eng, reqs)
+    assert e.value.code == janas_b200.EFULL
+    assert eng.pool.n_free == 0
+    for o in [held] + others:
+        lib.check(lib.lib().jb_llm_slot_free(eng._h, o.value))
+    assert eng.pool.n_free == 3 and not eng.len

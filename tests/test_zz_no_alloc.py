@@ -61,16 +61,27 @@ def test_noalloc_attention_equals_the_ordinary_entry_point():
             want = ops.attention(q, kc, vc, pos, seq, bt, window, scale, mc)
             out = torch.zeros_like(q)
             torch.cuda.synchronize()
-            free_before = torch.cuda.mem_get_info()[0]
+            # what this process has taken from the device, as its allocator sees it (the
+            # device-wide figure would also move with other users of the GPU)
+            held_before = torch.cuda.memory_reserved()
             rc, got = _call_noalloc(lib, q, kc, vc, pos, seq, bt, window, scale, mc, out=out)
             assert rc == 0, lib.jb_attention_noalloc_error()
             torch.cuda.synchronize()
-            if round_ == 1:        # kernels loaded, address known: the device's free memory stays
-                assert torch.cuda.mem_get_info()[0] == free_before
+            assert torch.cuda.memory_reserved() == held_before
             # the same kernels on the same inputs: the same bits (the tests' tolerance
             # for this kernel against its plain reference is 2^-8 / 5e-6)
             assert torch.equal(got, want), (round_, i)
             assert lib.jb_attention_noalloc_error() == b""
+            # the rows in two unequal parts (row0 > 0 in the second), into one output:
+            # each part's partial results start at the array's beginning
+            halves = torch.zeros_like(q)
+            cut = n // 3
+            for row0, cnt in ((0, cut), (cut, n - cut)):
+                rc, _ = _call_noalloc(lib, q, kc, vc, pos, seq, bt, window, scale, mc, row0=row0,
+                                      n_rows=cnt, out=halves)
+                assert rc == 0, lib.jb_attention_noalloc_error()
+            torch.cuda.synchronize()
+            assert torch.equal(halves, want), (round_, i)
 
 
 def test_noalloc_attention_refuses_what_does_not_fit():
