@@ -130,11 +130,19 @@ class Clocks:
                 "samples": len(mhz)}
 
 
+def model_cfg(args):
+    """The chosen model's config.json; the context it allows grows with --context."""
+    cfg = dict(MODELS[args.model])
+    need = (args.context + 1024 + 1023) // 1024 * 1024
+    cfg["max_position_embeddings"] = max(cfg["max_position_embeddings"], need)
+    return cfg
+
+
 def build_engine(args, n_layers, max_tokens, max_seqs, dtype=None):
     """A model of the chosen sizes with weights made at random on the device, and a
     cache of ``max_tokens``."""
     from janas_b200.engine import Engine
-    cfg = dict(MODELS[args.model], num_hidden_layers=n_layers)
+    cfg = dict(model_cfg(args), num_hidden_layers=n_layers)
     return Engine.open_random(cfg, seed=0, dtype=dtype or args.dtype, max_tokens=max_tokens,
                               max_seqs=max_seqs, n_ctx=cfg["max_position_embeddings"])
 
@@ -383,7 +391,7 @@ def main():
     if args.only == "generate":
         room, big_batch = (args.context + 256 + 127) // 64 * 64, args.batch
     eng = build_engine(args, args.layers, room * max(big_batch, args.batch), max(big_batch, args.batch))
-    cfg = dict(MODELS[args.model])
+    cfg = model_cfg(args)
 
     if args.only == "timeline":
         slots, toks = fill(eng, args.batch, args.context, rng)
