@@ -305,6 +305,43 @@ def prefill_timed(eng, rng, T, rounds=6):
     return min(times[1:])
 
 
+def prefill_timeline(eng, rng, T):
+    """Prints, for one prompt of T tokens recorded with torch.profiler, how much of
+    the step each kernel accounts for: the sum, over its launches, of the time from
+    the end of the kernel before it to its own end (kernels overlap their
+    predecessors, so durations would count the overlap twice)."""
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+    from janas_b200.engine import StepEntry
+    prefill_timed(eng, rng, T, rounds=3)
+    s = eng.new_sequence()
+    toks = rng.integers(0, eng.vocab_size, size=T).tolist()
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        eng.step([StepEntry(s, toks, [T - 1])])
+        torch.cuda.synchronize()
+    eng.free_sequence(s)
+    evs = [e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA
+           and "memcpy" not in e.name.lower()]
+    evs.sort(key=lambda e: e.time_range.start)
+    t0 = evs[0].time_range.start
+    prev_end = t0
+    per = {}
+    for e in evs:
+        gain = max(0.0, e.time_range.end - prev_end)
+        name = e.name.split("(")[0][:60]
+        c = per.setdefault(name, [0, 0.0, 0.0])
+        c[0] += 1
+        c[1] += gain
+        c[2] += e.time_range.end - e.time_range.start
+        prev_end = max(prev_end, e.time_range.end)
+    total = prev_end - t0
+    print(f"prefill of {T} tokens: {total / 1e3:.3f} ms from the first kernel's start to the last one's end")
+    print("launches   on the critical path (us)   share   sum of durations (us)   kernel")
+    for name, (cnt, gain, dur) in sorted(per.items(), key=lambda kv: -kv[1][1]):
+        print(f"{cnt:8d} {gain:16.1f} {gain / total:18.1%} {dur:16.1f}   {name}")
+
+
 def generate_workload(eng, args, rng, new_tokens=256, runs=3):
     """A batch of unequal prompts through the entry point: host token lists in, host
     token lists out.  Prints one line per run (the first pays for graph captures);
@@ -361,9 +398,10 @@ def main():
                     help="skip decoding at batch 1 and 64 and the 32-bit points")
     ap.add_argument("--all-configs", action="store_true",
                     help="also the 8B workload (unequal prompts, 256 steps) and the 32B points")
-    ap.add_argument("--only", default="", choices=["", "decode", "prefill", "timeline", "generate"],
+    ap.add_argument("--only", default="", choices=["", "decode", "prefill", "timeline", "prefill-timeline", "generate"],
                     help="run one part only and print its time (for profiling; no JSON line "
-                         "but for generate); timeline: when each kernel of one replayed decode "
+                         "but for generate); prefill-timeline: each kernel's share of one prefill "
+                         "step; timeline: when each kernel of one replayed decode "
                          "step ends; generate: --batch prompts of lengths uniform in [64, "
                          "--context], all in one step, then 256 tokens each through the Python "
                          "entry point")
@@ -414,6 +452,9 @@ def main():
 
     # ---- prefill of one prompt
     T = args.prefill_tokens
+    if args.only == "prefill-timeline":
+        prefill_timeline(eng, rng, T)
+        return 0
     pre_ms = prefill_timed(eng, rng, T)
     if args.only == "prefill":
         print(f"prefill {T} tokens: {pre_ms:.3f} ms")

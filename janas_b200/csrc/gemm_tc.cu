@@ -81,7 +81,7 @@ template <int BN, int MT, bool DEEP = false> struct TileCfg {
     static constexpr int A_TILE_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = MT * W_TILE_BYTES + A_TILE_BYTES;
     // 2 CTAs per SM for the small tiles that stream weights, 1 for the large ones
-    static constexpr int RING_BYTES = (BN <= 64 && MT == 1) ? (DEEP ? 110 : 100) * 1024 : 225 * 1024;
+    static constexpr int RING_BYTES = (BN <= 128 && MT == 1) ? (DEEP ? 110 : 100) * 1024 : 225 * 1024;
     static constexpr int STAGES = RING_BYTES / STAGE_BYTES < 2 ? 2 : (RING_BYTES / STAGE_BYTES > 8 ? 8 : RING_BYTES / STAGE_BYTES);
     static constexpr int TMEM_COLS = MT * BN <= 32 ? 32 : MT * BN <= 64 ? 64 : MT * BN <= 128 ? 128 : MT * BN <= 256 ? 256 : 512;
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment */ + 256 /* barriers */;
