@@ -375,7 +375,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         // next 32 is in flight while the last 32 are stored.
         int hgrp = (warp - 2) >> 2;             // which of the two warps of this quarter
         if (EPI == EPI_SWIGLU_HALF) {
-            if constexpr (MT == 1 && BN <= 64)
+            if constexpr (MT == 1 && BN <= 128)
                 store_swiglu_half<BN>(taddr, q, lane, hgrp, ok, (float *)smem, out_act, m0,
                                       second_off, n0, n);
         } else if (ok) {
@@ -651,9 +651,8 @@ extern "C" int jb_gemm_tc_swiglu(const void *A, const void *W, void *out_act, in
         return JB_SWIGLU_HALF(32);
     if (n <= 64)
         return JB_SWIGLU_HALF(64);
+    return JB_SWIGLU_HALF(128);
 #undef JB_SWIGLU_HALF
-    return launch_tc<128, 2, EPI_SWIGLU>(A, W, nullptr, (bf16 *)out_act, n, 2 * ff, k, 2 * ff, ff,
-                                         1, st);
 }
 
 // Reads and clears the error word: 0, or which wait ran out first (1: a free

@@ -19,7 +19,7 @@ public:
     // Rows up to which the one kernel runs too, in tiles of 64 gate and 64 up
     // features, if the plain product would not cut k either (a wide feed-forward:
     // the tiles alone fill the SMs).  It saves the activation kernel of a decode step.
-    static constexpr long long FUSED_UP_TO = 64;
+    static constexpr long long FUSED_UP_TO = 128;
 
     SwiGLU(const PartSpec &s, DType dt, Device *d) : FeedForward(s, dt, d) {
         hidden_ = s.get_int("hidden_size");
