@@ -196,8 +196,8 @@ __device__ __forceinline__ void store_swiglu(uint32_t taddr, int hgrp, bf16 *__r
 
 // The same for a tile whose TMEM lanes [0, 64) are gate features and [64, 128) the
 // up features of the same indices: the warps of the upper lanes hand their values
-// to the lower ones through shared memory (xch, 64 rows of BN + 1 floats: the ring's
-// first stage, which nothing reads any more).  All eight epilogue warps meet at the
+// to the lower ones through shared memory (xch, 64 rows of BN + 1 floats at the
+// start of the ring, which nothing reads any more).  All eight epilogue warps meet at the
 // barrier, whether their wait for the accumulator ran out or not.
 template <int BN>
 __device__ __forceinline__ void store_swiglu_half(uint32_t taddr, int q, int lane, int hgrp,

@@ -18,7 +18,8 @@ public:
     static constexpr long long FUSED_FROM = 512;
     // Rows up to which the one kernel runs too, in tiles of 64 gate and 64 up
     // features, if the plain product would not cut k either (a wide feed-forward:
-    // the tiles alone fill the SMs).  It saves the activation kernel of a decode step.
+    // the tiles alone fill the SMs).  It saves the activation kernel of a decode step
+    // and of a short prompt (a prompt of 128 tokens: 3.22 -> 3.13 ms).
     static constexpr long long FUSED_UP_TO = 128;
 
     SwiGLU(const PartSpec &s, DType dt, Device *d) : FeedForward(s, dt, d) {
