@@ -375,3 +375,82 @@ def test_a_model_of_toy_parts_is_registered_built_and_stepped():
         b = np.stack([batched[rid][p] for p in range(len(reqs[i]))])
         assert rel_err(b, want[i]) <= 1e-5, rid
     eng.cache.check()
+
+
+def test_a_toy_norm_is_registered_and_used_in_every_place_a_norm_stands():
+    """Another norm, defined here: a layer norm (mean taken off, a weight and a
+    bias), as the norm before the mixer, before the feed-forward and before the
+    head of a two-layer model.  Nothing in the framework knows it."""
+    from janas_b200.config import LayerSpec, ModelSpec, PartSpec, RunEntry
+    from janas_b200.engine import Engine, expected_tensors
+    from janas_b200.parts import Norm, register_norm
+    from janas_b200.weights import NORM, TensorSpec, random_tensors
+    from helpers import rel_err, run_trace, trace_tail, trace_whole
+
+    @register_norm("toy_layer_norm")
+    class LayerNorm(Norm):
+        def __init__(self, spec, dtype, device):
+            super().__init__(spec, dtype, device)
+            self.size, self.eps = int(spec.params["size"]), float(spec.params["eps"])
+
+        def tensors(self, prefix):
+            return {self._name(prefix, "weight"): TensorSpec((self.size,), NORM),
+                    self._name(prefix, "bias"): TensorSpec((self.size,), NORM)}
+
+        def load(self, prefix, tensors):
+            self.w = tensors[self._name(prefix, "weight")].float()
+            self.b = tensors[self._name(prefix, "bias")].float()
+
+        def apply(self, x, out_dtype, rows=None):
+            if rows is not None:
+                x = x[rows.long()]
+            c = x - x.mean(1, keepdim=True)
+            return (c / torch.sqrt(c.pow(2).mean(1, keepdim=True) + self.eps) * self.w + self.b).to(out_dtype)
+
+    dm = 40
+    norm = PartSpec("toy_layer_norm", {"size": dm, "eps": 1e-4})
+    rope = PartSpec("rope_neox", {"rotary_dim": 16, "theta": 1e4, "max_positions": 128})
+    att = PartSpec("gqa_attention", {"hidden_size": dm, "num_heads": 2, "num_kv_heads": 1, "head_dim": 16,
+                                     "qk_norm_eps": 1e-5, "window": 0, "position": rope})
+    ffn = PartSpec("swiglu", {"hidden_size": dm, "intermediate_size": 56})
+    layers = tuple(LayerSpec("prenorm", att, ffn, norm, norm, f"t.layers.{i}") for i in range(2))
+    spec = ModelSpec(architecture="ToyNorm", hidden_size=dm, vocab_size=61, max_positions=128, layers=layers,
+                     run_order=(RunEntry(0), RunEntry(1)), final_norm=norm, tie_embeddings=True,
+                     embedding_name="t.embed.weight", final_norm_name="t.norm")
+    names = expected_tensors(spec)
+    assert "t.layers.1.post_attention_layernorm.bias" in names and "t.norm.bias" in names
+    w = dict(random_tensors(names, 3, torch.float32))
+    eng = Engine.from_spec(spec, {n: t.to(DEV) for n, t in w.items()}, dtype="float32", max_tokens=512,
+                           max_seqs=2)
+
+    def ln(x, p):
+        c = x - x.mean(1, keepdim=True)
+        return c / torch.sqrt(c.pow(2).mean(1, keepdim=True) + 1e-4) * w[p + ".weight"] + w[p + ".bias"]
+
+    def plain_model(toks):
+        n = len(toks)
+        x = plain.embedding(w["t.embed.weight"], toks)
+        for i in range(2):
+            p = f"t.layers.{i}."
+            h = ln(x, p + "input_layernorm")
+            q = plain.rms_norm((h @ w[p + "self_attn.q_proj.weight"].T).view(n, 2, 16),
+                               w[p + "self_attn.q_norm.weight"], 1e-5)
+            k = plain.rms_norm((h @ w[p + "self_attn.k_proj.weight"].T).view(n, 1, 16),
+                               w[p + "self_attn.k_norm.weight"], 1e-5)
+            v = (h @ w[p + "self_attn.v_proj.weight"].T).view(n, 1, 16)
+            cs, sn = plain.rope_table(range(n), 16, 1e4)
+            q, k = plain.rope_neox(q, cs, sn), plain.rope_neox(k, cs, sn)
+            x = x + plain.attention(q, k, v, 0).reshape(n, 32) @ w[p + "self_attn.o_proj.weight"].T
+            x = x + plain.swiglu(ln(x, p + "post_attention_layernorm"), w, p + "mlp.", None)
+        return ln(x, "t.norm") @ w["t.embed.weight"].T
+
+    rng = np.random.default_rng(2)
+    reqs = [rng.integers(0, 61, size=n).tolist() for n in (9, 50)]
+    whole = run_trace(eng, trace_whole(reqs))
+    tail = run_trace(eng, trace_tail(reqs, 32))
+    for i, r in enumerate(reqs):
+        want = plain_model(r).numpy()
+        a = np.stack([whole[f"r{i}"][p] for p in range(len(r))])
+        b = np.stack([tail[f"r{i}"][p] for p in range(len(r))])
+        assert rel_err(a, want) <= 1e-5 and rel_err(b, want) <= 1e-5, i
+    eng.cache.check()
