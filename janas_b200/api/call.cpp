@@ -24,6 +24,7 @@
 //   gen.tokens_needed, gen.plan_batches, gen.finish_reason, gen.goes_on     the generation loop's decisions
 //   llm.open_foreign  {fn, user, max_batch}          -> {llm}: a handle whose engine is the callback fn
 //   llm.set           {llm, use_graphs, max_graphs, drop_graphs, trim}   switches of an open engine -> {use_graphs, graphs}
+//   llm.step_trace    {llm, entries: [{slot, tokens}]}   one step; -> {n_rows, hidden, layers}: the residual stream after every layer
 //   llm.launches      {}                             -> {launches}: kernels launched so far
 //   kernels.wait_selftest {limit_cycles}             -> {code}: a bounded wait that nothing ends (csrc/selftest.cu)
 #include <cstring>
@@ -720,6 +721,51 @@ static Json dispatch(const std::string &method, const Json &a, Json *error_detai
         }
         r.set("use_graphs", e.use_graphs);
         r.set("graphs", (long long)e.n_graphs());
+        return r;
+    }
+    if (method == "llm.step_trace") {
+        // {llm, entries: [{slot, tokens}]} -> {n_rows, hidden, layers: [[n_rows * hidden floats] per entry of
+        // the run order]}: one step whose residual stream is copied out after every layer
+        jb_llm *l = ptr_of<jb_llm>(a.get("llm"));
+        if (!l || !l->engine) fail(JB_LLM_EINVAL, "llm.step_trace: no engine behind this handle");
+        Engine &e = *l->engine;
+        std::vector<StepEntry> entries;
+        std::vector<std::vector<int32_t>> toks;
+        for (const Json &je : a.get("entries").items()) {
+            toks.emplace_back();
+            for (const Json &t : je.get("tokens").items()) toks.back().push_back((int32_t)t.as_int());
+        }
+        size_t i = 0;
+        long long rows = 0;
+        for (const Json &je : a.get("entries").items()) {
+            StepEntry se;
+            se.slot = (int)je.get("slot").as_int();
+            se.tokens = toks[i].data();
+            se.n = (long long)toks[i].size();
+            rows += se.n;
+            entries.push_back(se);
+            i++;
+        }
+        std::vector<std::vector<float>> layers;
+        e.trace = &layers;
+        try {
+            long long n_wanted = 0;
+            e.step(entries, &n_wanted);
+            e.dev->sync();
+        } catch (...) {
+            e.trace = nullptr;
+            throw;
+        }
+        e.trace = nullptr;
+        Json out = Json::array();
+        for (auto &v : layers) {
+            Json row = Json::array();
+            for (float f : v) row.push((double)f);
+            out.push(std::move(row));
+        }
+        r.set("n_rows", rows);
+        r.set("hidden", e.model->spec.hidden_size);
+        r.set("layers", std::move(out));
         return r;
     }
     if (method == "llm.launches") {

@@ -241,6 +241,7 @@ Buf Engine::step(const std::vector<StepEntry> &entries, long long *n_wanted) {
     ctx.seq_len = p.lens;
     ctx.seq_row0 = row0;
     ctx.max_pos = max_pos;
+    ctx.trace = trace;
     std::map<const KVGroup *, std::pair<const int32_t *, int>> bt;
     for (size_t gi = 0; gi < cache->groups.size(); gi++)
         bt[cache->groups[gi].get()] = {d + tab_off[gi], widths[gi]};

@@ -102,6 +102,10 @@ public:
     // entry's want (an empty Buf when nothing is wanted).  The work is queued on
     // the device's stream; the caller synchronizes (or copies on that stream).
     Buf step(const std::vector<StepEntry> &entries, long long *n_wanted);
+    // When set, the next steps also leave the residual stream after every entry of
+    // the run order here (see StepContext::trace): a tool for finding the first
+    // layer that goes wrong, not a product path.
+    std::vector<std::vector<float>> *trace = nullptr;
 
     // One decode step for sequences that each go on by one token, with the choice
     // of the next token on the device.  decode_begin launches and returns at once;

@@ -271,6 +271,17 @@ class Engine:
         self._step(entries, out.ctypes.data, out.size)
         return out
 
+    def step_trace(self, entries: Sequence[StepEntry]) -> List[np.ndarray]:
+        """One step (no logits) whose residual stream is copied out after every
+        entry of the model's run order: a list of float32 arrays [rows, hidden],
+        rows being the entries' tokens one entry after the other.  For finding the
+        first layer that goes wrong against a plain implementation; slow."""
+        entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
+        res = lib.call("llm.step_trace", llm=self._h.value,
+                       entries=[{"slot": int(e.slot), "tokens": [int(t) for t in e.tokens]} for e in entries])
+        n, hidden = int(res["n_rows"]), int(res["hidden"])
+        return [np.asarray(layer, dtype=np.float32).reshape(n, hidden) for layer in res["layers"]]
+
     # ---------------------------------------------------------------- decode
     def set_sampler(self, slot: int, options) -> None:
         """The sampling settings of one sequence (a GenOptions); the seed restarts

@@ -174,8 +174,20 @@ Buf DecoderModel::forward(StepContext &ctx, const int32_t *tokens, std::vector<L
     long long n = ctx.n_rows;
     Buf x = ops::embed(d, embedding, tokens, n);
     Stack pending;
-    for (size_t e = 0; e < spec.run_order.size(); e++)
+    for (size_t e = 0; e < spec.run_order.size(); e++) {
         blocks[(size_t)spec.run_order[e].layer]->forward(ctx, x.as<float>(), pending, caches[e]);
+        if (ctx.trace) {
+            if (pending) {
+                ops::add_(d, x.as<float>(), n, spec.hidden_size, pending);
+                pending = Stack();
+            }
+            std::vector<float> host((size_t)n * (size_t)spec.hidden_size);
+            cuda_check(cudaMemcpyAsync(host.data(), x.ptr, host.size() * 4, cudaMemcpyDeviceToHost, d.stream),
+                       "copying the residual stream");
+            d.sync();
+            ctx.trace->push_back(std::move(host));
+        }
+    }
     if (n_want == 0) return Buf();
     bool all = n_want < 0;
     Buf h = final_norm->apply(ctx, x.as<float>(), n, ctx.dtype, pending ? &pending : nullptr,

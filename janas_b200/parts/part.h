@@ -68,6 +68,10 @@ struct StepContext {
     std::vector<long long> seq_row0;     // first row of each sequence (n_seqs + 1 values)
     long long max_pos = 0;               // the largest position of any row (a bound, in a captured step)
     bool captured = false;               // the launches are being recorded into a graph
+    // For finding the first layer that goes wrong: when set, the model copies the
+    // residual stream [n_rows, hidden] to the host after every entry of the run
+    // order (what is still to be added is added first), one vector per entry.
+    std::vector<std::vector<float>> *trace = nullptr;
     // what a part computed once for all layers of this step (the attention's blocks)
     struct Extra { Buf buf; int n = 0; };
     std::map<std::string, Extra> extras;

@@ -168,3 +168,33 @@ def test_batches_drawn_at_random(name, seed, dtype):
             a = np.stack([alone[f"r{k}"][p] for p in range(len(toks))])
             b = np.stack([got[rid][p] for p in range(len(toks))])
             assert rel_err(b, a) <= FP32_CUT_TOL, f"{name} {rid}: batched and alone differ"
+
+
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("B", "float32"), ("C", "bfloat16")])
+def test_the_residual_stream_after_every_layer_is_the_plain_model_s(name, dtype):
+    """``Engine.step_trace`` copies the residual stream out after every layer: a whole
+    prompt, then its continuation in a second step from the cache, each against
+    the plain model's trace of the same positions.  It is the tool that finds the
+    first layer that goes wrong; here every layer is right."""
+    import plain_qwen3 as plain
+    from helpers import plain_model
+    c, w = plain_model(name)
+    toks = requests(name)[-1]
+    cut = len(toks) - 5
+    want = []
+    plain.forward(c, w, toks, trace=want)
+    eng = engine(name, dtype)
+    slot = eng.new_sequence()
+    try:
+        first = eng.step_trace([(slot, toks[:cut], [])])
+        rest = eng.step_trace([(slot, toks[cut:], [])])
+    finally:
+        eng.free_sequence(slot)
+    assert len(first) == len(rest) == c["num_hidden_layers"] == len(want)
+    tol = 2e-5 if dtype == "float32" else 3e-2
+    for layer, (a, b, x) in enumerate(zip(first, rest, want)):
+        x = x.numpy()
+        assert a.shape == (cut, c["hidden_size"]) and b.shape == (len(toks) - cut, c["hidden_size"])
+        assert rel_err(a, x[:cut]) <= tol, (layer, rel_err(a, x[:cut]))
+        assert rel_err(b, x[cut:]) <= tol, (layer, rel_err(b, x[cut:]))
+    eng.cache.check()
